@@ -1,0 +1,128 @@
+/*
+ * mixedgemm_c.h - C ABI of the B200 (sm_100a) implementation of MixedGemm's hot path:
+ * activation / weight reorder-and-quantise followed by the mixed MXFP4/6/8 x MXFP4
+ * block-scaled GEMM.
+ *
+ * Conventions for every entry point:
+ *   - plain pointers and sizes only; all data pointers are DEVICE pointers on the
+ *     current CUDA device unless a comment says "host";
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream); calls are
+ *     asynchronous, never synchronise the device and never print;
+ *   - the return value is an MG_* status; nothing throws or exits;
+ *   - output buffers are caller-owned; the library allocates no device memory.
+ *
+ * Paths below (src/..., include/...) are relative to the MixedGemm project and name
+ * the reference interface each entry point replaces.
+ */
+#ifndef MIXEDGEMM_C_H
+#define MIXEDGEMM_C_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "fp4.h"
+#include "fp6.h"
+#include "fp8.h"
+#include "mxdtype.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  MG_OK = 0,
+  MG_ERR_SHAPE = 1,      /* a size is not supported (segments must be multiples of 32, ...) */
+  MG_ERR_NULL = 2,       /* a required pointer is NULL */
+  MG_ERR_ALIGN = 3,      /* a pointer or pitch breaks an alignment rule */
+  MG_ERR_WORKSPACE = 4,  /* workspace missing or too small */
+  MG_ERR_CUDA = 5,       /* a CUDA runtime / driver call failed (see mg_last_cuda_error) */
+  MG_ERR_DEVICE = 6,     /* the device is not an sm_100 part */
+  MG_ERR_TIMEOUT = 7     /* a kernel gave up on a bounded wait (see mg_device_status) */
+};
+
+/* Human-readable text of a status. */
+const char* mg_strerror(int status);
+
+/* cudaError_t value of the last failing CUDA call seen by this library on this thread. */
+int mg_last_cuda_error(void);
+
+/* Library version, major*100 + minor. */
+int mg_version(void);
+
+/*
+ * Reads and clears the device-side error word that kernels set when a bounded wait
+ * expires.  Synchronises `stream`.  *status receives 0 or a kernel-specific code.
+ */
+int mg_device_status(int* status_host, void* stream);
+
+/* Bytes of a scale buffer for `rows` rows of a `kseg`-element segment: whole atoms,
+ * ceil(rows/128) * ceil(kseg/128) * 512. */
+size_t mg_sf_bytes(int rows, int kseg);
+
+/*
+ * Activation reorder-and-quantise.
+ * Replaces run_reorder_bf16_mixed<32,K> (include/reorder.cuh:295-308, src/reorder.cu:434-469)
+ * and its kernel reorder_bf16_mixed_kernel (src/reorder.cu:94-269), for any K = KN+KS+KO with
+ * all three multiples of 32 and K <= 32736.
+ *   X      [M,K] bf16 row-major, 16-byte aligned
+ *   idx    [K]   int16: reordered position j takes input channel idx[j]
+ *   AN     [M,KN/2]    AS [M,3*KS/4]    AO [M,KO]          packed codes (mxdtype.h)
+ *   SFAN / SFAS / SFAO  at least mg_sf_bytes(M, KN / KS / KO) bytes each; only the
+ *          positions of real (row, 32-block) pairs are written.
+ * A segment of size 0 may pass NULL buffers.
+ */
+int mg_reorder_quantize_x(const void* X, int M, int K, const int16_t* idx, int KN, int KS, int KO,
+                          uint8_t* AN, uint8_t* AS, uint8_t* AO, uint8_t* SFAN, uint8_t* SFAS,
+                          uint8_t* SFAO, void* stream);
+
+/*
+ * Weight reorder-and-quantise: all three segments become MXFP4.
+ * Replaces run_reorder_bf16_fp4<32,K> (include/reorder.cuh:310-323, src/reorder.cu:471-506)
+ * and reorder_bf16_fp4_kernel (src/reorder.cu:271-432).
+ *   W [N,K] bf16;  BN [N,KN/2]  BS [N,KS/2]  BO [N,KO/2];  SFB* as above with rows = N.
+ */
+int mg_reorder_quantize_w(const void* W, int N, int K, const int16_t* idx, int KN, int KS, int KO,
+                          uint8_t* BN, uint8_t* BS, uint8_t* BO, uint8_t* SFBN, uint8_t* SFBS,
+                          uint8_t* SFBO, void* stream);
+
+/*
+ * Bytes of scratch mg_matmul needs for this problem (0 when every segment is a multiple
+ * of 128 elements).  Segments that are only multiples of 64 are first copied to a
+ * 128-padded pitch there, because the tensor-map types that unpack FP4/FP6 need it.
+ */
+size_t mg_matmul_workspace_bytes(int M, int N, int KN, int KS, int KO);
+
+/*
+ * Mixed block-scaled GEMM:  D[M,N] = bf16( sum over the three segments of A_seg * B_seg^T
+ * (+ C when C != NULL) ), fp32 accumulation in one accumulator, one rounding at the end.
+ * Replaces matmul_host (include/gemm.h:21-41, src/gemm.cu:22-47) and the three CUTLASS
+ * GEMMs it chains (src/fp4.cu, src/fp6.cu, src/fp8.cu).
+ *   AN/AS/AO, SFAN/SFAS/SFAO   as written by mg_reorder_quantize_x (M rows)
+ *   BN/BS/BO, SFBN/SFBS/SFBO   as written by mg_reorder_quantize_w (N rows, N % 128 == 0)
+ *   D      [M,N] bf16, row pitch `ldd` elements (ldd % 8 == 0, 16-byte aligned base)
+ *   C      optional [M,N] bf16 with the same pitch, added before the final rounding
+ *   workspace / workspace_bytes   scratch of mg_matmul_workspace_bytes() bytes, 1024-aligned
+ * Segments must be multiples of 64 (KN of 128); code buffers 32-byte aligned.
+ */
+int mg_matmul(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, const uint8_t* BS,
+              const uint8_t* AO, const uint8_t* BO, int M, int N, int KN, int KS, int KO,
+              const void* C_bf16, void* D_bf16, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
+              const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
+              void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Same product with the fp32 accumulator written unrounded: D_f32 [M,N] float, pitch `ldd`
+ * elements (ldd % 4 == 0).  The reference has no such output (its GEMMs write bf16,
+ * src/fp4.cu:175-179); it exists so that the accumulation can be checked against a
+ * float64 product without the bf16 rounding step in between.
+ */
+int mg_matmul_f32(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, const uint8_t* BS,
+                  const uint8_t* AO, const uint8_t* BO, int M, int N, int KN, int KS, int KO,
+                  const void* C_bf16, float* D_f32, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
+                  const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,66 @@
+"""ctypes binding of libmixedgemm_b200.so (the C ABI declared in include/mixedgemm_c.h).
+
+The library is the product path: there is no Python or CPU fallback.  If the shared
+library is missing, importing this module raises with the build command.
+"""
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libmixedgemm_b200.so")
+
+MG_OK = 0
+STATUS_NAMES = {0: "MG_OK", 1: "MG_ERR_SHAPE", 2: "MG_ERR_NULL", 3: "MG_ERR_ALIGN", 4: "MG_ERR_WORKSPACE",
+                5: "MG_ERR_CUDA", 6: "MG_ERR_DEVICE", 7: "MG_ERR_TIMEOUT"}
+
+# every symbol include/*.h declares, with its prototype
+_vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+PROTOTYPES = {
+    "mg_strerror": (ctypes.c_char_p, [_i]),
+    "mg_last_cuda_error": (_i, []),
+    "mg_version": (_i, []),
+    "mg_device_status": (_i, [ctypes.POINTER(_i), _vp]),
+    "mg_sf_bytes": (_sz, [_i, _i]),
+    "mg_reorder_quantize_x": (_i, [_vp, _i, _i, _vp, _i, _i, _i] + [_vp] * 6 + [_vp]),
+    "mg_reorder_quantize_w": (_i, [_vp, _i, _i, _vp, _i, _i, _i] + [_vp] * 6 + [_vp]),
+    "mg_matmul_workspace_bytes": (_sz, [_i] * 5),
+    "mg_matmul": (_i, [_vp] * 6 + [_i] * 5 + [_vp, _vp, _i] + [_vp] * 6 + [_vp, _sz, _vp]),
+    "mg_matmul_f32": (_i, [_vp] * 6 + [_i] * 5 + [_vp, _vp, _i] + [_vp] * 6 + [_vp, _sz, _vp]),
+    "mg_matmul_fp4": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "mg_matmul_fp6": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "mg_matmul_fp8": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+}
+
+_lib = None
+
+
+def load():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                "libmixedgemm_b200.so is not built; run `python -m mixedgemm_b200.build` "
+                "(nvcc for sm_100a).  There is no fallback path.")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+class MixedGemmError(RuntimeError):
+    def __init__(self, status, where):
+        lib = load()
+        msg = lib.mg_strerror(status).decode()
+        extra = ""
+        if status == 5:
+            extra = " (cudaError %d)" % lib.mg_last_cuda_error()
+        super().__init__("%s: %s [%s]%s" % (where, msg, STATUS_NAMES.get(status, status), extra))
+        self.status = status
+
+
+def check(status, where):
+    if status != MG_OK:
+        raise MixedGemmError(status, where)

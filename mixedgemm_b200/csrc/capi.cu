@@ -1,0 +1,92 @@
+// Status, device queries and small helpers of the C ABI.
+#include <mutex>
+
+#include "mg_common.h"
+
+namespace {
+thread_local int tl_last_cuda_error = 0;
+
+// Set by kernels whose bounded waits expire; read and cleared by mg_device_status().
+__device__ int g_device_status = 0;
+
+constexpr int kMaxDevices = 64;
+mg::DeviceInfo g_info[kMaxDevices];
+bool g_info_ok[kMaxDevices];
+int* g_status_ptr[kMaxDevices];
+std::mutex g_mu;
+}  // namespace
+
+namespace mg {
+
+int note_cuda_error(cudaError_t e) {
+  tl_last_cuda_error = (int)e;
+  return MG_ERR_CUDA;
+}
+
+int device_info(DeviceInfo* out) {
+  int dev = 0;
+  MG_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return MG_ERR_DEVICE;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_info_ok[dev]) {
+    DeviceInfo di;
+    MG_CUDA_TRY(cudaDeviceGetAttribute(&di.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    MG_CUDA_TRY(cudaDeviceGetAttribute(&di.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    MG_CUDA_TRY(cudaDeviceGetAttribute(&di.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    g_info[dev] = di;
+    g_info_ok[dev] = true;
+  }
+  *out = g_info[dev];
+  return out->cc_major == 10 ? MG_OK : MG_ERR_DEVICE;
+}
+
+int device_status_word(int** dev_ptr) {
+  int dev = 0;
+  MG_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return MG_ERR_DEVICE;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_status_ptr[dev]) {
+    void* p = nullptr;
+    MG_CUDA_TRY(cudaGetSymbolAddress(&p, g_device_status));
+    g_status_ptr[dev] = static_cast<int*>(p);
+  }
+  *dev_ptr = g_status_ptr[dev];
+  return MG_OK;
+}
+
+}  // namespace mg
+
+extern "C" const char* mg_strerror(int status) {
+  switch (status) {
+    case MG_OK: return "ok";
+    case MG_ERR_SHAPE: return "unsupported shape";
+    case MG_ERR_NULL: return "null pointer";
+    case MG_ERR_ALIGN: return "misaligned pointer or pitch";
+    case MG_ERR_WORKSPACE: return "workspace missing or too small";
+    case MG_ERR_CUDA: return "CUDA call failed";
+    case MG_ERR_DEVICE: return "device is not sm_100";
+    case MG_ERR_TIMEOUT: return "kernel gave up on a bounded wait";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int mg_last_cuda_error(void) { return tl_last_cuda_error; }
+
+extern "C" int mg_version(void) { return 1; }
+
+extern "C" size_t mg_sf_bytes(int rows, int kseg) {
+  if (rows <= 0 || kseg <= 0) return 0;
+  return (size_t)((rows + 127) / 128) * (size_t)((kseg + 127) / 128) * 512;
+}
+
+extern "C" int mg_device_status(int* status_host, void* stream) {
+  if (!status_host) return MG_ERR_NULL;
+  int* dptr = nullptr;
+  int rc = mg::device_status_word(&dptr);
+  if (rc != MG_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MG_CUDA_TRY(cudaStreamSynchronize(st));
+  MG_CUDA_TRY(cudaMemcpy(status_host, dptr, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*status_host != 0) MG_CUDA_TRY(cudaMemset(dptr, 0, sizeof(int)));
+  return MG_OK;
+}

@@ -1,0 +1,552 @@
+// Mixed MXFP4 / MXFP6 / MXFP8 x MXFP4 block-scaled GEMM for sm_100a.
+//
+// One persistent, warp-specialised kernel carries all three K segments of MixedGemm's
+// matmul_host (src/gemm.cu:22-47 of that project, three chained CUTLASS GEMMs there) in a
+// single fp32 accumulator in tensor memory:
+//   warp 0      TMA producer: A / B tiles (tiled tensor maps, 128-byte swizzle) and the
+//               512-byte scale atoms (1-D bulk copies) into a ring of shared-memory stages
+//   warp 1      MMA issuer: copies the scale atoms to TMEM (tcgen05.cp) and issues
+//               tcgen05.mma kind::mxf4 (FP4 segment, K=64 per instruction) or
+//               kind::mxf8f6f4 (FP6 / FP8 segments, K=32 per instruction)
+//   warps 2-5   epilogue: tcgen05.ld the accumulator, round once to bf16, store
+// Every stage is 128 bytes of K per row for both operands: 256 FP4 elements in the FP4
+// segment (dense nibbles), 128 elements in the FP6 / FP8 segments, where the tensor-map
+// types 16U6_ALIGN16B / 16U4_ALIGN16B expand the packed FP6 / FP4 rows to the
+// one-byte-per-element slots kind::mxf8f6f4 reads.
+// All waits are bounded; on expiry a kernel records a code in the device status word,
+// tells the other roles of its CTA to stop, frees its tensor memory and returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_bf16.h>
+
+#include <cstdlib>
+#include <mutex>
+
+#include "mg_common.h"
+#include "ptx_sm100.cuh"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
+
+struct SegParams {
+  int kseg;     // valid elements of the segment
+  int nstages;  // pipeline stages it takes
+  int katoms;   // scale atoms along K: ceil(kseg / 128)
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+};
+
+struct GemmParams {
+  int M, N, ldd;
+  int tiles_m, tiles_n;
+  SegParams seg[3];
+  const __nv_bfloat16* C;
+  __nv_bfloat16* D;
+  float* Df32;  // when set, the fp32 accumulator is stored here instead of D
+  int* status;
+  uint32_t tx_a[3], tx_b[3];  // bytes one A / B tile load of the segment signals
+};
+
+// Bounded mbarrier wait.  Returns false when the CTA is stopping.
+__device__ __forceinline__ bool wait_parity(uint32_t bar, uint32_t parity, volatile int* stop, int* status,
+                                            int code) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t spin = 1;; ++spin) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    if ((spin & 63u) == 0) {
+      if (*stop) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *stop = 1;
+        atomicOr(status, code);
+        return false;
+      }
+    }
+  }
+}
+
+template <int BN>
+struct Cfg {
+  static constexpr int STAGES = BN == 128 ? 6 : 4;
+  static constexpr int ACC = BN == 128 ? 2 : 1;
+  static constexpr int NB = BN / 128;
+  static constexpr uint32_t A_BYTES = BM * 128;
+  static constexpr uint32_t B_BYTES = BN * 128;
+  static constexpr uint32_t SFA_BYTES = 1024;      // up to two atoms
+  static constexpr uint32_t SFB_BYTES = NB * 1024;  // up to two atoms per 128 columns
+  static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr uint32_t SF_SLOT_COLS = 8 + NB * 8;  // TMEM columns of one scale slot
+  static constexpr uint32_t SF_COL0 = ACC * BN;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static_assert(SF_COL0 + 2 * SF_SLOT_COLS <= kTmemCols, "tensor memory budget");
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
+                  const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmA1,
+                  const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmA2,
+                  const __grid_constant__ CUtensorMap tmB2) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - raw);
+  const uint32_t bar0 = base + C::STAGES * C::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + C::ACC + a); };
+  volatile uint32_t* tmem_holder =
+      reinterpret_cast<volatile uint32_t*>(gbase + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 2 * C::ACC));
+  volatile int* stop = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < C::ACC; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 4);
+    }
+    *stop = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tmap(&tmA0);
+    ptx::prefetch_tmap(&tmB0);
+    ptx::prefetch_tmap(&tmA1);
+    ptx::prefetch_tmap(&tmB1);
+    ptx::prefetch_tmap(&tmA2);
+    ptx::prefetch_tmap(&tmB2);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int total_tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool live = true;
+      for (int t = blockIdx.x; t < total_tiles && live; t += gridDim.x) {
+        const int m_tile = t % p.tiles_m, n_tile = t / p.tiles_m;
+        for (int seg = 0; seg < 3 && live; ++seg) {
+          const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
+          const CUtensorMap* ta = seg == 0 ? &tmA0 : (seg == 1 ? &tmA1 : &tmA2);
+          const CUtensorMap* tb = seg == 0 ? &tmB0 : (seg == 1 ? &tmB1 : &tmB2);
+          const uint32_t tx_ab = seg == 0 ? p.tx_a[0] + p.tx_b[0]
+                                          : (seg == 1 ? p.tx_a[1] + p.tx_b[1] : p.tx_a[2] + p.tx_b[2]);
+          for (int s = 0; s < sp.nstages; ++s) {
+            if (!wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, 1)) { live = false; break; }
+            const int atom0 = seg == 0 ? 2 * s : s;
+            const int natoms = seg == 0 ? min(2, sp.katoms - atom0) : 1;
+            const uint32_t sbase = base + stage * C::STAGE_BYTES;
+            const uint32_t fb = full_bar(stage);
+            ptx::mbar_expect_tx(fb, tx_ab + (uint32_t)natoms * 512u * (1 + C::NB));
+            ptx::tma_load_2d(sbase, ta, s * 128, m_tile * BM, fb);
+            ptx::tma_load_2d(sbase + C::A_BYTES, tb, s * 128, n_tile * BN, fb);
+            ptx::bulk_load_1d(sbase + C::A_BYTES + C::B_BYTES,
+                              sp.sfa + ((size_t)m_tile * sp.katoms + atom0) * 512, natoms * 512, fb);
+#pragma unroll
+            for (int nb = 0; nb < C::NB; ++nb)
+              ptx::bulk_load_1d(sbase + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + nb * 1024,
+                                sp.sfb + ((size_t)(n_tile * C::NB + nb) * sp.katoms + atom0) * 512,
+                                natoms * 512, fb);
+            if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptors: scale type UE8M0, M = 128, N = BN, both operands K-major
+      const uint32_t common = ((uint32_t)(BN >> 3) << 17) | (1u << 23) | ((uint32_t)(BM >> 4) << 24);
+      const uint32_t idesc[3] = {common | (1u << 7) | (1u << 10),   // mxf4: E2M1 x E2M1
+                                 common | (4u << 7) | (5u << 10),   // E3M2 x E2M1
+                                 common | (0u << 7) | (5u << 10)};  // E4M3 x E2M1
+      int stage = 0;
+      uint32_t phase = 0, slot = 0;
+      bool live = true;
+      int it = 0;
+      for (int t = blockIdx.x; t < total_tiles && live; t += gridDim.x, ++it) {
+        const int acc = it % C::ACC;
+        const uint32_t acc_phase = (uint32_t)(it / C::ACC) & 1u;
+        if (!wait_parity(tempty_bar(acc), acc_phase ^ 1u, stop, p.status, 4)) { live = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+        uint32_t accumulate = 0;
+        for (int seg = 0; seg < 3 && live; ++seg) {
+          const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
+          const uint32_t id0 = seg == 0 ? idesc[0] : (seg == 1 ? idesc[1] : idesc[2]);
+          for (int s = 0; s < sp.nstages; ++s) {
+            if (!wait_parity(full_bar(stage), phase, stop, p.status, 2)) { live = false; break; }
+            ptx::tc_fence_after();
+            const uint32_t sbase = base + stage * C::STAGE_BYTES;
+            const uint32_t sfa_s = sbase + C::A_BYTES + C::B_BYTES;
+            const uint32_t sfb_s = sfa_s + C::SFA_BYTES;
+            const uint32_t sfa_t = tmem_base + C::SF_COL0 + slot * C::SF_SLOT_COLS;
+            const uint32_t sfb_t = sfa_t + 8;
+            const int atom0 = seg == 0 ? 2 * s : s;
+            const int natoms = seg == 0 ? min(2, sp.katoms - atom0) : 1;
+            for (int a = 0; a < natoms; ++a) {
+              ptx::tc_cp_sf(sfa_t + a * 4, ptx::smem_desc_sf(sfa_s + a * 512));
+#pragma unroll
+              for (int nb = 0; nb < C::NB; ++nb)
+                ptx::tc_cp_sf(sfb_t + a * (C::NB * 4) + nb * 4, ptx::smem_desc_sf(sfb_s + nb * 1024 + a * 512));
+            }
+            const uint64_t adesc = ptx::smem_desc_sw128(sbase);
+            const uint64_t bdesc = ptx::smem_desc_sw128(sbase + C::A_BYTES);
+            if (seg == 0) {
+              const int nm = min(4, (sp.kseg - s * 256) >> 6);
+              for (int j = 0; j < nm; ++j) {
+                const uint32_t a = j >> 1, sfid = (j & 1) * 2;
+                ptx::mma_mxf4(d_tmem, adesc + j * 2, bdesc + j * 2, id0 | (sfid << 4) | (sfid << 29),
+                              sfa_t + a * 4, sfb_t + a * (C::NB * 4), accumulate);
+                accumulate = 1;
+              }
+            } else {
+              const int nm = min(4, (sp.kseg - s * 128) >> 5);
+              for (int j = 0; j < nm; ++j) {
+                ptx::mma_mxf8f6f4(d_tmem, adesc + j * 2, bdesc + j * 2,
+                                  id0 | ((uint32_t)j << 4) | ((uint32_t)j << 29), sfa_t, sfb_t, accumulate);
+                accumulate = 1;
+              }
+            }
+            ptx::tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+            slot ^= 1u;
+            if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+        if (live) ptx::tc_commit(tfull_bar(acc));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps)
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    int it = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      const int m_tile = t % p.tiles_m, n_tile = t / p.tiles_m;
+      const int acc = it % C::ACC;
+      const uint32_t acc_phase = (uint32_t)(it / C::ACC) & 1u;
+      bool ok = wait_parity(tfull_bar(acc), acc_phase, stop, p.status, 8);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      const int row = m_tile * BM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * BN;
+      const size_t goff = (size_t)row * p.ldd + (size_t)n_tile * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr + c * 32, r);
+        ptx::tmem_ld_wait();
+        if (row < p.M) {
+          if (p.C != nullptr) {
+            const uint4* cp = reinterpret_cast<const uint4*>(p.C + goff + c * 32);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const uint4 cv = cp[v];
+              const uint32_t w[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                r[v * 8 + k * 2] = __float_as_uint(__uint_as_float(r[v * 8 + k * 2]) + __uint_as_float(w[k] << 16));
+                r[v * 8 + k * 2 + 1] =
+                    __float_as_uint(__uint_as_float(r[v * 8 + k * 2 + 1]) + __uint_as_float(w[k] & 0xFFFF0000u));
+              }
+            }
+          }
+          if (p.Df32 != nullptr) {
+            uint4* fp = reinterpret_cast<uint4*>(p.Df32 + goff + c * 32);
+#pragma unroll
+            for (int v = 0; v < 8; ++v) fp[v] = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+            continue;
+          }
+          uint4* dp = reinterpret_cast<uint4*>(p.D + goff + c * 32);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + k * 2]),
+                                                       __uint_as_float(r[v * 8 + k * 2 + 1]));
+              w[k] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            dp[v] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  if (*stop) {
+    // give copies and MMAs that are still in flight time to land before the CTA goes away
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// Copies `rows` rows of `src_pitch` bytes to a wider pitch, zero-filling the tail; up to
+// four such jobs per launch (blockIdx.y).  Used for segments that are not a multiple of 128.
+struct RepackJob {
+  const uint8_t* src;
+  uint8_t* dst;
+  int rows, src_pitch, dst_pitch;
+};
+struct RepackJobs {
+  RepackJob j[4];
+};
+
+__global__ void repack_rows_kernel(const RepackJobs jobs) {
+  const RepackJob jb = blockIdx.y == 0 ? jobs.j[0] : blockIdx.y == 1 ? jobs.j[1] : blockIdx.y == 2 ? jobs.j[2] : jobs.j[3];
+  const int words = jb.dst_pitch >> 2, src_words = jb.src_pitch >> 2;
+  const size_t total = (size_t)jb.rows * words;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / words), w = (int)(i - (size_t)r * words);
+    uint32_t v = 0;
+    if (w < src_words) v = reinterpret_cast<const uint32_t*>(jb.src + (size_t)r * jb.src_pitch)[w];
+    reinterpret_cast<uint32_t*>(jb.dst + (size_t)r * jb.dst_pitch)[w] = v;
+  }
+}
+
+// ---------------------------------------------------------------- host side
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+std::once_flag g_encode_once;
+
+int get_encoder(PFN_cuTensorMapEncodeTiled_v12000* out) {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  });
+  *out = g_encode;
+  return g_encode ? MG_OK : MG_ERR_CUDA;
+}
+
+// 2-D K-major operand: `kdim` elements of type `dt` per row, `rows` rows, `pitch` bytes.
+int make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, uint64_t kdim, uint64_t rows,
+             uint64_t pitch, uint32_t box_k, uint32_t box_rows) {
+  PFN_cuTensorMapEncodeTiled_v12000 enc;
+  if (get_encoder(&enc) != MG_OK) return MG_ERR_CUDA;
+  cuuint64_t dims[2] = {kdim, rows};
+  cuuint64_t strides[1] = {pitch};
+  cuuint32_t box[2] = {box_k, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    mg::note_cuda_error(cudaErrorInvalidValue);
+    return MG_ERR_CUDA;
+  }
+  return MG_OK;
+}
+
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Workspace {
+  size_t as, bs, ao, bo, total;
+  int ksp, kop;  // padded segment sizes
+};
+
+Workspace plan_workspace(int M, int N, int KS, int KO) {
+  Workspace w{};
+  w.ksp = round_up(KS, 128);
+  w.kop = round_up(KO, 128);
+  size_t off = 0;
+  if (w.ksp != KS) {
+    w.as = off; off = align_up(off + (size_t)M * (w.ksp / 4 * 3), 1024);
+    w.bs = off; off = align_up(off + (size_t)N * (w.ksp / 2), 1024);
+  }
+  if (w.kop != KO) {
+    w.ao = off; off = align_up(off + (size_t)M * w.kop, 1024);
+    w.bo = off; off = align_up(off + (size_t)N * (w.kop / 2), 1024);
+  }
+  w.total = off;
+  return w;
+}
+
+int choose_bn(int M, int N, int sms) {
+  if (const char* e = std::getenv("MG_GEMM_BN")) {
+    int v = std::atoi(e);
+    if (v == 128 || (v == 256 && N % 256 == 0)) return v;
+  }
+  if (N % 256 != 0) return 128;
+  const int tm = (M + BM - 1) / BM;
+  auto eff = [&](int bn, double w) {
+    const int tiles = tm * (N / bn);
+    const int waves = (tiles + sms - 1) / sms;
+    return w * (double)tiles / ((double)waves * sms);
+  };
+  return eff(256, 1.0) >= eff(128, 0.92) ? 256 : 128;
+}
+
+template <int BN>
+int launch_gemm(const GemmParams& p, const CUtensorMap* maps, int sms, cudaStream_t st) {
+  using C = Cfg<BN>;
+  auto kern = mixed_gemm_kernel<BN>;
+  MG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sms ? tiles : sms;
+  kern<<<grid, kThreads, C::SMEM, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
+  MG_CUDA_TRY(cudaGetLastError());
+  return MG_OK;
+}
+
+}  // namespace
+
+extern "C" size_t mg_matmul_workspace_bytes(int M, int N, int KN, int KS, int KO) {
+  (void)KN;
+  if (M <= 0 || N <= 0 || KS < 0 || KO < 0) return 0;
+  return plan_workspace(M, N, KS, KO).total;
+}
+
+static int matmul_impl(bool f32_out, const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
+                       const uint8_t* AO, const uint8_t* BO, int M, int N, int KN, int KS, int KO,
+                       const void* C_bf16, void* D_bf16, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
+                       const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  if (M < 0 || N <= 0 || KN < 0 || KS < 0 || KO < 0 || KN + KS + KO <= 0) return MG_ERR_SHAPE;
+  if (KN % 128 || KS % 64 || KO % 64 || N % 128 || ldd < N || ldd % 8) return MG_ERR_SHAPE;
+  if (M == 0) return MG_OK;
+  if (!D_bf16) return MG_ERR_NULL;
+  if ((KN && (!AN || !BN_ || !SFAN || !SFBN)) || (KS && (!AS || !BS || !SFAS || !SFBS)) ||
+      (KO && (!AO || !BO || !SFAO || !SFBO)))
+    return MG_ERR_NULL;
+  if (!mg::aligned(D_bf16, 16) || !mg::aligned(C_bf16, 16)) return MG_ERR_ALIGN;
+  const void* ptrs[] = {AN, BN_, AS, BS, AO, BO};
+  for (const void* q : ptrs)
+    if (!mg::aligned(q, 32)) return MG_ERR_ALIGN;
+  const void* sfs[] = {SFAN, SFBN, SFAS, SFBS, SFAO, SFBO};
+  for (const void* q : sfs)
+    if (!mg::aligned(q, 16)) return MG_ERR_ALIGN;
+
+  mg::DeviceInfo di;
+  int rc = mg::device_info(&di);
+  if (rc != MG_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  // Segments that are not a multiple of 128 go through a 128-padded copy in the workspace.
+  const Workspace ws = plan_workspace(M, N, KS, KO);
+  if (ws.total) {
+    if (!workspace || workspace_bytes < ws.total) return MG_ERR_WORKSPACE;
+    if (!mg::aligned(workspace, 1024)) return MG_ERR_ALIGN;
+    uint8_t* w = static_cast<uint8_t*>(workspace);
+    RepackJobs jobs{};
+    int nj = 0;
+    if (ws.ksp != KS) {
+      jobs.j[nj++] = {AS, w + ws.as, M, KS / 4 * 3, ws.ksp / 4 * 3};
+      jobs.j[nj++] = {BS, w + ws.bs, N, KS / 2, ws.ksp / 2};
+      AS = w + ws.as;
+      BS = w + ws.bs;
+    }
+    if (ws.kop != KO) {
+      jobs.j[nj++] = {AO, w + ws.ao, M, KO, ws.kop};
+      jobs.j[nj++] = {BO, w + ws.bo, N, KO / 2, ws.kop / 2};
+      AO = w + ws.ao;
+      BO = w + ws.bo;
+    }
+    repack_rows_kernel<<<dim3(di.sm_count * 2, nj), 256, 0, st>>>(jobs);
+    MG_CUDA_TRY(cudaGetLastError());
+  }
+
+  const int bn = choose_bn(M, N, di.sm_count);
+
+  GemmParams p{};
+  p.M = M;
+  p.N = N;
+  p.ldd = ldd;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = N / bn;
+  p.seg[0] = {KN, (KN + 255) / 256, (KN + 127) / 128, SFAN, SFBN};
+  p.seg[1] = {KS, (KS + 127) / 128, (KS + 127) / 128, SFAS, SFBS};
+  p.seg[2] = {KO, (KO + 127) / 128, (KO + 127) / 128, SFAO, SFBO};
+  p.C = static_cast<const __nv_bfloat16*>(C_bf16);
+  p.D = f32_out ? nullptr : static_cast<__nv_bfloat16*>(D_bf16);
+  p.Df32 = f32_out ? static_cast<float*>(D_bf16) : nullptr;
+  rc = mg::device_status_word(&p.status);
+  if (rc != MG_OK) return rc;
+  // A tensor-map load signals the packed byte count of its box on the mbarrier.
+  p.tx_a[0] = BM * 128;       p.tx_b[0] = (uint32_t)bn * 128;
+  p.tx_a[1] = BM * 96;        p.tx_b[1] = (uint32_t)bn * 64;
+  p.tx_a[2] = BM * 128;       p.tx_b[2] = (uint32_t)bn * 64;
+
+  CUtensorMap maps[6];
+  // a zero-sized segment still needs valid maps as kernel arguments: alias the first real one
+  const int first = KN ? 0 : (KS ? 1 : 2);
+  for (int seg = 0; seg < 3; ++seg) {
+    const int s = (seg == 0 ? KN : seg == 1 ? KS : KO) ? seg : first;
+    if (s == 0) {
+      if ((rc = make_map(&maps[seg * 2], CU_TENSOR_MAP_DATA_TYPE_UINT8, AN, KN / 2, M, KN / 2, 128, BM))) return rc;
+      if ((rc = make_map(&maps[seg * 2 + 1], CU_TENSOR_MAP_DATA_TYPE_UINT8, BN_, KN / 2, N, KN / 2, 128, bn))) return rc;
+    } else if (s == 1) {
+      if ((rc = make_map(&maps[seg * 2], CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, AS, ws.ksp, M, ws.ksp / 4 * 3, 128, BM))) return rc;
+      if ((rc = make_map(&maps[seg * 2 + 1], CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, BS, ws.ksp, N, ws.ksp / 2, 128, bn))) return rc;
+    } else {
+      if ((rc = make_map(&maps[seg * 2], CU_TENSOR_MAP_DATA_TYPE_UINT8, AO, ws.kop, M, ws.kop, 128, BM))) return rc;
+      if ((rc = make_map(&maps[seg * 2 + 1], CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, BO, ws.kop, N, ws.kop / 2, 128, bn))) return rc;
+    }
+  }
+  return bn == 256 ? launch_gemm<256>(p, maps, di.sm_count, st) : launch_gemm<128>(p, maps, di.sm_count, st);
+}
+
+extern "C" int mg_matmul(const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
+                         const uint8_t* AO, const uint8_t* BO, int M, int N, int KN, int KS, int KO,
+                         const void* C_bf16, void* D_bf16, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
+                         const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
+                         void* workspace, size_t workspace_bytes, void* stream) {
+  return matmul_impl(false, AN, BN_, AS, BS, AO, BO, M, N, KN, KS, KO, C_bf16, D_bf16, ldd, SFAN, SFBN, SFAS, SFBS,
+                     SFAO, SFBO, workspace, workspace_bytes, stream);
+}
+
+extern "C" int mg_matmul_f32(const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
+                             const uint8_t* AO, const uint8_t* BO, int M, int N, int KN, int KS, int KO,
+                             const void* C_bf16, float* D_f32, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
+                             const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+  return matmul_impl(true, AN, BN_, AS, BS, AO, BO, M, N, KN, KS, KO, C_bf16, D_f32, ldd, SFAN, SFBN, SFAS, SFBS,
+                     SFAO, SFBO, workspace, workspace_bytes, stream);
+}
+
+extern "C" int mg_matmul_fp4(const uint8_t* A, const uint8_t* B, int M, int N, int K, const void* C_bf16,
+                             void* D_bf16, const uint8_t* SFA, const uint8_t* SFB, void* stream) {
+  return mg_matmul(A, B, nullptr, nullptr, nullptr, nullptr, M, N, K, 0, 0, C_bf16, D_bf16, N, SFA, SFB, nullptr,
+                   nullptr, nullptr, nullptr, nullptr, 0, stream);
+}
+extern "C" int mg_matmul_fp6(const uint8_t* A, const uint8_t* B, int M, int N, int K, const void* C_bf16,
+                             void* D_bf16, const uint8_t* SFA, const uint8_t* SFB, void* stream) {
+  if (K % 128) return MG_ERR_SHAPE;
+  return mg_matmul(nullptr, nullptr, A, B, nullptr, nullptr, M, N, 0, K, 0, C_bf16, D_bf16, N, nullptr, nullptr, SFA,
+                   SFB, nullptr, nullptr, nullptr, 0, stream);
+}
+extern "C" int mg_matmul_fp8(const uint8_t* A, const uint8_t* B, int M, int N, int K, const void* C_bf16,
+                             void* D_bf16, const uint8_t* SFA, const uint8_t* SFB, void* stream) {
+  if (K % 128) return MG_ERR_SHAPE;
+  return mg_matmul(nullptr, nullptr, nullptr, nullptr, A, B, M, N, 0, 0, K, C_bf16, D_bf16, N, nullptr, nullptr,
+                   nullptr, nullptr, SFA, SFB, nullptr, 0, stream);
+}

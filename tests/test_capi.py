@@ -1,0 +1,76 @@
+"""CPU checks of the boundary: the C-ABI library loads and exports every symbol that
+include/*.h declares, and its argument checks answer without touching a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    names = set()
+    for h in ("mixedgemm_c.h", "fp4.h", "fp6.h", "fp8.h", "mxdtype.h"):
+        txt = open(os.path.join(ROOT, "include", h)).read()
+        txt = re.sub(r"/\*.*?\*/", "", txt, flags=re.S)
+        for m in re.finditer(r"^\s*(?:const\s+)?(?:int|size_t|char\s*\*|const char\s*\*)\s*\*?\s*(mg_\w+)\s*\(", txt, re.M):
+            if "static inline" not in txt[max(0, m.start() - 20):m.start() + 20]:
+                names.add(m.group(1))
+    return names
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from mixedgemm_b200 import build, _capi
+    build.build_lib()
+    return _capi.load()
+
+
+def test_exports_every_declared_symbol(lib):
+    from mixedgemm_b200 import _capi
+    declared = _declared_symbols()
+    assert {"mg_reorder_quantize_x", "mg_reorder_quantize_w", "mg_matmul", "mg_matmul_f32", "mg_matmul_fp4",
+            "mg_matmul_fp6", "mg_matmul_fp8", "mg_sf_bytes", "mg_matmul_workspace_bytes", "mg_strerror",
+            "mg_device_status", "mg_version", "mg_last_cuda_error"} <= declared
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert declared <= set(_capi.PROTOTYPES), declared - set(_capi.PROTOTYPES)
+
+
+def test_pure_host_entry_points(lib):
+    assert lib.mg_version() >= 1
+    assert lib.mg_sf_bytes(300, 448) == 3 * 4 * 512
+    assert lib.mg_sf_bytes(128, 128) == 512
+    assert lib.mg_sf_bytes(0, 128) == 0
+    assert lib.mg_strerror(0) == b"ok"
+    assert b"shape" in lib.mg_strerror(1)
+    assert lib.mg_matmul_workspace_bytes(2048, 4096, 2560, 1408, 128) == 0
+    # K=14336: 4928 and 448 are padded to 4992 and 512
+    want = 0
+    for n in (2048 * (4992 // 4 * 3), 4096 * (4992 // 2), 2048 * 512, 4096 * 256):
+        want += (n + 1023) // 1024 * 1024
+    assert lib.mg_matmul_workspace_bytes(2048, 4096, 8960, 4928, 448) == want
+
+
+def test_argument_checks_need_no_gpu(lib):
+    null = None
+    # shape errors are detected before any CUDA call
+    assert lib.mg_reorder_quantize_x(null, 4, 128, null, 64, 32, 16, *[null] * 6, null) == 1
+    assert lib.mg_reorder_quantize_x(null, 4, 128, null, 80, 32, 16, *[null] * 6, null) == 1
+    assert lib.mg_reorder_quantize_x(null, 0, 128, null, 64, 32, 32, *[null] * 6, null) == 0
+    assert lib.mg_reorder_quantize_x(null, 4, 128, null, 64, 32, 32, *[null] * 6, null) == 2
+    assert lib.mg_matmul(*[null] * 6, 128, 100, 256, 128, 128, null, null, 100, *[null] * 6, null, 0, null) == 1
+    assert lib.mg_matmul(*[null] * 6, 128, 128, 256, 128, 128, null, null, 128, *[null] * 6, null, 0, null) == 2
+
+
+def test_python_mirror_has_reference_entry_points():
+    import inspect
+    import mixedgemm_b200 as mg
+    assert mg.test_function() == "Hello from test_function!"
+    assert list(inspect.signature(mg.reorder_quantize_x).parameters)[:7] == [
+        "X", "reorder_index", "KN", "KS", "KO", "seqlen", "outfeatures"]
+    assert list(inspect.signature(mg.reorder_quantize_w).parameters)[:7] == [
+        "W", "reorder_index", "KN", "KS", "KO", "seqlen", "outfeatures"]
+    assert list(inspect.signature(mg.matmul).parameters)[:12] == [
+        "AN", "BN", "AS", "BS", "AO", "BO", "SFAN", "SFBN", "SFAS", "SFBS", "SFAO", "SFBO"]

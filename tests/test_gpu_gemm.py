@@ -1,0 +1,169 @@
+"""GPU parity of the mixed block-scaled GEMM, through the C ABI (ctypes).
+
+Oracle: float64 dequantise-then-matmul of the SAME packed operands (oracle/mx_oracle.py).
+Tolerances (stated by the benchmark definition): relative Frobenius error <= 1e-3 and
+max-abs error <= 1e-2 * RMS(output).  They are applied to the fp32 accumulator
+(mg_matmul_f32); the bf16 result must then be exactly the nearest-even rounding of that
+accumulator, and is additionally compared with the bf16-rounded float64 product.  (bf16
+rounding alone costs up to 2^-9 relative, so a raw bf16-vs-float64 max-abs bound of
+1e-2 RMS cannot hold for any implementation.)"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import mx_oracle as orc
+from tests import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+REL_FRO_TOL = 1e-3
+MAX_ABS_TOL = 1e-2  # times the output RMS
+
+
+def _quantise(M, N, K, split, seed=0, dist="normal", outlier=20.0, wstd=0.02):
+    import mixedgemm_b200 as mg
+    KN, KS, KO = split
+    X = H.make_x(M, K, seed=seed, dist=dist, outlier=outlier)
+    W = H.make_w(N, K, seed=seed + 1, std=wstd)
+    idx = H.reorder_index(X).cuda()
+    A = mg.reorder_quantize_x(X.cuda(), idx, KN, KS, KO, M, N)
+    B = mg.reorder_quantize_w(W.cuda(), idx, KN, KS, KO, M, N)
+    return A, B
+
+
+def _oracle(A, B, M, N, split, rows=None):
+    KN, KS, KO = split
+    a = [t.cpu().numpy() for t in A]
+    b = [t.cpu().numpy() for t in B]
+    if rows is not None:
+        # scale buffers are addressed by absolute row, so dequantise first, then sample
+        Y = np.zeros((len(rows), N))
+        for i, (k, fa) in enumerate(((KN, orc.FMT_E2M1), (KS, orc.FMT_E3M2), (KO, orc.FMT_E4M3))):
+            if k == 0:
+                continue
+            ad = orc.np_dequantize(a[i], a[3 + i], M, k, fa)[rows]
+            bd = orc.np_dequantize(b[i], b[3 + i], N, k, orc.FMT_E2M1)
+            Y += ad @ bd.T
+        return Y
+    return orc.gemm_f64(a, b, M, N, KN, KS, KO)
+
+
+def _check(A, B, M, N, split, rows=None, C=None):
+    import mixedgemm_b200 as mg
+    args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+    Y32 = mg.matmul(*args, out_dtype=torch.float32, C=C)
+    Y16 = mg.matmul(*args, C=C)
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    Yo = _oracle(A, B, M, N, split, rows)
+    if C is not None:
+        Yo = Yo + (C.float().cpu().numpy().astype(np.float64) if rows is None else
+                   C.float().cpu().numpy().astype(np.float64)[rows])
+    y32 = Y32.cpu().numpy().astype(np.float64)
+    y16 = Y16.float().cpu().numpy()
+    if rows is not None:
+        y32s, y16s = y32[rows], y16[rows]
+    else:
+        y32s, y16s = y32, y16
+    rms = np.sqrt(np.mean(Yo ** 2))
+    fro = np.linalg.norm(y32s - Yo) / np.linalg.norm(Yo)
+    mx = np.abs(y32s - Yo).max() / rms
+    assert fro <= REL_FRO_TOL, "fp32 accumulator: rel-Frobenius %.3e" % fro
+    assert mx <= MAX_ABS_TOL, "fp32 accumulator: max-abs %.3e RMS" % mx
+    # the bf16 output is the accumulator rounded once, to nearest even
+    assert np.array_equal(y16, orc.bf16_round(Y32.cpu().numpy())), "bf16 output is not RNE(fp32 accumulator)"
+    # against the bf16-rounded float64 product: Frobenius bound, and max-abs up to one-ulp flips
+    yo16 = orc.bf16_round(Yo).astype(np.float64)
+    fro16 = np.linalg.norm(y16s - yo16) / np.linalg.norm(yo16)
+    assert fro16 <= REL_FRO_TOL, "bf16 vs bf16(fp64): rel-Frobenius %.3e" % fro16
+    diff = np.abs(y16s - yo16)
+    ulp = np.abs(yo16) * 2.0 ** -7 + 1e-30
+    assert np.all((diff <= MAX_ABS_TOL * rms) | (diff <= ulp)), "bf16 vs bf16(fp64): more than a one-ulp flip"
+    return fro, mx
+
+
+@pytest.mark.parametrize("M,N,split", [
+    (128, 128, (256, 0, 0)), (128, 128, (0, 128, 0)), (128, 128, (0, 0, 128)),
+    (128, 256, (256, 128, 128)), (16, 128, (128, 128, 128)), (114, 384, (2560, 896, 128)),
+    (300, 512, (640, 384, 128)), (1, 128, (256, 256, 128)), (257, 1024, (2560, 1408, 128))])
+def test_small_shapes(M, N, split):
+    K = sum(split)
+    A, B = _quantise(M, N, K, split, seed=M + N)
+    _check(A, B, M, N, split)
+
+
+@pytest.mark.parametrize("bn", ["128", "256"])
+def test_both_tile_widths(bn, monkeypatch):
+    monkeypatch.setenv("MG_GEMM_BN", bn)
+    M, N, split = 384, 1024, (1280, 768, 128)
+    A, B = _quantise(M, N, sum(split), split, seed=9)
+    _check(A, B, M, N, split)
+
+
+def test_segments_with_64_tails():
+    """K = 14336 splits into 8960 / 4928 / 448: the last two are only multiples of 64 and go
+    through the padded copy in the workspace."""
+    M, N, split = 200, 256, (8960, 4928, 448)
+    A, B = _quantise(M, N, sum(split), split, seed=4)
+    _check(A, B, M, N, split)
+    M, N, split = 130, 128, (128, 192, 64)
+    A, B = _quantise(M, N, sum(split), split, seed=5)
+    _check(A, B, M, N, split)
+
+
+def test_accumulate_into_c():
+    M, N, split = 256, 256, (512, 256, 128)
+    A, B = _quantise(M, N, sum(split), split, seed=6)
+    g = torch.Generator().manual_seed(1)
+    C = torch.randn(M, N, generator=g).to(torch.bfloat16).cuda()
+    _check(A, B, M, N, split, C=C)
+
+
+def test_known_answer_integers():
+    """main.py:24-27 style case: small-integer X and W, exactly representable after quantisation
+    with power-of-two scales, so the product is exact."""
+    import mixedgemm_b200 as mg
+    M, N, split = 128, 128, (256, 128, 128)
+    K = sum(split)
+    g = torch.Generator().manual_seed(2)
+    X = torch.randint(-3, 4, (M, K), generator=g).to(torch.bfloat16)
+    X[:, 0::32] = 3  # every group holds its maximum so that the scale is 2^-1 and values double exactly
+    W = torch.randint(-3, 4, (N, K), generator=g).to(torch.bfloat16)
+    W[:, 0::32] = 3
+    idx = torch.arange(K, dtype=torch.int16).cuda()
+    A = mg.reorder_quantize_x(X.cuda(), idx, *split, M, N)
+    B = mg.reorder_quantize_w(W.cuda(), idx, *split, M, N)
+    Y = mg.matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5], out_dtype=torch.float32)
+    want = X.double() @ W.double().T
+    assert torch.equal(Y.cpu().double(), want)
+
+
+@pytest.mark.parametrize("M,N,K,dist,outlier,wstd", [
+    (2048, 4096, 4096, "normal", 20.0, 0.02), (2048, 1024, 4096, "normal", 20.0, 0.02),
+    (2048, 14336, 4096, "normal", 20.0, 0.02), (2048, 4096, 14336, "normal", 20.0, 0.02),
+    (4096, 1024, 8192, "student3", 30.0, 0.015), (64, 4096, 4096, "normal", 20.0, 0.02),
+    (8, 14336, 4096, "normal", 20.0, 0.02)])
+def test_benchmark_shapes_row_sample(M, N, K, dist, outlier, wstd):
+    """Benchmark-size problems: a seeded sample of output rows against the float64 oracle, plus
+    linearity in the scales over the whole output (doubling every A scale doubles Y exactly)."""
+    import mixedgemm_b200 as mg
+    split = H.split_k(K)
+    A, B = _quantise(M, N, K, split, seed=21, dist=dist, outlier=outlier, wstd=wstd)
+    rng = np.random.default_rng(0)
+    rows = np.unique(np.concatenate([[0, M - 1], rng.integers(0, M, 46)]))
+    _check(A, B, M, N, split, rows=rows)
+    args = lambda A_: (A_[0], B[0], A_[1], B[1], A_[2], B[2], A_[3], B[3], A_[4], B[4], A_[5], B[5])
+    Y1 = mg.matmul(*args(A), out_dtype=torch.float32)
+    A2 = list(A[:3]) + [t + 1 for t in A[3:]]
+    Y2 = mg.matmul(*args(A2), out_dtype=torch.float32)
+    assert torch.equal(Y2, Y1 * 2)
+
+
+def test_rejects_bad_arguments():
+    import mixedgemm_b200 as mg
+    M, N, split = 128, 128, (256, 128, 128)
+    A, B = _quantise(M, N, sum(split), split)
+    with pytest.raises(RuntimeError):  # N not a multiple of 128
+        mg.matmul(A[0], B[0][:100], A[1], B[1][:100], A[2], B[2][:100], A[3], B[3], A[4], B[4], A[5], B[5])
+    with pytest.raises(RuntimeError):
+        mg.matmul(A[0].cpu(), B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
