@@ -1,0 +1,487 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: activation reorder-and-quantise + mixed MXFP4/6/8 GEMM.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                  [--workload NAME] [--exchange bcast|replicated] [--no-graph]
+
+One "step" is one pass over a projection set of a Llama-shaped layer stack: every distinct
+activation is reorder-quantised once and multiplied with each weight that consumes it
+(q/k/v share one activation, gate/up another).  Weights are quantised once, outside the
+timed region, as in deployment.
+
+  N = 1 (default)   workload llama3-8b-m2048   (BASELINE configs[1])
+  N > 1             workload llama3-70b-m4096  (BASELINE configs[3]): weights sharded along N
+                    over the ranks, quantised activations broadcast from rank 0 with NCCL
+                    (--exchange replicated: every rank quantises locally instead)
+
+Prints ONE JSON line (rank 0).  `value` is the whole-job GEMM throughput with inputs resident
+in HBM; `e2e` is the same metric with the activations starting in pinned host memory and the
+outputs ending there (copies inside the timed region).  `--impl reference` times the CPU
+restatement of the same path on the host cores (the reference has no CPU code and its GEMMs
+do not run on sm_100).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: M, [(activation K, [(layer, N), ...]), ...], X distribution, outlier scale, W std
+    "llama3-8b-m2048": dict(M=2048, dist="normal", outlier=20.0, wstd=0.02, groups=[
+        (4096, [("q", 4096), ("k", 1024), ("v", 1024)]),
+        (4096, [("o", 4096)]),
+        (4096, [("gate", 14336), ("up", 14336)]),
+        (14336, [("down", 4096)])]),
+    "llama3-70b-m4096": dict(M=4096, dist="student3", outlier=30.0, wstd=0.015, groups=[
+        (8192, [("q", 8192), ("k", 1024), ("v", 1024)]),
+        (8192, [("o", 8192)]),
+        (8192, [("gate", 28672), ("up", 28672)]),
+        (28672, [("down", 8192)])]),
+    # BASELINE configs[0]: the CPU-runnable single layer
+    "single-layer-m16": dict(M=16, dist="normal", outlier=20.0, wstd=0.02, groups=[(4096, [("proj", 4096)])]),
+}
+
+
+def split_k(K):
+    KO = K // 32
+    KN = K * 5 // 8
+    return KN, K - KN - KO, KO
+
+
+def reorder_bytes(M, K):
+    KN, KS, KO = split_k(K)
+    return M * K * 2 + M * (KN // 2 + KS // 4 * 3 + KO + K // 32)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=d["hbm_gbs"], bf16=d["bf16_tflops"], bf16_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                    source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def blended_peak(bf16_tflops, K):
+    """Tensor peak of a K split 62.5/34.375/3.125 %: FP4 runs at 4x and FP6/FP8 at 2x the bf16 rate."""
+    KN, KS, KO = split_k(K)
+    return K / (KN / (4 * bf16_tflops) + (KS + KO) / (2 * bf16_tflops))
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append((time.time(), ln.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = [l for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for (_, l) in self.lines]
+        for ln in rows:
+            f = [x.strip() for x in ln.split(",")]
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+                for n, v in zip(names, f[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                pass
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- CPU arm
+def cpu_arm(wl_name, rows, steps, warmup):
+    """The CPU restatement of the path (oracle): reorder-quantise with the C/OpenMP oracle, then
+    dequantise-then-matmul in fp32 on all host cores, bf16 output.  `rows` activation rows per
+    step stand for the workload's M (rows are independent; throughput is reported per flop)."""
+    import numpy as np
+    from oracle import mx_oracle as orc
+    wl = WORKLOADS[wl_name]
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    g = torch.Generator().manual_seed(0)
+    groups = []
+    flops = 0
+    qbytes = 0
+    for K, layers in wl["groups"]:
+        KN, KS, KO = split_k(K)
+        X = torch.randn(rows, K, generator=g)
+        ch = torch.randperm(K, generator=g)[:K // 32]
+        X[:, ch] *= wl["outlier"]
+        Xb = X.to(torch.bfloat16)
+        idx = torch.sort(Xb.float().abs().amax(0), stable=True).indices.to(torch.int16).numpy()
+        xbits = Xb.view(torch.int16).numpy().view(np.uint16)
+        Ws = []
+        for name, N in layers:
+            Nc = min(N, 4096)  # bounded sample of output columns; flops counted for what is computed
+            W = (torch.randn(Nc, K, generator=g) * wl["wstd"]).to(torch.bfloat16)
+            wq = orc.c_reorder_quantize(W.view(torch.int16).numpy().view(np.uint16), idx, KN, KS, KO, weights=True)
+            Wd = torch.from_numpy(np.concatenate(
+                [orc.c_dequantize(wq[i], wq[3 + i], Nc, k, orc.FMT_E2M1) for i, k in enumerate((KN, KS, KO))], 1))
+            Ws.append(Wd)
+            flops += 2 * rows * Nc * K
+        qbytes += reorder_bytes(rows, K)
+        groups.append((xbits, idx, (KN, KS, KO), Ws))
+
+    def step():
+        tq = 0.0
+        for xbits, idx, (KN, KS, KO), Ws in groups:
+            t0 = time.perf_counter()
+            a = orc.c_reorder_quantize(xbits, idx, KN, KS, KO)
+            tq += time.perf_counter() - t0
+            Ad = torch.from_numpy(np.concatenate(
+                [orc.c_dequantize(a[i], a[3 + i], rows, k, f) for i, (k, f) in
+                 enumerate(((KN, orc.FMT_E2M1), (KS, orc.FMT_E3M2), (KO, orc.FMT_E4M3)))], 1))
+            for Wd in Ws:
+                (Ad @ Wd.T).to(torch.bfloat16)
+        return tq
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    tq = 0.0
+    for _ in range(steps):
+        tq += step()
+    dt = time.perf_counter() - t0
+    return dict(tflops=flops * steps / dt / 1e12, reorder_gbs=qbytes * steps / tq / 1e9, cores=cores,
+                ms_per_step=dt / steps * 1e3,
+                sample="%d of %d activation rows per step, output columns capped at 4096 per layer, %d steps" % (
+                    rows, wl["M"], steps))
+
+
+# ----------------------------------------------------------------------------- GPU arm
+class Job:
+    """Device-resident state of one rank: activations, reorder indices, quantised weight shards,
+    output buffers."""
+
+    def __init__(self, wl_name, rank, world, device, exchange):
+        import mixedgemm_b200 as mg
+        self.mg = mg
+        wl = WORKLOADS[wl_name]
+        self.M = M = wl["M"]
+        self.rank, self.world, self.exchange = rank, world, exchange
+        g = torch.Generator(device=device).manual_seed(1234)  # same activations on every rank
+        self.groups = []
+        self.flops_local = 0
+        self.flops_total = 0
+        self.reorder_bytes = 0
+        self.gemm_shapes = []
+        self.n_kernels = 0
+        for gi, (K, layers) in enumerate(wl["groups"]):
+            KN, KS, KO = split_k(K)
+            X = torch.randn(M, K, generator=g, device=device)
+            if wl["dist"] == "student3":
+                chi = torch.zeros(M, K, device=device)
+                for _ in range(3):
+                    chi += torch.randn(M, K, generator=g, device=device).pow_(2)
+                X = X / (chi / 3).sqrt_() / (3 ** 0.5)
+                del chi
+            ch = torch.randperm(K, generator=g, device=device)[:K // 32]
+            X[:, ch] *= wl["outlier"]
+            Xb = X.to(torch.bfloat16)
+            del X
+            idx = torch.sort(Xb.float().abs().amax(0), stable=True).indices.to(torch.int16)
+            A = mg.alloc_quantized_x(M, KN, KS, KO, device)
+            Ls = []
+            for li, (name, N) in enumerate(layers):
+                assert N % (128 * world) == 0, "every shard must be a multiple of 128 columns"
+                Nl = N // world
+                gw = torch.Generator(device=device).manual_seed(977 * gi + 31 * li + 7)
+                W = (torch.randn(N, K, generator=gw, device=device) * wl["wstd"]).to(torch.bfloat16)
+                Wl = W[rank * Nl:(rank + 1) * Nl].contiguous()
+                del W
+                B = mg.reorder_quantize_w(Wl, idx, KN, KS, KO, M, Nl)
+                del Wl
+                Y = torch.empty((M, Nl), dtype=torch.bfloat16, device=device)
+                Ls.append((name, Nl, B, Y))
+                self.flops_local += 2 * M * Nl * K
+                self.flops_total += 2 * M * N * K
+                self.gemm_shapes.append((M, Nl, K))
+                self.n_kernels += 1 + (1 if (KS % 128 or KO % 128) else 0)
+            self.n_kernels += 1
+            self.reorder_bytes += reorder_bytes(M, K)
+            self.groups.append(dict(K=K, split=(KN, KS, KO), X=Xb, idx=idx, A=A, layers=Ls))
+        torch.cuda.synchronize()
+
+    def quantize(self, gr):
+        KN, KS, KO = gr["split"]
+        self.mg.reorder_quantize_x(gr["X"], gr["idx"], KN, KS, KO, self.M, 0, out=gr["A"])
+
+    def exchange_a(self, gr):
+        import torch.distributed as dist
+        for t in gr["A"]:
+            if t.numel():
+                dist.broadcast(t, src=0)
+
+    def gemms(self, gr):
+        A = gr["A"]
+        for name, Nl, B, Y in gr["layers"]:
+            self.mg.matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5], out=Y)
+
+    def step(self):
+        for gr in self.groups:
+            if self.world == 1 or self.exchange == "replicated":
+                self.quantize(gr)
+            else:
+                if self.rank == 0:
+                    self.quantize(gr)
+                self.exchange_a(gr)
+            self.gemms(gr)
+
+
+def timed(fn, steps, sync):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    sync()
+    return e0.elapsed_time(e1) / steps  # ms per step
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=list(WORKLOADS))
+    ap.add_argument("--exchange", default="bcast", choices=["bcast", "replicated"])
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--cpu-rows", type=int, default=128)
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    wl_name = a.workload or ("llama3-8b-m2048" if a.gpus == 1 else "llama3-70b-m4096")
+    metric, unit = "mixed_mx_gemm_tflops", "TFLOP/s"
+
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        steps = min(a.steps, 5)
+        r = cpu_arm(wl_name, a.cpu_rows, steps, min(a.warmup, 1))
+        cb = {"value": r["tflops"], "unit": unit, "cores": r["cores"], "kind": "port", "sample": r["sample"],
+              "reorder_quant_gbs": r["reorder_gbs"]}
+        print(json.dumps({
+            "impl": "reference", "metric": metric, "value": r["tflops"], "unit": unit, "n_gpus": a.gpus,
+            "steps": steps, "warmup": min(a.warmup, 1), "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong" if a.gpus > 1 else "weak", "vs_baseline": None, "dtype": "mxfp4/mxfp6/mxfp8 x mxfp4, f32 accumulate",
+            "data": "synthetic", "config": {"workload": wl_name, "note": "CPU restatement of the path on host cores; "
+                                            "the reference ships no CPU code and its sm_120 GEMMs do not run on sm_100"},
+            "cpu_baseline": cb,
+            "e2e": {"value": r["tflops"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback of the product path)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    def sync():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    job = Job(wl_name, rank, world, device, a.exchange)
+    pk = peaks()
+
+    # ---- whole-step timing, inputs resident in HBM
+    use_graph = not a.no_graph
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(a.warmup):
+            job.step()
+        torch.cuda.synchronize()
+        run = job.step
+        if use_graph:
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    job.step()
+                graph.replay()
+                torch.cuda.synchronize()
+                run = graph.replay
+            except Exception as e:  # capture of NCCL or of a driver call may be refused
+                use_graph = False
+                sys.stderr.write("CUDA graph capture failed (%r); timing eager launches\n" % (e,))
+                torch.cuda.synchronize()
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",")
+        smi_index = vis[local_rank] if local_rank < len(vis) and vis[local_rank].strip().isdigit() else local_rank
+        sampler = ClockSampler(smi_index)
+        if rank == 0:
+            sampler.start()
+            time.sleep(0.25)
+        t0 = time.time()
+        ms = timed(run, a.steps, sync)
+        t1 = time.time()
+        # nvidia-smi samples every 100 ms: when the K timed steps are shorter than that, the clocks are
+        # read over an identical window of back-to-back steps that follows them immediately
+        clock_window = "the timed steps"
+        if t1 - t0 < 0.6:
+            n_extra = int(0.6 / max(ms / 1e3, 1e-6)) + 1
+            t0 = time.time()
+            timed(run, n_extra, sync)
+            t1 = time.time()
+            clock_window = "%d further identical steps right after the timed ones" % n_extra
+        clocks = sampler.stop(t0, t1) if rank == 0 else None
+        if clocks is not None:
+            clocks["window"] = clock_window
+
+        # ---- per-kernel durations (instrumented pass, eager launches on the same stream)
+        ev = lambda: torch.cuda.Event(enable_timing=True)
+        q_ms, g_ms, q_each, g_each = 0.0, 0.0, [], []
+        if world == 1:
+            reps = max(3, min(a.steps, 10))
+            for gr in job.groups:
+                es = [ev() for _ in range(reps + 1)]
+                job.quantize(gr)
+                torch.cuda.synchronize()
+                es[0].record()
+                for i in range(reps):
+                    job.quantize(gr)
+                    es[i + 1].record()
+                torch.cuda.synchronize()
+                tq = es[0].elapsed_time(es[reps]) / reps
+                q_ms += tq
+                q_each.append((gr["K"], tq))
+                A = gr["A"]
+                for name, Nl, B, Y in gr["layers"]:
+                    f = lambda: job.mg.matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5], out=Y)
+                    f()
+                    torch.cuda.synchronize()
+                    es[0].record()
+                    for i in range(reps):
+                        f()
+                    es[1].record()
+                    torch.cuda.synchronize()
+                    tg = es[0].elapsed_time(es[1]) / reps
+                    g_ms += tg
+                    g_each.append((name, job.M, Nl, gr["K"], tg))
+
+        # ---- end to end: activations from pinned host memory, results back to pinned host memory
+        hX = [gr["X"].cpu().pin_memory() for gr in job.groups]
+        hY = [[torch.empty(Y.shape, dtype=Y.dtype).pin_memory() for (_, _, _, Y) in gr["layers"]] for gr in job.groups]
+        h2d = sum(t.numel() * 2 for t in hX)
+        d2h = sum(t.numel() * 2 for ys in hY for t in ys)
+
+        def e2e_step():
+            for gr, hx, hys in zip(job.groups, hX, hY):
+                gr["X"].copy_(hx, non_blocking=True)
+                if world == 1 or a.exchange == "replicated":
+                    job.quantize(gr)
+                else:
+                    if rank == 0:
+                        job.quantize(gr)
+                    job.exchange_a(gr)
+                job.gemms(gr)
+                for (_, _, _, Y), hy in zip(gr["layers"], hys):
+                    hy.copy_(Y, non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        e2e_ms = timed(e2e_step, max(3, min(a.steps, 10)), sync)
+
+    # max over ranks
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms, e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+    status = job.mg.device_status()
+    if status != 0:
+        raise SystemExit("a kernel reported device status %d" % status)
+    if rank != 0:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+        return
+
+    value = job.flops_total / (ms * 1e-3) / 1e12
+    out = {
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+        "vs_baseline": None, "dtype": "mxfp4/mxfp6/mxfp8 x mxfp4, f32 accumulate, bf16 out", "data": "synthetic",
+        "config": {"workload": wl_name, "M": job.M,
+                   "layers": [[gr["K"], [[n, N * world] for (n, N, _, _) in gr["layers"]]] for gr in job.groups],
+                   "k_split": "62.5% fp4 / 34.375% fp6 / 3.125% fp8", "parallelism": "n-shard x%d" % world,
+                   "exchange": a.exchange if world > 1 else "none", "cuda_graph": use_graph,
+                   "l2": "inputs larger than L2: one step touches ~%d MB of weights, activations and outputs" % (
+                       (sum(t.numel() * t.element_size() for gr in job.groups for (_, _, B, Y) in gr["layers"]
+                            for t in list(B) + [Y]) + h2d) >> 20)},
+        "clocks": clocks,
+        "gpu_launches": job.n_kernels * a.steps,
+        "e2e": {"value": job.flops_total / (e2e_ms * 1e-3) / 1e12, "unit": unit, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+    }
+    if world == 1:
+        Kdom = max(job.groups, key=lambda gr: gr["K"])["K"]
+        gemm_flops = job.flops_local
+        peak_t = blended_peak(pk["bf16_sustained"], 4096)  # same split for every K
+        out["roofline"] = {
+            "kernel": "mixed_gemm_kernel", "bound": "tensor", "achieved": gemm_flops / (g_ms * 1e-3) / 1e12,
+            "peak": peak_t, "unit": "TFLOP/s", "frac": gemm_flops / (g_ms * 1e-3) / 1e12 / peak_t, "traffic": None,
+            "peak_note": "K-blended tensor peak: fp4 segment at 4x and fp6/fp8 at 2x the %s sustained bf16 rate (%.1f TF/s)" % (
+                pk["source"], pk["bf16_sustained"]),
+            "launches": [{"layer": n, "M": M, "N": N, "K": K, "us": t * 1e3, "tflops": 2 * M * N * K / (t * 1e-3) / 1e12}
+                         for (n, M, N, K, t) in g_each]}
+        out["roofline_reorder"] = {
+            "kernel": "reorder_quantize_kernel", "bound": "hbm", "achieved": job.reorder_bytes / (q_ms * 1e-3) / 1e9,
+            "peak": pk["hbm"], "unit": "GB/s", "frac": job.reorder_bytes / (q_ms * 1e-3) / 1e9 / pk["hbm"], "traffic": None,
+            "peak_note": "%s copy bandwidth" % pk["source"],
+            "launches": [{"M": job.M, "K": K, "us": t * 1e3, "gbs": reorder_bytes(job.M, K) / (t * 1e-3) / 1e9}
+                         for (K, t) in q_each]}
+        out["reorder_quant_gbs"] = out["roofline_reorder"]["achieved"]
+        r = cpu_arm(wl_name, a.cpu_rows, 2, 1)
+        out["cpu_baseline"] = {"value": r["tflops"], "unit": unit, "cores": r["cores"], "kind": "port",
+                               "sample": r["sample"], "reorder_quant_gbs": r["reorder_gbs"]}
+    print(json.dumps(out))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

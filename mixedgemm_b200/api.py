@@ -37,18 +37,31 @@ def _check_in(X, reorder_index, KN, KS, KO, what):
         raise RuntimeError("%s: K = %d does not match KN+KS+KO or the index length" % (what, X.size(1)))
 
 
-def reorder_quantize_x(X, reorder_index, KN, KS, KO, seqlen=None, outfeatures=None):
+def alloc_quantized_x(M, KN, KS, KO, device):
+    """Output buffers of reorder_quantize_x with the reference's shapes (bindings.cpp:88-93)."""
+    lib = _capi.load()
+    u8 = dict(dtype=torch.uint8, device=device)
+    return (torch.empty((M, KN // 2), **u8), torch.empty((M, KS // 4 * 3), **u8), torch.empty((M, KO), **u8)) + tuple(
+        torch.empty(max(lib.mg_sf_bytes(M, k), (M // 128 + 1) * 128 * k // 32), **u8) for k in (KN, KS, KO))
+
+
+def alloc_quantized_w(N, KN, KS, KO, device):
+    """Output buffers of reorder_quantize_w (bindings.cpp:207-212)."""
+    lib = _capi.load()
+    u8 = dict(dtype=torch.uint8, device=device)
+    return (torch.empty((N, KN // 2), **u8), torch.empty((N, KS // 2), **u8), torch.empty((N, KO // 2), **u8)) + tuple(
+        torch.empty(max(lib.mg_sf_bytes(N, k), N * k // 32), **u8) for k in (KN, KS, KO))
+
+
+def reorder_quantize_x(X, reorder_index, KN, KS, KO, seqlen=None, outfeatures=None, out=None):
     """bindings.cpp:69-186.  Returns (XN[M,KN/2], XS[M,3KS/4], XO[M,KO], SFXN, SFXS, SFXO), all uint8.
-    `seqlen` / `outfeatures` are accepted and ignored, as in the reference."""
+    `seqlen` / `outfeatures` are accepted and ignored, as in the reference.  `out` may pass the
+    six buffers of alloc_quantized_x() to write into."""
     _check_in(X, reorder_index, KN, KS, KO, "reorder_quantize_x")
     lib = _capi.load()
     M = X.size(0)
     dev = X.device
-    u8 = dict(dtype=torch.uint8, device=dev)
-    XN = torch.empty((M, KN // 2), **u8)
-    XS = torch.empty((M, KS // 4 * 3), **u8)
-    XO = torch.empty((M, KO), **u8)
-    sfs = [torch.empty(max(lib.mg_sf_bytes(M, k), (M // 128 + 1) * 128 * k // 32), **u8) for k in (KN, KS, KO)]
+    XN, XS, XO, *sfs = out if out is not None else alloc_quantized_x(M, KN, KS, KO, dev)
     with torch.cuda.device(dev):
         st = lib.mg_reorder_quantize_x(_ptr(X), M, X.size(1), _ptr(reorder_index), KN, KS, KO, _ptr(XN), _ptr(XS),
                                        _ptr(XO), _ptr(sfs[0]), _ptr(sfs[1]), _ptr(sfs[2]), _stream())
@@ -56,17 +69,13 @@ def reorder_quantize_x(X, reorder_index, KN, KS, KO, seqlen=None, outfeatures=No
     return XN, XS, XO, sfs[0], sfs[1], sfs[2]
 
 
-def reorder_quantize_w(W, reorder_index, KN, KS, KO, seqlen=None, outfeatures=None):
+def reorder_quantize_w(W, reorder_index, KN, KS, KO, seqlen=None, outfeatures=None, out=None):
     """bindings.cpp:188-305.  Returns (WN[N,KN/2], WS[N,KS/2], WO[N,KO/2], SFWN, SFWS, SFWO), all uint8."""
     _check_in(W, reorder_index, KN, KS, KO, "reorder_quantize_w")
     lib = _capi.load()
     N = W.size(0)
     dev = W.device
-    u8 = dict(dtype=torch.uint8, device=dev)
-    WN = torch.empty((N, KN // 2), **u8)
-    WS = torch.empty((N, KS // 2), **u8)
-    WO = torch.empty((N, KO // 2), **u8)
-    sfs = [torch.empty(max(lib.mg_sf_bytes(N, k), N * k // 32), **u8) for k in (KN, KS, KO)]
+    WN, WS, WO, *sfs = out if out is not None else alloc_quantized_w(N, KN, KS, KO, dev)
     with torch.cuda.device(dev):
         st = lib.mg_reorder_quantize_w(_ptr(W), N, W.size(1), _ptr(reorder_index), KN, KS, KO, _ptr(WN), _ptr(WS),
                                        _ptr(WO), _ptr(sfs[0]), _ptr(sfs[1]), _ptr(sfs[2]), _stream())

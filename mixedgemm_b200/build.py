@@ -79,7 +79,7 @@ def build_ext(force=False, verbose=False):
     cmd += ["-I" + p for p in cpp_extension.include_paths()]
     cmd += [src, "-o", out, "-L" + PKG, "-lmixedgemm_b200", "-L" + tlib, "-ltorch", "-ltorch_cpu", "-lc10",
             "-ltorch_python", "-lc10_cuda", "-ltorch_cuda", "-L/usr/local/cuda/lib64", "-lcudart",
-            "-Wl,-rpath," + PKG, "-Wl,-rpath," + tlib]
+            "-Wl,-rpath,$ORIGIN/..", "-Wl,-rpath," + tlib]
     if verbose:
         print(" ".join(cmd))
     subprocess.check_call(cmd)
