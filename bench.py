@@ -274,6 +274,65 @@ def timed(fn, steps, sync):
     return e0.elapsed_time(e1) / steps  # ms per step
 
 
+def single_kernel(a):
+    """One kernel, one shape, rotating operand sets larger than L2: the command the ncu summaries
+    under profiles/ are made with."""
+    import mixedgemm_b200 as mg
+    M, N, K = [int(v) for v in a.shape.split(",")]
+    KN, KS, KO = split_k(K)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(5)
+    pk = peaks()
+    X = torch.randn(M, K, generator=g, device=dev)
+    X[:, torch.randperm(K, generator=g, device=dev)[:K // 32]] *= 20
+    X = X.to(torch.bfloat16)
+    idx = torch.sort(X.float().abs().amax(0), stable=True).indices.to(torch.int16)
+    L2 = 130 << 20
+    if a.kernel == "reorder":
+        per = reorder_bytes(M, K)
+        nb = a.buffers or max(2, L2 // (M * K * 2) + 1)
+        Xs = [X.clone() for _ in range(nb)]
+        outs = [mg.alloc_quantized_x(M, KN, KS, KO, dev) for _ in range(nb)]
+        fns = [lambda i=i: mg.reorder_quantize_x(Xs[i], idx, KN, KS, KO, M, 0, out=outs[i]) for i in range(nb)]
+        work, unit, peak, bound = per / 1e9, "GB/s", pk["hbm"], "hbm"
+    else:
+        W = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        wbytes = N * K // 2 + N * K // 32
+        nb = a.buffers or max(2, L2 // wbytes + 1)
+        A = mg.reorder_quantize_x(X, idx, KN, KS, KO, M, N)
+        Bs = [mg.reorder_quantize_w(W, idx, KN, KS, KO, M, N) for _ in range(nb)]
+        Ys = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _ in range(nb)]
+        fns = [lambda i=i: mg.matmul(A[0], Bs[i][0], A[1], Bs[i][1], A[2], Bs[i][2], A[3], Bs[i][3], A[4], Bs[i][4],
+                                     A[5], Bs[i][5], out=Ys[i]) for i in range(nb)]
+        work, unit, bound = 2.0 * M * N * K / 1e12, "TFLOP/s", "tensor"
+        peak = blended_peak(pk["bf16"], K)
+    for i in range(max(a.warmup, 1)):
+        fns[i % nb]()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        fns[0]()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=st):
+            for i in range(a.steps):
+                fns[i % nb]()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / a.steps
+    assert mg.device_status() == 0
+    print(json.dumps({"kernel": a.kernel, "M": M, "N": N, "K": K, "launches": a.steps, "operand_sets": nb,
+                      "us_per_launch": us, "achieved": work / (us * 1e-6), "unit": unit, "bound": bound,
+                      "peak": peak, "frac": work / (us * 1e-6) / peak,
+                      "peak_note": "%s burst figures (kernel timed alone)" % pk["source"]}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -284,6 +343,11 @@ def main():
     ap.add_argument("--exchange", default="bcast", choices=["bcast", "replicated"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--cpu-rows", type=int, default=128)
+    ap.add_argument("--kernel", default=None, choices=["gemm", "reorder"],
+                    help="run only this kernel on --shape (for profiling); prints a short JSON line")
+    ap.add_argument("--shape", default="2048,4096,4096", help="M,N,K for --kernel")
+    ap.add_argument("--buffers", type=int, default=0,
+                    help="--kernel: rotate this many operand sets (0 = enough to exceed L2)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
 
@@ -292,6 +356,9 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     wl_name = a.workload or ("llama3-8b-m2048" if a.gpus == 1 else "llama3-70b-m4096")
     metric, unit = "mixed_mx_gemm_tflops", "TFLOP/s"
+
+    if a.kernel:
+        return single_kernel(a)
 
     if a.impl == "reference":
         if rank != 0:
@@ -370,36 +437,40 @@ def main():
         if clocks is not None:
             clocks["window"] = clock_window
 
-        # ---- per-kernel durations (instrumented pass, eager launches on the same stream)
+        # ---- per-kernel durations: an instrumented pass of whole steps in launch order, so every kernel
+        # sees the cache state it has inside a step.  A spin kernel keeps the GPU busy while the CPU
+        # enqueues, so the event pairs bracket pure GPU execution rather than Python launch overhead.
         ev = lambda: torch.cuda.Event(enable_timing=True)
         q_ms, g_ms, q_each, g_each = 0.0, 0.0, [], []
         if world == 1:
             reps = max(3, min(a.steps, 10))
-            for gr in job.groups:
-                es = [ev() for _ in range(reps + 1)]
-                job.quantize(gr)
-                torch.cuda.synchronize()
-                es[0].record()
-                for i in range(reps):
+            marks = []
+            torch.cuda.synchronize()
+            torch.cuda._sleep(int(1.0e7) * reps)
+            for _ in range(reps):
+                for gi, gr in enumerate(job.groups):
+                    e0, e1 = ev(), ev()
+                    e0.record()
                     job.quantize(gr)
-                    es[i + 1].record()
-                torch.cuda.synchronize()
-                tq = es[0].elapsed_time(es[reps]) / reps
-                q_ms += tq
-                q_each.append((gr["K"], tq))
-                A = gr["A"]
-                for name, Nl, B, Y in gr["layers"]:
-                    f = lambda: job.mg.matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5], out=Y)
-                    f()
-                    torch.cuda.synchronize()
-                    es[0].record()
-                    for i in range(reps):
-                        f()
-                    es[1].record()
-                    torch.cuda.synchronize()
-                    tg = es[0].elapsed_time(es[1]) / reps
-                    g_ms += tg
-                    g_each.append((name, job.M, Nl, gr["K"], tg))
+                    e1.record()
+                    marks.append((("q", gi), e0, e1))
+                    A = gr["A"]
+                    for li, (name, Nl, B, Y) in enumerate(gr["layers"]):
+                        e0, e1 = ev(), ev()
+                        e0.record()
+                        job.mg.matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5], out=Y)
+                        e1.record()
+                        marks.append((("g", gi, li), e0, e1))
+            torch.cuda.synchronize()
+            acc = {}
+            for key, e0, e1 in marks:
+                acc[key] = acc.get(key, 0.0) + e0.elapsed_time(e1) / reps
+            for gi, gr in enumerate(job.groups):
+                q_each.append((gr["K"], acc[("q", gi)]))
+                q_ms += acc[("q", gi)]
+                for li, (name, Nl, B, Y) in enumerate(gr["layers"]):
+                    g_each.append((name, job.M, Nl, gr["K"], acc[("g", gi, li)]))
+                    g_ms += acc[("g", gi, li)]
 
         # ---- end to end: activations from pinned host memory, results back to pinned host memory
         hX = [gr["X"].cpu().pin_memory() for gr in job.groups]
