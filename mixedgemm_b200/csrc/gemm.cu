@@ -49,21 +49,27 @@ struct GemmParams {
   float* Df32;  // when set, the fp32 accumulator is stored here instead of D
   int* status;
   uint32_t tx_a[3], tx_b[3];  // bytes one A / B tile load of the segment signals
+  int dbg;  // timing experiments only (MG_GEMM_DEBUG): 1 = no MMAs, 2 = no loads, 4 = no stores
 };
 
-// Bounded mbarrier wait.  Returns false when the CTA is stopping.
-__device__ __forceinline__ bool wait_parity(uint32_t bar, uint32_t parity, volatile int* stop, int* status,
+// Bounded mbarrier wait.  Control flow stays warp-uniform: when the limit expires the lane
+// records `code`, raises the CTA's stop flag and returns; from then on every wait of the CTA
+// returns at once, the loops run out (their results are garbage and are not stored) and
+// the kernel ends normally.
+__device__ __forceinline__ void wait_parity(uint32_t bar, uint32_t parity, volatile int* stop, int* status,
                                             int code) {
-  if (ptx::mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (uint32_t spin = 1;; ++spin) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
+  if (ptx::mbar_try_wait(bar, parity)) return;
+  long long t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    if (ptx::mbar_try_wait(bar, parity)) return;
     if ((spin & 63u) == 0) {
-      if (*stop) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (*stop) return;
+      const long long now = clock64();
+      if (spin == 0) t0 = now;
+      if (now - t0 > kWaitLimitCycles) {
         *stop = 1;
         atomicOr(status, code);
-        return false;
+        return;
       }
     }
   }
@@ -136,104 +142,123 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
 
   const int total_tiles = p.tiles_m * p.tiles_n;
 
+  // Producer and MMA warps run their loops with all 32 lanes, so that addresses and
+  // descriptors are warp-uniform values; one elected lane issues the asynchronous operations.
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool live = true;
-      for (int t = blockIdx.x; t < total_tiles && live; t += gridDim.x) {
-        const int m_tile = t % p.tiles_m, n_tile = t / p.tiles_m;
-        for (int seg = 0; seg < 3 && live; ++seg) {
-          const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
-          const CUtensorMap* ta = seg == 0 ? &tmA0 : (seg == 1 ? &tmA1 : &tmA2);
-          const CUtensorMap* tb = seg == 0 ? &tmB0 : (seg == 1 ? &tmB1 : &tmB2);
-          const uint32_t tx_ab = seg == 0 ? p.tx_a[0] + p.tx_b[0]
-                                          : (seg == 1 ? p.tx_a[1] + p.tx_b[1] : p.tx_a[2] + p.tx_b[2]);
-          for (int s = 0; s < sp.nstages; ++s) {
-            if (!wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, 1)) { live = false; break; }
-            const int atom0 = seg == 0 ? 2 * s : s;
-            const int natoms = seg == 0 ? min(2, sp.katoms - atom0) : 1;
-            const uint32_t sbase = base + stage * C::STAGE_BYTES;
-            const uint32_t fb = full_bar(stage);
-            ptx::mbar_expect_tx(fb, tx_ab + (uint32_t)natoms * 512u * (1 + C::NB));
-            ptx::tma_load_2d(sbase, ta, s * 128, m_tile * BM, fb);
-            ptx::tma_load_2d(sbase + C::A_BYTES, tb, s * 128, n_tile * BN, fb);
-            ptx::bulk_load_1d(sbase + C::A_BYTES + C::B_BYTES,
-                              sp.sfa + ((size_t)m_tile * sp.katoms + atom0) * 512, natoms * 512, fb);
+    const bool leader = ptx::elect_one();
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const int m_tile = t % p.tiles_m, n_tile = t / p.tiles_m;
+#pragma unroll 1
+      for (int seg = 0; seg < 3; ++seg) {
+        const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
+        const CUtensorMap* ta = seg == 0 ? &tmA0 : (seg == 1 ? &tmA1 : &tmA2);
+        const CUtensorMap* tb = seg == 0 ? &tmB0 : (seg == 1 ? &tmB1 : &tmB2);
+        const uint32_t tx_ab = seg == 0 ? p.tx_a[0] + p.tx_b[0]
+                                        : (seg == 1 ? p.tx_a[1] + p.tx_b[1] : p.tx_a[2] + p.tx_b[2]);
+        const uint8_t* sfa_row = sp.sfa + (size_t)m_tile * sp.katoms * 512;
+        const uint8_t* sfb_row = sp.sfb + (size_t)n_tile * C::NB * sp.katoms * 512;
+#pragma unroll 1
+        for (int s = 0; s < sp.nstages; ++s) {
+          wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, 1);
+          const int atom0 = seg == 0 ? 2 * s : s;
+          const int natoms = seg == 0 ? min(2, sp.katoms - atom0) : 1;
+          const uint32_t sbase = base + stage * C::STAGE_BYTES;
+          const uint32_t fb = full_bar(stage);
+          if (leader) {
+            if (p.dbg & 2) {
+              ptx::mbar_arrive(fb);
+            } else {
+              ptx::mbar_expect_tx(fb, tx_ab + (uint32_t)natoms * 512u * (1 + C::NB));
+              ptx::tma_load_2d(sbase, ta, s * 128, m_tile * BM, fb);
+              ptx::tma_load_2d(sbase + C::A_BYTES, tb, s * 128, n_tile * BN, fb);
+              ptx::bulk_load_1d(sbase + C::A_BYTES + C::B_BYTES, sfa_row + (size_t)atom0 * 512, natoms * 512, fb);
 #pragma unroll
-            for (int nb = 0; nb < C::NB; ++nb)
-              ptx::bulk_load_1d(sbase + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + nb * 1024,
-                                sp.sfb + ((size_t)(n_tile * C::NB + nb) * sp.katoms + atom0) * 512,
-                                natoms * 512, fb);
-            if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+              for (int nb = 0; nb < C::NB; ++nb)
+                ptx::bulk_load_1d(sbase + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + nb * 1024,
+                                  sfb_row + ((size_t)nb * sp.katoms + atom0) * 512, natoms * 512, fb);
+            }
           }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      // instruction descriptors: scale type UE8M0, M = 128, N = BN, both operands K-major
-      const uint32_t common = ((uint32_t)(BN >> 3) << 17) | (1u << 23) | ((uint32_t)(BM >> 4) << 24);
-      const uint32_t idesc[3] = {common | (1u << 7) | (1u << 10),   // mxf4: E2M1 x E2M1
-                                 common | (4u << 7) | (5u << 10),   // E3M2 x E2M1
-                                 common | (0u << 7) | (5u << 10)};  // E4M3 x E2M1
-      int stage = 0;
-      uint32_t phase = 0, slot = 0;
-      bool live = true;
-      int it = 0;
-      for (int t = blockIdx.x; t < total_tiles && live; t += gridDim.x, ++it) {
-        const int acc = it % C::ACC;
-        const uint32_t acc_phase = (uint32_t)(it / C::ACC) & 1u;
-        if (!wait_parity(tempty_bar(acc), acc_phase ^ 1u, stop, p.status, 4)) { live = false; break; }
-        ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
-        uint32_t accumulate = 0;
-        for (int seg = 0; seg < 3 && live; ++seg) {
-          const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
-          const uint32_t id0 = seg == 0 ? idesc[0] : (seg == 1 ? idesc[1] : idesc[2]);
-          for (int s = 0; s < sp.nstages; ++s) {
-            if (!wait_parity(full_bar(stage), phase, stop, p.status, 2)) { live = false; break; }
-            ptx::tc_fence_after();
-            const uint32_t sbase = base + stage * C::STAGE_BYTES;
-            const uint32_t sfa_s = sbase + C::A_BYTES + C::B_BYTES;
-            const uint32_t sfb_s = sfa_s + C::SFA_BYTES;
-            const uint32_t sfa_t = tmem_base + C::SF_COL0 + slot * C::SF_SLOT_COLS;
-            const uint32_t sfb_t = sfa_t + 8;
-            const int atom0 = seg == 0 ? 2 * s : s;
-            const int natoms = seg == 0 ? min(2, sp.katoms - atom0) : 1;
-            for (int a = 0; a < natoms; ++a) {
-              ptx::tc_cp_sf(sfa_t + a * 4, ptx::smem_desc_sf(sfa_s + a * 512));
+    const bool leader = ptx::elect_one();
+    // instruction descriptors: scale type UE8M0, M = 128, N = BN, both operands K-major
+    constexpr uint32_t kCommon = ((uint32_t)(BN >> 3) << 17) | (1u << 23) | ((uint32_t)(BM >> 4) << 24);
+    constexpr uint32_t kIdesc[3] = {kCommon | (1u << 7) | (1u << 10),   // mxf4: E2M1 x E2M1
+                                    kCommon | (4u << 7) | (5u << 10),   // E3M2 x E2M1
+                                    kCommon | (0u << 7) | (5u << 10)};  // E4M3 x E2M1
+    int stage = 0;
+    uint32_t phase = 0, slot = 0;
+    int it = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      const int acc = it % C::ACC;
+      const uint32_t acc_phase = (uint32_t)(it / C::ACC) & 1u;
+      wait_parity(tempty_bar(acc), acc_phase ^ 1u, stop, p.status, 4);
+      ptx::tc_fence_after();
+      const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
+      uint32_t accumulate = 0;
+#pragma unroll 1
+      for (int seg = 0; seg < 3; ++seg) {
+        const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
+        const uint32_t id0 = seg == 0 ? kIdesc[0] : (seg == 1 ? kIdesc[1] : kIdesc[2]);
+#pragma unroll 1
+        for (int s = 0; s < sp.nstages; ++s) {
+          wait_parity(full_bar(stage), phase, stop, p.status, 2);
+          ptx::tc_fence_after();
+          const uint32_t sbase = base + stage * C::STAGE_BYTES;
+          const uint32_t sfa_lo = ptx::desc_lo(sbase + C::A_BYTES + C::B_BYTES);
+          const uint32_t sfb_lo = sfa_lo + (C::SFA_BYTES >> 4);
+          const uint32_t sfa_t = tmem_base + C::SF_COL0 + slot * C::SF_SLOT_COLS;
+          const uint32_t sfb_t = sfa_t + 8;
+          const uint32_t a_lo = ptx::desc_lo(sbase), b_lo = ptx::desc_lo(sbase + C::A_BYTES);
+          // K elements left in this segment, in MMA steps (64 for FP4, 32 for FP6 / FP8)
+          const int nm = seg == 0 ? min(4, (sp.kseg - s * 256) >> 6) : min(4, (sp.kseg - s * 128) >> 5);
+          if (leader && !(p.dbg & 1)) {
+            // scale atoms -> TMEM: atom a of A to columns a*4.., of B (per 128 columns) to a*NB*4 + nb*4..
+            ptx::tc_cp_sf(sfa_t, sfa_lo, ptx::kDescHiSf);
+#pragma unroll
+            for (int nb = 0; nb < C::NB; ++nb) ptx::tc_cp_sf(sfb_t + nb * 4, sfb_lo + nb * 64, ptx::kDescHiSf);
+            if (seg == 0 && nm > 2) {
+              ptx::tc_cp_sf(sfa_t + 4, sfa_lo + 32, ptx::kDescHiSf);
 #pragma unroll
               for (int nb = 0; nb < C::NB; ++nb)
-                ptx::tc_cp_sf(sfb_t + a * (C::NB * 4) + nb * 4, ptx::smem_desc_sf(sfb_s + nb * 1024 + a * 512));
+                ptx::tc_cp_sf(sfb_t + C::NB * 4 + nb * 4, sfb_lo + nb * 64 + 32, ptx::kDescHiSf);
             }
-            const uint64_t adesc = ptx::smem_desc_sw128(sbase);
-            const uint64_t bdesc = ptx::smem_desc_sw128(sbase + C::A_BYTES);
             if (seg == 0) {
-              const int nm = min(4, (sp.kseg - s * 256) >> 6);
-              for (int j = 0; j < nm; ++j) {
-                const uint32_t a = j >> 1, sfid = (j & 1) * 2;
-                ptx::mma_mxf4(d_tmem, adesc + j * 2, bdesc + j * 2, id0 | (sfid << 4) | (sfid << 29),
-                              sfa_t + a * 4, sfb_t + a * (C::NB * 4), accumulate);
-                accumulate = 1;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (j < nm) {
+                  constexpr uint32_t kNB4 = C::NB * 4;
+                  const uint32_t a = j >> 1, sfid = (j & 1) * 2;
+                  ptx::mma_mxf4(d_tmem, a_lo + j * 2, b_lo + j * 2, ptx::kDescHiSw128,
+                                id0 | (sfid << 4) | (sfid << 29), sfa_t + a * 4, sfb_t + a * kNB4, accumulate);
+                  accumulate = 1;
+                }
               }
             } else {
-              const int nm = min(4, (sp.kseg - s * 128) >> 5);
-              for (int j = 0; j < nm; ++j) {
-                ptx::mma_mxf8f6f4(d_tmem, adesc + j * 2, bdesc + j * 2,
-                                  id0 | ((uint32_t)j << 4) | ((uint32_t)j << 29), sfa_t, sfb_t, accumulate);
-                accumulate = 1;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (j < nm) {
+                  ptx::mma_mxf8f6f4(d_tmem, a_lo + j * 2, b_lo + j * 2, ptx::kDescHiSw128,
+                                    id0 | ((uint32_t)j << 4) | ((uint32_t)j << 29), sfa_t, sfb_t, accumulate);
+                  accumulate = 1;
+                }
               }
             }
-            ptx::tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
-            slot ^= 1u;
-            if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
           }
+          accumulate = 1;
+          if (leader) ptx::tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          slot ^= 1u;
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (live) ptx::tc_commit(tfull_bar(acc));
       }
+      if (leader) ptx::tc_commit(tfull_bar(acc));
     }
   } else {
     // ------------------------------------------------------------ epilogue (4 warps)
@@ -243,11 +268,11 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
       const int m_tile = t % p.tiles_m, n_tile = t / p.tiles_m;
       const int acc = it % C::ACC;
       const uint32_t acc_phase = (uint32_t)(it / C::ACC) & 1u;
-      bool ok = wait_parity(tfull_bar(acc), acc_phase, stop, p.status, 8);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      wait_parity(tfull_bar(acc), acc_phase, stop, p.status, 8);
+      __syncwarp();
       ptx::tc_fence_after();
       const int row = m_tile * BM + q * 32 + lane;
+      const bool store = row < p.M && !(p.dbg & 4) && !*stop;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * BN;
       const size_t goff = (size_t)row * p.ldd + (size_t)n_tile * BN;
 #pragma unroll 1
@@ -255,7 +280,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
         uint32_t r[32];
         ptx::tmem_ld_32x32(taddr + c * 32, r);
         ptx::tmem_ld_wait();
-        if (row < p.M) {
+        if (store) {
           if (p.C != nullptr) {
             const uint4* cp = reinterpret_cast<const uint4*>(p.C + goff + c * 32);
 #pragma unroll
@@ -274,19 +299,19 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
             uint4* fp = reinterpret_cast<uint4*>(p.Df32 + goff + c * 32);
 #pragma unroll
             for (int v = 0; v < 8; ++v) fp[v] = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
-            continue;
-          }
-          uint4* dp = reinterpret_cast<uint4*>(p.D + goff + c * 32);
+          } else {
+            uint4* dp = reinterpret_cast<uint4*>(p.D + goff + c * 32);
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint32_t w[4];
+            for (int v = 0; v < 4; ++v) {
+              uint32_t w[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + k * 2]),
-                                                       __uint_as_float(r[v * 8 + k * 2 + 1]));
-              w[k] = *reinterpret_cast<uint32_t*>(&h);
+              for (int k = 0; k < 4; ++k) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + k * 2]),
+                                                         __uint_as_float(r[v * 8 + k * 2 + 1]));
+                w[k] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              dp[v] = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            dp[v] = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
@@ -495,6 +520,8 @@ static int matmul_impl(bool f32_out, const uint8_t* AN, const uint8_t* BN_, cons
   p.tx_a[0] = BM * 128;       p.tx_b[0] = (uint32_t)bn * 128;
   p.tx_a[1] = BM * 96;        p.tx_b[1] = (uint32_t)bn * 64;
   p.tx_a[2] = BM * 128;       p.tx_b[2] = (uint32_t)bn * 64;
+
+  if (const char* e = std::getenv("MG_GEMM_DEBUG")) p.dbg = std::atoi(e);
 
   CUtensorMap maps[6];
   // a zero-sized segment still needs valid maps as kernel arguments: alias the first real one

@@ -10,6 +10,17 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// One lane of a converged warp gets true.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
@@ -75,27 +86,38 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// Shared-memory matrix descriptors are passed as (lo, hi) 32-bit halves: lo holds the
+// 16-byte-granular start address, hi the constant layout fields (see the constants below).
+
 // Copy one 512-byte scale atom (32 rows x 16 bytes) into 4 TMEM columns, replicated to the
 // four 32-lane quadrants.
-__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint32_t desc_lo, uint32_t desc_hi) {
+  asm volatile(
+      "{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\t"
+      "tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n\t}"
+      ::"r"(taddr), "r"(desc_lo), "r"(desc_hi)
+      : "memory");
 }
 
 // D(tmem) (+)= A(smem) * B(smem) with per-32 UE8M0 scales held in TMEM.
-__device__ __forceinline__ void mma_mxf8f6f4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa,
-                                             uint32_t sfb, uint32_t accumulate) {
+__device__ __forceinline__ void mma_mxf8f6f4(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                             uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], da, db, %4, [%6], [%7], p;\n\t}"
+      ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
       : "memory");
 }
-__device__ __forceinline__ void mma_mxf4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa,
-                                         uint32_t sfb, uint32_t accumulate) {
+__device__ __forceinline__ void mma_mxf4(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                         uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-      ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], da, db, %4, [%6], [%7], p;\n\t}"
+      ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
       : "memory");
 }
 
@@ -115,15 +137,12 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------- descriptors
-// Shared-memory matrix descriptor, K-major operand whose rows are 128 bytes, 128-byte
-// swizzle: 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
-  return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
-         ((uint64_t)2 << 61);
-}
-// Unswizzled 32 x 16-byte block (a scale atom): 8-row groups are 128 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sf(uint32_t saddr) {
-  return (uint64_t)((saddr >> 4) & 0x3FFF) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
-}
+// Low half of a shared-memory matrix descriptor: start address in 16-byte units.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) { return (saddr >> 4) & 0x3FFFu; }
+// High half, K-major operand with 128-byte rows and 128-byte swizzle: 8-row groups 1024 bytes
+// apart (bits 32-45), descriptor version 1 (bit 46), layout type SWIZZLE_128B = 2 (bits 61-63).
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+// High half, unswizzled 32 x 16-byte block (a scale atom): 8-row groups 128 bytes apart.
+constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);
 
 }  // namespace ptx
