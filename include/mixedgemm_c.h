@@ -122,6 +122,34 @@ int mg_matmul_f32(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, const
                   const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
                   void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * mg_matmul for callers that cannot allocate.  No counterpart in the reference (its binding
+ * allocates with torch on every call, src/bindings.cpp:36).
+ *
+ * Meant for hosts that have no way to get device memory when they need the product - a serving
+ * process whose own pool already owns all free HBM, so that cudaMalloc fails; a plugin whose
+ * execute callback must not allocate.  The scratch that mg_matmul takes from the caller lives in
+ * a fixed array inside the library instead (MG_STATIC_WS_BYTES, held by every device that loads
+ * the library until the process ends).  Same arguments and result as mg_matmul without the two
+ * workspace arguments.
+ *
+ *  - Problems whose padded copies need more than MG_STATIC_WS_BYTES (see
+ *    mg_matmul_workspace_bytes) are refused with MG_ERR_WORKSPACE; nothing is launched.
+ *  - The call itself makes no cudaMalloc / cudaFree and uses no allocating library routine.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress);
+ *    make that first call outside any stream capture.
+ *  - All calls share the one array and it keeps whatever the previous call left there.  Nothing
+ *    has to be cleared: each call rewrites every byte it later reads, zero padding included.
+ *    Two calls that overlap on the GPU (different streams, no dependency) race on it - order
+ *    them.
+ */
+#define MG_STATIC_WS_BYTES (24u << 20)
+int mg_matmul_static_ws(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, const uint8_t* BS,
+                        const uint8_t* AO, const uint8_t* BO, int M, int N, int KN, int KS, int KO,
+                        const void* C_bf16, void* D_bf16, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
+                        const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
+                        void* stream);
+
 #ifdef __cplusplus
 }
 #endif

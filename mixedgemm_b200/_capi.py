@@ -26,6 +26,7 @@ PROTOTYPES = {
     "mg_matmul_workspace_bytes": (_sz, [_i] * 5),
     "mg_matmul": (_i, [_vp] * 6 + [_i] * 5 + [_vp, _vp, _i] + [_vp] * 6 + [_vp, _sz, _vp]),
     "mg_matmul_f32": (_i, [_vp] * 6 + [_i] * 5 + [_vp, _vp, _i] + [_vp] * 6 + [_vp, _sz, _vp]),
+    "mg_matmul_static_ws": (_i, [_vp] * 6 + [_i] * 5 + [_vp, _vp, _i] + [_vp] * 6 + [_vp]),
     "mg_matmul_fp4": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "mg_matmul_fp6": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "mg_matmul_fp8": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),

@@ -577,3 +577,45 @@ extern "C" int mg_matmul_fp8(const uint8_t* A, const uint8_t* B, int M, int N, i
   return mg_matmul(nullptr, nullptr, nullptr, nullptr, A, B, M, N, 0, 0, K, C_bf16, D_bf16, N, nullptr, nullptr,
                    nullptr, nullptr, SFA, SFB, nullptr, 0, stream);
 }
+
+// ---------------------------------------------------------------- entry point that allocates nothing
+//
+// Some hosts of this library cannot obtain device memory at the moment they need a product:
+// a serving runtime that handed all free HBM to its own pool at start-up (a later cudaMalloc
+// simply fails there), or a plugin whose execute callback is forbidden to allocate because an
+// allocation may synchronise the whole device.  mg_matmul needs scratch only for K segments
+// that are not a multiple of 128, and only as much as the padded copies take; for those
+// callers the scratch below is part of the library image instead.  Every device that loads
+// the library carries it until the process exits.
+namespace {
+static __device__ __align__(256) uint8_t g_static_ws[MG_STATIC_WS_BYTES + 1024];
+uint8_t* g_static_ws_ptr[64];  // resolved address per device, 1024-aligned inside the array
+std::mutex g_static_ws_mu;
+}  // namespace
+
+extern "C" int mg_matmul_static_ws(const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
+                                   const uint8_t* AO, const uint8_t* BO, int M, int N, int KN, int KS, int KO,
+                                   const void* C_bf16, void* D_bf16, int ldd, const uint8_t* SFAN,
+                                   const uint8_t* SFBN, const uint8_t* SFAS, const uint8_t* SFBS,
+                                   const uint8_t* SFAO, const uint8_t* SFBO, void* stream) {
+  if (M < 0 || N <= 0 || KN < 0 || KS < 0 || KO < 0) return MG_ERR_SHAPE;
+  const size_t need = plan_workspace(M, N, KS, KO).total;
+  if (need > (size_t)MG_STATIC_WS_BYTES) return MG_ERR_WORKSPACE;  // beyond the built-in scratch
+  int dev = 0;
+  MG_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return MG_ERR_DEVICE;
+  uint8_t* ws = nullptr;
+  {
+    // The array's name is only a host-side handle; the device address has to be asked for,
+    // once per device, with that device current.
+    std::lock_guard<std::mutex> lk(g_static_ws_mu);
+    if (!g_static_ws_ptr[dev]) {
+      void* p = nullptr;
+      MG_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_ws));
+      g_static_ws_ptr[dev] = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~(uintptr_t)1023);
+    }
+    ws = g_static_ws_ptr[dev];
+  }
+  return matmul_impl(false, AN, BN_, AS, BS, AO, BO, M, N, KN, KS, KO, C_bf16, D_bf16, ldd, SFAN, SFBN, SFAS, SFBS,
+                     SFAO, SFBO, ws, (size_t)MG_STATIC_WS_BYTES, stream);
+}
