@@ -4,24 +4,33 @@
 // (FP4 in all three segments).  It produces byte-for-byte what MixedGemm's
 // reorder_bf16_mixed_kernel / reorder_bf16_fp4_kernel write (src/reorder.cu:94-432 of that
 // project), but is organised for an HBM-bound B200:
-//   * a CTA stages R whole rows in shared memory with 128-bit coalesced loads and keeps
-//     the reorder index there, pre-multiplied to byte offsets, for all its row tiles;
-//   * a thread owns one (row, 32-element group): lanes of a warp walk R rows of the same
+//   * one persistent CTA per SM; a producer warp streams whole rows into a ring of
+//     shared-memory stages with 1-D bulk copies (cp.async.bulk + mbarrier), R rows per stage,
+//     while 16 consumer warps quantise the previous stage - loads, math and stores overlap;
+//   * the reorder index stays in shared memory for the life of the CTA, pre-multiplied to
+//     byte offsets;
+//   * a thread owns one (row, 32-element group): lanes of a warp walk the R rows of the same
 //     group, and rows are skewed by 16 bytes, so the channel gather hits distinct banks;
 //   * the group maximum, the E8M0 scale (exponent arithmetic, no log2) and the codes are
 //     computed in registers; codes leave as 16/8-byte vector stores;
 //   * float -> E2M1/E3M2/E4M3 uses the sm_100 cvt.rn.satfinite.*x2 instructions.
+// Waits on mbarriers are bounded; on expiry a code goes to the device status word and the
+// CTA winds down (see wait_parity).
 #include <cuda_bf16.h>
 #include <cuda_fp4.h>
 #include <cuda_fp6.h>
 #include <cuda_fp8.h>
 
 #include "mg_common.h"
+#include "ptx_sm100.cuh"
 
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kRowSkew = 16;  // bytes added to the shared-memory row pitch
+constexpr int kConsumerWarps = 16;
+constexpr int kConsumers = kConsumerWarps * 32;
+constexpr int kThreads = kConsumers + 32;  // + one producer warp
+constexpr int kRowSkew = 16;               // bytes added to the shared-memory row pitch
+constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
 
 struct SegOut {
   uint8_t* codes;  // packed codes of this segment
@@ -37,20 +46,28 @@ struct ReorderParams {
   int g4, g46;  // groups in segment 0, in segments 0+1
   SegOut seg[3];
   int num_tiles;
+  int stages;
+  int* status;
 };
 
-__device__ __forceinline__ int4 ld_stream16(const void* p) {
-  int4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
-// Integer nearest, halves away from zero, sign kept on zero: roundf() for |t| < 2^22.
-__device__ __forceinline__ float round_half_away(float t) {
-  float h = __uint_as_float((__float_as_uint(t) & 0x80000000u) | 0x3f000000u);
-  return truncf(t + h);
+// Bounded mbarrier wait; after a timeout every wait of the CTA returns at once.
+__device__ __forceinline__ void wait_parity(uint32_t bar, uint32_t parity, volatile int* stop, int* status,
+                                            int code) {
+  if (ptx::mbar_try_wait(bar, parity)) return;
+  long long t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    if (ptx::mbar_try_wait(bar, parity)) return;
+    if ((spin & 63u) == 0) {
+      if (*stop) return;
+      const long long now = clock64();
+      if (spin == 0) t0 = now;
+      if (now - t0 > kWaitLimitCycles) {
+        *stop = 1;
+        atomicOr(status, code);
+        return;
+      }
+    }
+  }
 }
 
 // E8M0 byte of the smallest power of two 2^e with maxv <= fmt_max * 2^e, from the bf16
@@ -65,135 +82,205 @@ __device__ __forceinline__ int scale_byte(float maxv, int fmt) {
   return a == 0 ? 126 : sf;
 }
 
+__device__ __forceinline__ unsigned lds_u16(uint32_t addr) {
+  unsigned short v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// What a thread keeps for its row across the groups it quantises in one stage.
+struct RowCtx {
+  uint32_t smem_row;    // shared address of the staged row
+  uint32_t sf_row;      // row part of the scale offset: (row%32)*16 + (row/32%4)*4
+  uint32_t row_blk;     // row / 128
+  uint32_t row;
+};
+
+// round(x * rs) to the nearest integer, halves away from zero, keeping the sign of x on zero
+// (what roundf() returns for these magnitudes): trunc(x*rs + copysign(0.5, x)).
+__device__ __forceinline__ float scale_round(float x, float rs) {
+  const float h = __uint_as_float((__float_as_uint(x) & 0x80000000u) | 0x3f000000u);
+  return truncf(fmaf(x, rs, h));
+}
+
+// One (row, group): gather, scale, quantise, pack, store.
+template <bool WEIGHTS>
+__device__ __forceinline__ void quantise_group(const ReorderParams& p, const RowCtx& rc, uint32_t idx2_addr, int g) {
+  float x[32];
+  float maxv = 0.f;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint4 iv = lds_v4(idx2_addr + g * 64 + q * 16);
+    const unsigned o[4] = {iv.x, iv.y, iv.z, iv.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const unsigned lo = lds_u16(rc.smem_row + (o[j] & 0xFFFFu));
+      const unsigned hi = lds_u16(rc.smem_row + (o[j] >> 16));
+      x[q * 8 + j * 2] = __uint_as_float(lo << 16);
+      x[q * 8 + j * 2 + 1] = __uint_as_float(hi << 16);
+      maxv = fmaxf(maxv, fmaxf(fabsf(x[q * 8 + j * 2]), fabsf(x[q * 8 + j * 2 + 1])));
+    }
+  }
+
+  const int seg = g < p.g4 ? 0 : (g < p.g46 ? 1 : 2);
+  const int gs = g - (seg == 0 ? 0 : (seg == 1 ? p.g4 : p.g46));
+  const int fmt = WEIGHTS ? 0 : seg;
+  const SegOut so = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
+
+  const int sf = scale_byte(maxv, fmt);
+  so.sf[rc.sf_row + (gs & 3) + (size_t)(gs >> 2) * 512 + (size_t)rc.row_blk * 512 * so.katoms] = (uint8_t)sf;
+  const float rs = __uint_as_float((unsigned)(254 - sf) << 23);  // 2^(127-sf)
+
+#pragma unroll
+  for (int i = 0; i < 32; ++i) x[i] = scale_round(x[i], rs);
+
+  uint8_t* out = so.codes + (size_t)rc.row * so.pitch;
+  if (fmt == 0) {
+    unsigned wds[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      // four cvt.rn.satfinite.e2m1x2.f32 (first source -> high nibble) packed into one word
+      asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+          "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+          "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+          "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+          "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+          "mov.b32 %0, {b0, b1, b2, b3};\n\t}"
+          : "=r"(wds[q])
+          : "f"(x[q * 8]), "f"(x[q * 8 + 1]), "f"(x[q * 8 + 2]), "f"(x[q * 8 + 3]), "f"(x[q * 8 + 4]),
+            "f"(x[q * 8 + 5]), "f"(x[q * 8 + 6]), "f"(x[q * 8 + 7]));
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)gs * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+  } else if (fmt == 1) {
+    unsigned w24[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      unsigned p01 = __nv_cvt_float2_to_fp6x2(make_float2(x[q * 4], x[q * 4 + 1]), __NV_E3M2, cudaRoundNearest);
+      unsigned p23 = __nv_cvt_float2_to_fp6x2(make_float2(x[q * 4 + 2], x[q * 4 + 3]), __NV_E3M2, cudaRoundNearest);
+      w24[q] = (p01 & 0x3Fu) | ((p01 >> 2) & 0xFC0u) | ((p23 & 0x3Fu) << 12) | ((p23 & 0x3F00u) << 10);
+    }
+    unsigned ow[6];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const unsigned a = w24[h * 4], b = w24[h * 4 + 1], c = w24[h * 4 + 2], d = w24[h * 4 + 3];
+      ow[h * 3] = a | (b << 24);
+      ow[h * 3 + 1] = (b >> 8) | (c << 16);
+      ow[h * 3 + 2] = (c >> 16) | (d << 8);
+    }
+    uint2* o8 = reinterpret_cast<uint2*>(out + (size_t)gs * 24);
+    o8[0] = make_uint2(ow[0], ow[1]);
+    o8[1] = make_uint2(ow[2], ow[3]);
+    o8[2] = make_uint2(ow[4], ow[5]);
+  } else {
+    unsigned wds[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      unsigned wd = 0;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        // the reference rounds the integer to bf16 before the E4M3 conversion
+        float a = __bfloat162float(__float2bfloat16_rn(x[q * 4 + j * 2]));
+        float b = __bfloat162float(__float2bfloat16_rn(x[q * 4 + j * 2 + 1]));
+        unsigned h = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+        wd |= (h & 0xFFFFu) << (16 * j);
+      }
+      wds[q] = wd;
+    }
+    uint4* o16 = reinterpret_cast<uint4*>(out + (size_t)gs * 32);
+    o16[0] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+    o16[1] = make_uint4(wds[4], wds[5], wds[6], wds[7]);
+  }
+}
+
 template <int R, bool WEIGHTS>
-__global__ void __launch_bounds__(kThreads) reorder_quantize_kernel(const ReorderParams p) {
+__global__ void __launch_bounds__(kThreads, 1) reorder_quantize_kernel(const ReorderParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int K = p.K;
-  const int tid = threadIdx.x;
-  uint16_t* idx2 = reinterpret_cast<uint16_t*>(smem);
-  uint8_t* tile = smem + ((2 * K + 15) & ~15);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int S = p.stages;
   const int pitch = 2 * K + kRowSkew;
+  const int idx_bytes = (2 * K + 15) & ~15;
+  uint16_t* idx2 = reinterpret_cast<uint16_t*>(smem);
+  uint8_t* tiles = smem + idx_bytes;
+  const int stage_bytes = R * pitch;
+  uint8_t* tail = tiles + (size_t)S * stage_bytes;  // barriers: full[8], empty[8], then the stop flag
+  const uint32_t bar0 = ptx::smem_u32(tail);
+  volatile int* stop = reinterpret_cast<volatile int*>(tail + 16 * 8);
 
   for (int i = tid; i < K; i += kThreads) {
     unsigned v = (uint16_t)p.idx[i];
     v = min(v, (unsigned)(K - 1));
     idx2[i] = (uint16_t)(v * 2);
   }
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      ptx::mbar_init(bar0 + 8 * s, 1);                     // full: one expect_tx arrival + bytes
+      ptx::mbar_init(bar0 + 8 * (8 + s), kConsumerWarps);  // empty: one arrival per consumer warp
+    }
+    *stop = 0;
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+
+  // This CTA's contiguous share of the rows, walked in stages of up to R rows.
+  const int row_begin = (int)((long long)p.rows * blockIdx.x / gridDim.x);
+  const int row_end = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
+  const int nstage = (row_end - row_begin + R - 1) / R;
 
   const int G = K >> 5;
-  const int chunks = K >> 3;  // 16-byte chunks per row
-
-  for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
-    const int row0 = t * R;
-    __syncthreads();  // the previous tile has been consumed (and idx2 is written)
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const bool live = row0 + r < p.rows;
-      const uint16_t* src = p.X + (size_t)(row0 + r) * K;
-#pragma unroll 2
-      for (int c = tid; c < chunks; c += kThreads) {
-        int4 v = make_int4(0, 0, 0, 0);
-        if (live) v = ld_stream16(src + c * 8);
-        *reinterpret_cast<int4*>(tile + r * pitch + c * 16) = v;
+  if (warp == kConsumerWarps) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      for (int it = 0; it < nstage; ++it) {
+        const int s = it % S;
+        const uint32_t ph = (uint32_t)(it / S) & 1u;
+        wait_parity(bar0 + 8 * (8 + s), ph ^ 1u, stop, p.status, 16);
+        const int row0 = row_begin + it * R;
+        const int nrows = min(R, row_end - row0);
+        const uint32_t fb = bar0 + 8 * s;
+        ptx::mbar_expect_tx(fb, (uint32_t)nrows * 2u * K);
+        const uint32_t dst = ptx::smem_u32(tiles + (size_t)s * stage_bytes);
+        for (int r = 0; r < nrows; ++r)
+          ptx::bulk_load_1d(dst + r * pitch, p.X + (size_t)(row0 + r) * K, 2u * K, fb);
       }
     }
-    __syncthreads();
-
-    for (int w = tid; w < R * G; w += kThreads) {
-      const int r = w % R, g = w / R;
-      const int row = row0 + r;
-      if (row >= p.rows) continue;
-      const uint8_t* rowp = tile + r * pitch;
-      const uint4* ip = reinterpret_cast<const uint4*>(idx2 + g * 32);
-
-      float x[32];
-      float maxv = 0.f;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint4 iv = ip[q];
-        const unsigned o[4] = {iv.x, iv.y, iv.z, iv.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          unsigned lo = *reinterpret_cast<const uint16_t*>(rowp + (o[j] & 0xFFFFu));
-          unsigned hi = *reinterpret_cast<const uint16_t*>(rowp + (o[j] >> 16));
-          x[q * 8 + j * 2] = __uint_as_float(lo << 16);
-          x[q * 8 + j * 2 + 1] = __uint_as_float(hi << 16);
-          maxv = fmaxf(maxv, fmaxf(fabsf(x[q * 8 + j * 2]), fabsf(x[q * 8 + j * 2 + 1])));
-        }
+  } else {
+    // ---------------------------------------------------------------- consumers
+    const int r = tid % R;          // kConsumers is a multiple of R: a thread keeps its row
+    const int g0 = tid / R;
+    constexpr int kGStep = kConsumers / R;
+    const uint32_t idx2_addr = ptx::smem_u32(idx2);
+    for (int it = 0; it < nstage; ++it) {
+      const int s = it % S;
+      const uint32_t ph = (uint32_t)(it / S) & 1u;
+      wait_parity(bar0 + 8 * s, ph, stop, p.status, 32);
+      const int row = row_begin + it * R + r;
+      if (row < row_end && !*stop) {
+        RowCtx rc;
+        rc.smem_row = ptx::smem_u32(tiles + (size_t)s * stage_bytes) + r * pitch;
+        rc.sf_row = (uint32_t)(row & 31) * 16 + (uint32_t)((row >> 5) & 3) * 4;
+        rc.row_blk = (uint32_t)row >> 7;
+        rc.row = (uint32_t)row;
+        for (int g = g0; g < G; g += kGStep) quantise_group<WEIGHTS>(p, rc, idx2_addr, g);
       }
-
-      const int seg = g < p.g4 ? 0 : (g < p.g46 ? 1 : 2);
-      const int gs = g - (seg == 0 ? 0 : (seg == 1 ? p.g4 : p.g46));
-      const int fmt = WEIGHTS ? 0 : seg;
-      const SegOut so = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
-
-      const int sf = scale_byte(maxv, fmt);
-      so.sf[(size_t)(row & 31) * 16 + (size_t)((row >> 5) & 3) * 4 + (gs & 3) + (size_t)(gs >> 2) * 512 +
-            (size_t)(row >> 7) * 512 * so.katoms] = (uint8_t)sf;
-      const float rs = __uint_as_float((unsigned)(254 - sf) << 23);  // 2^(127-sf)
-
-#pragma unroll
-      for (int i = 0; i < 32; ++i) x[i] = round_half_away(x[i] * rs);
-
-      uint8_t* out = so.codes + (size_t)row * so.pitch;
-      if (fmt == 0) {
-        unsigned wds[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          unsigned wd = 0;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            unsigned b = __nv_cvt_float2_to_fp4x2(make_float2(x[q * 8 + j * 2], x[q * 8 + j * 2 + 1]),
-                                                  __NV_E2M1, cudaRoundNearest);
-            wd |= (b & 0xFFu) << (8 * j);
-          }
-          wds[q] = wd;
-        }
-        *reinterpret_cast<uint4*>(out + (size_t)gs * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
-      } else if (fmt == 1) {
-        unsigned w24[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          unsigned p01 = __nv_cvt_float2_to_fp6x2(make_float2(x[q * 4], x[q * 4 + 1]), __NV_E3M2, cudaRoundNearest);
-          unsigned p23 = __nv_cvt_float2_to_fp6x2(make_float2(x[q * 4 + 2], x[q * 4 + 3]), __NV_E3M2, cudaRoundNearest);
-          w24[q] = (p01 & 0x3Fu) | ((p01 >> 2) & 0xFC0u) | ((p23 & 0x3Fu) << 12) | ((p23 & 0x3F00u) << 10);
-        }
-        unsigned ow[6];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const unsigned a = w24[h * 4], b = w24[h * 4 + 1], c = w24[h * 4 + 2], d = w24[h * 4 + 3];
-          ow[h * 3] = a | (b << 24);
-          ow[h * 3 + 1] = (b >> 8) | (c << 16);
-          ow[h * 3 + 2] = (c >> 16) | (d << 8);
-        }
-        uint2* o8 = reinterpret_cast<uint2*>(out + (size_t)gs * 24);
-        o8[0] = make_uint2(ow[0], ow[1]);
-        o8[1] = make_uint2(ow[2], ow[3]);
-        o8[2] = make_uint2(ow[4], ow[5]);
-      } else {
-        unsigned wds[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          unsigned wd = 0;
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-            // the reference rounds the integer to bf16 before the E4M3 conversion
-            float a = __bfloat162float(__float2bfloat16_rn(x[q * 4 + j * 2]));
-            float b = __bfloat162float(__float2bfloat16_rn(x[q * 4 + j * 2 + 1]));
-            unsigned h = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-            wd |= (h & 0xFFFFu) << (16 * j);
-          }
-          wds[q] = wd;
-        }
-        uint4* o16 = reinterpret_cast<uint4*>(out + (size_t)gs * 32);
-        o16[0] = make_uint4(wds[0], wds[1], wds[2], wds[3]);
-        o16[1] = make_uint4(wds[4], wds[5], wds[6], wds[7]);
-      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(bar0 + 8 * (8 + s));
     }
+  }
+  __syncthreads();
+  if (*stop) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);  // let copies in flight land
   }
 }
 
-size_t smem_bytes(int K, int R) { return (size_t)((2 * K + 15) & ~15) + (size_t)R * (2 * K + kRowSkew); }
+size_t smem_bytes(int K, int R, int S) {
+  return (size_t)((2 * K + 15) & ~15) + (size_t)S * R * (2 * K + kRowSkew) + 16 * 8 + 16;
+}
 
 template <int R, bool WEIGHTS>
 int launch(const ReorderParams& p, int grid, size_t smem, cudaStream_t st) {
@@ -231,15 +318,23 @@ int reorder_quantize(bool weights, const void* X, int rows, int K, const int16_t
   p.seg[1] = {o6, s6, (KS + 127) / 128, weights ? KS / 2 : KS / 4 * 3};
   p.seg[2] = {o8, s8, (KO + 127) / 128, weights ? KO / 2 : KO};
 
-  // Rows per tile: as many as keep three CTAs on an SM, fewer when that would leave SMs idle.
+  // Rows per stage: as many as fit twice (double buffering) beside the index, but no more than
+  // half of a CTA's share so that its last stage is not mostly empty.  Then as many stages as
+  // fit, up to 4.
+  const size_t budget = (size_t)di.smem_optin - 1024;
+  const int grid = rows < di.sm_count ? rows : di.sm_count;  // rows are dealt out evenly, at least one per CTA
+  const int rows_per_cta = rows / grid;
   int R = 8;
-  while (R > 1 && (smem_bytes(K, R) > 74 * 1024 || (rows + R - 1) / R < di.sm_count)) R >>= 1;
-  const size_t smem = smem_bytes(K, R);
+  while (R > 1 && (smem_bytes(K, R, 2) > budget || 2 * R > rows_per_cta)) R >>= 1;
+  int S = 2;
+  while (S < 4 && smem_bytes(K, R, S + 1) <= budget) ++S;
+  if (smem_bytes(K, R, 2) > budget) S = 1;
+  const size_t smem = smem_bytes(K, R, S);
   if (smem > (size_t)di.smem_optin) return MG_ERR_SHAPE;
   p.num_tiles = (rows + R - 1) / R;
-  int per_sm = (int)((size_t)228 * 1024 / (smem + 1024));
-  per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
-  int grid = p.num_tiles < di.sm_count * per_sm ? p.num_tiles : di.sm_count * per_sm;
+  p.stages = S;
+  rc = mg::device_status_word(&p.status);
+  if (rc != MG_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
 #define MG_LAUNCH_R(RR)                                                            \
