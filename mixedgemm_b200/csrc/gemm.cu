@@ -333,6 +333,283 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
   if (warp == 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
 }
 
+// ---------------------------------------------------------------- CTA-pair variant
+//
+// Two CTAs of a cluster (the two SMs of a TPC) compute one 256 x 256 tile with
+// tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and only its half (128
+// rows) of the B tile, so a stage is 35 KB instead of 51 KB for the same MMA time, and one
+// instruction issued by the leader CTA drives both tensor cores.  Per CTA:
+//   warp 0      TMA producer for this CTA's operands
+//   warp 1      MMA issuer (leader CTA only); owns the pair's TMEM allocation in both CTAs
+//   warp 2      relay: when this CTA's stage has landed, arrives on the leader's `ready` barrier
+//   warps 3-6   epilogue: TMEM -> registers -> bf16 -> swizzled shared staging -> TMA store;
+//               the accumulator is handed back as soon as it is in registers, so the next
+//               tile's MMAs overlap the stores
+template <int STAGES_, int NSLOT_>
+struct PairCfgT {
+  static constexpr int STAGES = STAGES_;
+  static constexpr int NSLOT = NSLOT_;  // 64-column output panels that can be staged at once
+  static constexpr int THREADS = 224;
+  static constexpr uint32_t A_BYTES = 128 * 128;
+  static constexpr uint32_t B_BYTES = 128 * 128;
+  static constexpr uint32_t SFA_BYTES = 1024;
+  static constexpr uint32_t SFB_BYTES = 2048;
+  static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;  // 35 KB
+  static constexpr uint32_t PANEL_BYTES = 128 * 128;         // 128 rows x 64 bf16 columns
+  static constexpr uint32_t STAGING_BYTES = NSLOT * PANEL_BYTES;
+  static constexpr uint32_t SF_COL0 = 256;
+  static constexpr uint32_t SF_SLOT_COLS = 8 + 16;
+  static constexpr size_t SMEM = 1024 + STAGING_BYTES + (size_t)STAGES * STAGE_BYTES + 256;
+};
+
+template <class C>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C::THREADS, 1)
+mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
+                       const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmA1,
+                       const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmA2,
+                       const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmD) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // staging first, then the stage ring, then barriers
+  uint8_t* gbase = smem_raw + (base - raw);
+  const uint32_t ring = base + C::STAGING_BYTES;
+  const uint32_t bar0 = ring + C::STAGES * C::STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto ready_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (2 * C::STAGES + s); };
+  const uint32_t tfull_bar = bar0 + 8u * (3 * C::STAGES);
+  const uint32_t tempty_bar = bar0 + 8u * (3 * C::STAGES + 1);
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(
+      gbase + C::STAGING_BYTES + C::STAGES * C::STAGE_BYTES + 8 * (3 * C::STAGES + 2));
+  volatile int* stop = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(ready_bar(s), 2);  // one relay arrival per CTA (used in the leader only)
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    ptx::mbar_init(tfull_bar, 1);
+    ptx::mbar_init(tempty_bar, 8);  // four epilogue warps in each CTA (used in the leader only)
+    *stop = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tmap(&tmA0);
+    ptx::prefetch_tmap(&tmB0);
+    ptx::prefetch_tmap(&tmA1);
+    ptx::prefetch_tmap(&tmB1);
+    ptx::prefetch_tmap(&tmA2);
+    ptx::prefetch_tmap(&tmB2);
+    ptx::prefetch_tmap(&tmD);
+  }
+  ptx::cluster_sync();  // both CTAs' barriers exist before anything arrives on them
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  ptx::cluster_sync();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int tiles_m2 = (p.M + 255) / 256;
+  const int total_tiles = tiles_m2 * (p.N / 256);
+  const int first_tile = (int)ptx::cluster_id_x(), tile_step = (int)ptx::nclusters_x();
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    const bool leader = ptx::elect_one();
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int t = first_tile; t < total_tiles; t += tile_step) {
+      const int m_pt = t % tiles_m2, n_tile = t / tiles_m2;
+      const int m_row0 = m_pt * 256 + (int)rank * 128, n_row0 = n_tile * 256 + (int)rank * 128;
+#pragma unroll 1
+      for (int seg = 0; seg < 3; ++seg) {
+        const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
+        const CUtensorMap* ta = seg == 0 ? &tmA0 : (seg == 1 ? &tmA1 : &tmA2);
+        const CUtensorMap* tb = seg == 0 ? &tmB0 : (seg == 1 ? &tmB1 : &tmB2);
+        const uint32_t tx_ab = seg == 0 ? p.tx_a[0] + p.tx_b[0]
+                                        : (seg == 1 ? p.tx_a[1] + p.tx_b[1] : p.tx_a[2] + p.tx_b[2]);
+        // a CTA whose 128 rows lie wholly beyond M reads the last real row block's scales (its
+        // accumulator rows are never stored), so that no copy leaves the scale buffer
+        const int row_blk = min(m_pt * 2 + (int)rank, (p.M + 127) / 128 - 1);
+        const uint8_t* sfa_row = sp.sfa + (size_t)row_blk * sp.katoms * 512;
+        const uint8_t* sfb_row = sp.sfb + (size_t)(n_tile * 2) * sp.katoms * 512;
+#pragma unroll 1
+        for (int s = 0; s < sp.nstages; ++s) {
+          wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, 1);
+          const int atom0 = seg == 0 ? 2 * s : s;
+          const int natoms = seg == 0 ? min(2, sp.katoms - atom0) : 1;
+          const uint32_t sbase = ring + stage * C::STAGE_BYTES;
+          const uint32_t fb = full_bar(stage);
+          if (leader && (p.dbg & 2)) {
+            ptx::mbar_arrive(fb);
+          } else if (leader) {
+            ptx::mbar_expect_tx(fb, tx_ab + (uint32_t)natoms * 512u * 3u);
+            ptx::tma_load_2d(sbase, ta, s * 128, m_row0, fb);
+            ptx::tma_load_2d(sbase + C::A_BYTES, tb, s * 128, n_row0, fb);
+            ptx::bulk_load_1d(sbase + C::A_BYTES + C::B_BYTES, sfa_row + (size_t)atom0 * 512, natoms * 512, fb);
+#pragma unroll
+            for (int nb = 0; nb < 2; ++nb)
+              ptx::bulk_load_1d(sbase + C::A_BYTES + C::B_BYTES + C::SFA_BYTES + nb * 1024,
+                                sfb_row + ((size_t)nb * sp.katoms + atom0) * 512, natoms * 512, fb);
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------ relay: stage landed -> leader's ready barrier
+    int stage = 0;
+    uint32_t phase = 0;
+    const int nst = p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages;
+    for (int t = first_tile; t < total_tiles; t += tile_step) {
+#pragma unroll 1
+      for (int s = 0; s < nst; ++s) {
+        wait_parity(full_bar(stage), phase, stop, p.status, 64);
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ready_bar(stage), 0));
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA)
+    if (rank == 0) {
+      const bool leader = ptx::elect_one();
+      // instruction descriptors: scale type UE8M0, M = 256 (pair), N = 256, both operands K-major
+      constexpr uint32_t kCommon = ((uint32_t)(256 >> 3) << 17) | (1u << 23) | ((uint32_t)(256 >> 4) << 24);
+      constexpr uint32_t kIdesc[3] = {kCommon | (1u << 7) | (1u << 10), kCommon | (4u << 7) | (5u << 10),
+                                      kCommon | (0u << 7) | (5u << 10)};
+      int stage = 0;
+      uint32_t phase = 0, slot = 0;
+      int it = 0;
+      for (int t = first_tile; t < total_tiles; t += tile_step, ++it) {
+        wait_parity(tempty_bar, ((uint32_t)it & 1u) ^ 1u, stop, p.status, 4);
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base;
+        uint32_t accumulate = 0;
+#pragma unroll 1
+        for (int seg = 0; seg < 3; ++seg) {
+          const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
+          const uint32_t id0 = seg == 0 ? kIdesc[0] : (seg == 1 ? kIdesc[1] : kIdesc[2]);
+#pragma unroll 1
+          for (int s = 0; s < sp.nstages; ++s) {
+            wait_parity(ready_bar(stage), phase, stop, p.status, 2);
+            ptx::tc_fence_after();
+            const uint32_t sbase = ring + stage * C::STAGE_BYTES;
+            const uint32_t sfa_lo = ptx::desc_lo(sbase + C::A_BYTES + C::B_BYTES);
+            const uint32_t sfb_lo = sfa_lo + (C::SFA_BYTES >> 4);
+            const uint32_t sfa_t = tmem_base + C::SF_COL0 + slot * C::SF_SLOT_COLS;
+            const uint32_t sfb_t = sfa_t + 8;
+            const uint32_t a_lo = ptx::desc_lo(sbase), b_lo = ptx::desc_lo(sbase + C::A_BYTES);
+            const int nm = seg == 0 ? min(4, (sp.kseg - s * 256) >> 6) : min(4, (sp.kseg - s * 128) >> 5);
+            if (leader && (p.dbg & 1)) {
+              ptx::tc_commit_pair(empty_bar(stage), 3);
+            } else if (leader) {
+              ptx::tc_cp_sf_pair(sfa_t, sfa_lo, ptx::kDescHiSf);
+              ptx::tc_cp_sf_pair(sfb_t, sfb_lo, ptx::kDescHiSf);
+              ptx::tc_cp_sf_pair(sfb_t + 4, sfb_lo + 64, ptx::kDescHiSf);
+              if (seg == 0 && nm > 2) {
+                ptx::tc_cp_sf_pair(sfa_t + 4, sfa_lo + 32, ptx::kDescHiSf);
+                ptx::tc_cp_sf_pair(sfb_t + 8, sfb_lo + 32, ptx::kDescHiSf);
+                ptx::tc_cp_sf_pair(sfb_t + 12, sfb_lo + 64 + 32, ptx::kDescHiSf);
+              }
+              if (seg == 0) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  if (j < nm) {
+                    const uint32_t a = j >> 1, sfid = (j & 1) * 2;
+                    ptx::mma_mxf4_pair(d_tmem, a_lo + j * 2, b_lo + j * 2, ptx::kDescHiSw128,
+                                       id0 | (sfid << 4) | (sfid << 29), sfa_t + a * 4, sfb_t + a * 8, accumulate);
+                    accumulate = 1;
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  if (j < nm) {
+                    ptx::mma_mxf8f6f4_pair(d_tmem, a_lo + j * 2, b_lo + j * 2, ptx::kDescHiSw128,
+                                           id0 | ((uint32_t)j << 4) | ((uint32_t)j << 29), sfa_t, sfb_t, accumulate);
+                    accumulate = 1;
+                  }
+                }
+              }
+              ptx::tc_commit_pair(empty_bar(stage), 3);  // frees the stage in both CTAs
+            }
+            accumulate = 1;
+            slot ^= 1u;
+            if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+        if (leader) ptx::tc_commit_pair(tfull_bar, 3);  // accumulators of both CTAs are complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 3-6)
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const int trow = q * 32 + lane;
+    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const uint32_t tempty_leader = ptx::map_to_cta(tempty_bar, 0);
+    const bool issuer = warp == 3 && lane == 0;
+    int it = 0;
+    for (int t = first_tile; t < total_tiles; t += tile_step, ++it) {
+      const int m_pt = t % tiles_m2, n_tile = t / tiles_m2;
+      wait_parity(tfull_bar, (uint32_t)it & 1u, stop, p.status, 8);
+      __syncwarp();
+      ptx::tc_fence_after();
+#pragma unroll 1
+      for (int j = 0; j < 4; ++j) {
+        // the store that last used this staging slot has finished reading it
+        if (issuer) ptx::bulk_wait_group_read<C::NSLOT - 1>();
+        ptx::named_barrier_sync(1, 128);
+        uint32_t r0[32], r1[32];
+        ptx::tmem_ld_32x32(taddr + j * 64, r0);
+        ptx::tmem_ld_32x32(taddr + j * 64 + 32, r1);
+        ptx::tmem_ld_wait();
+        if (j == 3) {  // the accumulator is in registers: hand TMEM back to the MMA warp
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader);
+        }
+        const uint32_t slot_addr = base + (uint32_t)(j % C::NSLOT) * C::PANEL_BYTES;
+        const uint32_t prow = slot_addr + trow * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t* r = c < 4 ? &r0[c * 8] : &r1[(c - 4) * 8];
+          uint32_t w[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[k * 2]), __uint_as_float(r[k * 2 + 1]));
+            w[k] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          ptx::sts_v4(prow + ((uint32_t)(c ^ (trow & 7)) << 4), w[0], w[1], w[2], w[3]);
+        }
+        ptx::fence_proxy_async_smem();
+        ptx::named_barrier_sync(1, 128);
+        const int m0 = m_pt * 256 + (int)rank * 128;
+        if (issuer) {
+          if (m0 < p.M && !*stop && !(p.dbg & 4)) ptx::tma_store_2d(&tmD, n_tile * 256 + j * 64, m0, slot_addr);
+          ptx::bulk_commit_group();  // one group per panel, also when nothing was stored
+        }
+      }
+    }
+    if (issuer) ptx::bulk_wait_group0();
+  }
+
+  // ------------------------------------------------------------ teardown
+  ptx::tc_fence_before();
+  ptx::cluster_sync();
+  ptx::tc_fence_after();
+  if (*stop) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    ptx::cluster_sync();
+  }
+  if (warp == 1) ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+}
+
 // Copies `rows` rows of `src_pitch` bytes to a wider pitch, zero-filling the tail; up to
 // four such jobs per launch (blockIdx.y).  Used for segments that are not a multiple of 128.
 struct RepackJob {
@@ -500,7 +777,13 @@ static int matmul_impl(bool f32_out, const uint8_t* AN, const uint8_t* BN_, cons
     MG_CUDA_TRY(cudaGetLastError());
   }
 
-  const int bn = choose_bn(M, N, di.sm_count);
+  // The CTA-pair kernel wants enough 256 x 256 tiles to occupy most SM pairs; smaller problems
+  // spread better as 128-row tiles over single SMs.
+  bool use_pair = !f32_out && C_bf16 == nullptr && N % 256 == 0 && M > 128;
+  const int pair_tiles = ((M + 255) / 256) * (N / 256);
+  if (const char* e = std::getenv("MG_GEMM_2CTA")) use_pair = use_pair && std::atoi(e) != 0;
+  else use_pair = use_pair && pair_tiles * 4 >= (di.sm_count / 2) * 3;
+  const int bn = use_pair ? 128 : choose_bn(M, N, di.sm_count);  // rows of one B tile load
 
   GemmParams p{};
   p.M = M;
@@ -538,6 +821,27 @@ static int matmul_impl(bool f32_out, const uint8_t* AN, const uint8_t* BN_, cons
       if ((rc = make_map(&maps[seg * 2], CU_TENSOR_MAP_DATA_TYPE_UINT8, AO, ws.kop, M, ws.kop, 128, BM))) return rc;
       if ((rc = make_map(&maps[seg * 2 + 1], CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, BO, ws.kop, N, ws.kop / 2, 128, bn))) return rc;
     }
+  }
+  if (use_pair) {
+    CUtensorMap mapD;
+    if ((rc = make_map(&mapD, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D_bf16, N, M, (uint64_t)ldd * 2, 64, 128))) return rc;
+    const int tiles = ((M + 255) / 256) * (N / 256);
+    const int clusters = tiles < di.sm_count / 2 ? tiles : di.sm_count / 2;
+    int variant = 1;
+    if (const char* e = std::getenv("MG_GEMM_PAIR_VARIANT")) variant = std::atoi(e);
+    if (variant == 0) {
+      using PC = PairCfgT<4, 4>;
+      MG_CUDA_TRY(cudaFuncSetAttribute(mixed_gemm_pair_kernel<PC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PC::SMEM));
+      mixed_gemm_pair_kernel<PC><<<2 * clusters, PC::THREADS, PC::SMEM, st>>>(p, maps[0], maps[1], maps[2], maps[3],
+                                                                            maps[4], maps[5], mapD);
+    } else {
+      using PC = PairCfgT<5, 2>;
+      MG_CUDA_TRY(cudaFuncSetAttribute(mixed_gemm_pair_kernel<PC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PC::SMEM));
+      mixed_gemm_pair_kernel<PC><<<2 * clusters, PC::THREADS, PC::SMEM, st>>>(p, maps[0], maps[1], maps[2], maps[3],
+                                                                            maps[4], maps[5], mapD);
+    }
+    MG_CUDA_TRY(cudaGetLastError());
+    return MG_OK;
   }
   return bn == 256 ? launch_gemm<256>(p, maps, di.sm_count, st) : launch_gemm<128>(p, maps, di.sm_count, st);
 }

@@ -94,9 +94,31 @@ def test_small_shapes(M, N, split):
 
 @pytest.mark.parametrize("bn", ["128", "256"])
 def test_both_tile_widths(bn, monkeypatch):
+    """The single-CTA kernel with 128- and 256-column tiles."""
+    monkeypatch.setenv("MG_GEMM_2CTA", "0")
     monkeypatch.setenv("MG_GEMM_BN", bn)
     M, N, split = 384, 1024, (1280, 768, 128)
     A, B = _quantise(M, N, sum(split), split, seed=9)
+    _check(A, B, M, N, split)
+
+
+@pytest.mark.parametrize("M,N,split", [(256, 256, (256, 128, 128)), (300, 512, (640, 384, 128)),
+                                       (129, 256, (128, 0, 0)), (1000, 768, (2560, 1408, 128)),
+                                       (640, 256, (384, 192, 64)), (2048, 1024, (2560, 1408, 128))])
+def test_cta_pair_kernel_equals_single_cta_kernel(M, N, split, monkeypatch):
+    """The CTA-pair kernel (256 x 256 tiles over two SMs, TMA-store epilogue) and the single-CTA
+    kernel accumulate the same products in the same order: same bytes, and both pass the oracle."""
+    import mixedgemm_b200 as mg
+    A, B = _quantise(M, N, sum(split), split, seed=M)
+    args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+    monkeypatch.setenv("MG_GEMM_2CTA", "1")
+    Yp = mg.matmul(*args)
+    monkeypatch.setenv("MG_GEMM_2CTA", "0")
+    Ys = mg.matmul(*args)
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    assert torch.equal(Yp.view(torch.int16), Ys.view(torch.int16))
+    monkeypatch.setenv("MG_GEMM_2CTA", "1")
     _check(A, B, M, N, split)
 
 
