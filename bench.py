@@ -231,7 +231,7 @@ class Job:
                 self.flops_local += 2 * M * Nl * K
                 self.flops_total += 2 * M * N * K
                 self.gemm_shapes.append((M, Nl, K))
-                self.n_kernels += 1 + (1 if (KS % 128 or KO % 128) else 0)
+                self.n_kernels += 1  # row-pitched buffers: no padded copy before the GEMM
             self.n_kernels += 1
             self.reorder_bytes += reorder_bytes(M, K)
             self.groups.append(dict(K=K, split=(KN, KS, KO), X=Xb, idx=idx, A=A, layers=Ls))

@@ -111,6 +111,29 @@ int mg_matmul(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, const uin
               void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Row-pitched variants.  The reference keeps every code buffer dense ([rows, K/2] and so on,
+ * src/bindings.cpp:88-90, :207-209); a segment that is only a multiple of 64 elements (K = 14336
+ * gives 4928 and 448) then has a row pitch that the unpacking tensor maps cannot take, and
+ * mg_matmul has to copy it.  Buffers allocated with the pitch mg_code_pitch() returns are read in
+ * place instead.  Logical contents are unchanged: row r of a buffer starts at r * pitch and its
+ * first K/2 (3K/4, K) bytes are the reference's row; the bytes after them are never interpreted.
+ *   pitches of mg_reorder_quantize_pitched: {FP4 buffer, FP6 (or second FP4) buffer, FP8 (or third FP4) buffer}
+ *   pitches of mg_matmul_pitched:           {AN, BN, AS, BS, AO, BO}
+ * mg_matmul_pitched needs workspace only for operands whose pitch does not qualify
+ * (mg_matmul_pitched_workspace_bytes); out_f32 != 0 selects the fp32 output of mg_matmul_f32.
+ */
+size_t mg_code_pitch(int weights, int segment, int kseg);
+int mg_reorder_quantize_pitched(int weights, const void* X, int rows, int K, const int16_t* idx, int KN, int KS,
+                                int KO, uint8_t* C4, uint8_t* C6, uint8_t* C8, const size_t* pitches,
+                                uint8_t* SF4, uint8_t* SF6, uint8_t* SF8, void* stream);
+size_t mg_matmul_pitched_workspace_bytes(int M, int N, int KN, int KS, int KO, const size_t* pitches);
+int mg_matmul_pitched(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, const uint8_t* BS,
+                      const uint8_t* AO, const uint8_t* BO, const size_t* pitches, int out_f32, int M, int N,
+                      int KN, int KS, int KO, const void* C_bf16, void* D, int ldd, const uint8_t* SFAN,
+                      const uint8_t* SFBN, const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO,
+                      const uint8_t* SFBO, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Same product with the fp32 accumulator written unrounded: D_f32 [M,N] float, pitch `ldd`
  * elements (ldd % 4 == 0).  The reference has no such output (its GEMMs write bf16,
  * src/fp4.cu:175-179); it exists so that the accumulation can be checked against a

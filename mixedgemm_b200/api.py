@@ -37,20 +37,43 @@ def _check_in(X, reorder_index, KN, KS, KO, what):
         raise RuntimeError("%s: K = %d does not match KN+KS+KO or the index length" % (what, X.size(1)))
 
 
-def alloc_quantized_x(M, KN, KS, KO, device):
-    """Output buffers of reorder_quantize_x with the reference's shapes (bindings.cpp:88-93)."""
+def _alloc_codes(rows, logical, pitch, device):
+    """[rows, logical] uint8 view of a buffer whose rows are `pitch` bytes apart."""
+    buf = torch.empty((rows, pitch), dtype=torch.uint8, device=device)
+    return buf[:, :logical] if pitch != logical else buf
+
+
+def alloc_quantized_x(M, KN, KS, KO, device, padded=True):
+    """Output buffers of reorder_quantize_x with the reference's shapes (bindings.cpp:88-93).
+    With padded=True the code tensors are row-pitched views (same shape, same contents) whose pitch
+    the GEMM can read in place even when a segment is only a multiple of 64."""
     lib = _capi.load()
     u8 = dict(dtype=torch.uint8, device=device)
-    return (torch.empty((M, KN // 2), **u8), torch.empty((M, KS // 4 * 3), **u8), torch.empty((M, KO), **u8)) + tuple(
+    logical = (KN // 2, KS // 4 * 3, KO)
+    pitch = [lib.mg_code_pitch(0, i, k) if padded else l for i, (k, l) in enumerate(zip((KN, KS, KO), logical))]
+    return tuple(_alloc_codes(M, l, p, device) for l, p in zip(logical, pitch)) + tuple(
         torch.empty(max(lib.mg_sf_bytes(M, k), (M // 128 + 1) * 128 * k // 32), **u8) for k in (KN, KS, KO))
 
 
-def alloc_quantized_w(N, KN, KS, KO, device):
-    """Output buffers of reorder_quantize_w (bindings.cpp:207-212)."""
+def alloc_quantized_w(N, KN, KS, KO, device, padded=True):
+    """Output buffers of reorder_quantize_w (bindings.cpp:207-212); see alloc_quantized_x."""
     lib = _capi.load()
     u8 = dict(dtype=torch.uint8, device=device)
-    return (torch.empty((N, KN // 2), **u8), torch.empty((N, KS // 2), **u8), torch.empty((N, KO // 2), **u8)) + tuple(
+    logical = (KN // 2, KS // 2, KO // 2)
+    pitch = [lib.mg_code_pitch(1, i, k) if padded else l for i, (k, l) in enumerate(zip((KN, KS, KO), logical))]
+    return tuple(_alloc_codes(N, l, p, device) for l, p in zip(logical, pitch)) + tuple(
         torch.empty(max(lib.mg_sf_bytes(N, k), N * k // 32), **u8) for k in (KN, KS, KO))
+
+
+def _pitches(tensors):
+    import ctypes
+    return (ctypes.c_size_t * len(tensors))(*[t.stride(0) if t.size(1) else 0 for t in tensors])
+
+
+def _check_codes(tensors, what):
+    for t in tensors:
+        if not t.is_cuda or t.dtype != torch.uint8 or t.dim() != 2 or (t.size(1) and t.stride(1) != 1):
+            raise RuntimeError("%s: code tensors must be 2-D CUDA uint8 with unit column stride" % what)
 
 
 def reorder_quantize_x(X, reorder_index, KN, KS, KO, seqlen=None, outfeatures=None, out=None):
@@ -62,9 +85,11 @@ def reorder_quantize_x(X, reorder_index, KN, KS, KO, seqlen=None, outfeatures=No
     M = X.size(0)
     dev = X.device
     XN, XS, XO, *sfs = out if out is not None else alloc_quantized_x(M, KN, KS, KO, dev)
+    _check_codes((XN, XS, XO), "reorder_quantize_x")
     with torch.cuda.device(dev):
-        st = lib.mg_reorder_quantize_x(_ptr(X), M, X.size(1), _ptr(reorder_index), KN, KS, KO, _ptr(XN), _ptr(XS),
-                                       _ptr(XO), _ptr(sfs[0]), _ptr(sfs[1]), _ptr(sfs[2]), _stream())
+        st = lib.mg_reorder_quantize_pitched(0, _ptr(X), M, X.size(1), _ptr(reorder_index), KN, KS, KO, _ptr(XN),
+                                             _ptr(XS), _ptr(XO), _pitches((XN, XS, XO)), _ptr(sfs[0]), _ptr(sfs[1]),
+                                             _ptr(sfs[2]), _stream())
     _capi.check(st, "reorder_quantize_x")
     return XN, XS, XO, sfs[0], sfs[1], sfs[2]
 
@@ -76,9 +101,11 @@ def reorder_quantize_w(W, reorder_index, KN, KS, KO, seqlen=None, outfeatures=No
     N = W.size(0)
     dev = W.device
     WN, WS, WO, *sfs = out if out is not None else alloc_quantized_w(N, KN, KS, KO, dev)
+    _check_codes((WN, WS, WO), "reorder_quantize_w")
     with torch.cuda.device(dev):
-        st = lib.mg_reorder_quantize_w(_ptr(W), N, W.size(1), _ptr(reorder_index), KN, KS, KO, _ptr(WN), _ptr(WS),
-                                       _ptr(WO), _ptr(sfs[0]), _ptr(sfs[1]), _ptr(sfs[2]), _stream())
+        st = lib.mg_reorder_quantize_pitched(1, _ptr(W), N, W.size(1), _ptr(reorder_index), KN, KS, KO, _ptr(WN),
+                                             _ptr(WS), _ptr(WO), _pitches((WN, WS, WO)), _ptr(sfs[0]), _ptr(sfs[1]),
+                                             _ptr(sfs[2]), _stream())
     _capi.check(st, "reorder_quantize_w")
     return WN, WS, WO, sfs[0], sfs[1], sfs[2]
 
@@ -107,9 +134,10 @@ def matmul(AN, BN, AS, BS, AO, BO, SFAN, SFBN, SFAS, SFBS, SFAO, SFBO, out=None,
     lib = _capi.load()
     M, N = AN.size(0), BN.size(0)
     KN, KS, KO = AN.size(1) * 2, AS.size(1) * 4 // 3, AO.size(1)
-    for t in (AN, BN, AS, BS, AO, BO, SFAN, SFBN, SFAS, SFBS, SFAO, SFBO):
+    _check_codes((AN, BN, AS, BS, AO, BO), "matmul")
+    for t in (SFAN, SFBN, SFAS, SFBS, SFAO, SFBO):
         if not t.is_cuda or t.dtype != torch.uint8 or not t.is_contiguous():
-            raise RuntimeError("matmul: operands must be contiguous CUDA uint8 tensors")
+            raise RuntimeError("matmul: scale tensors must be contiguous CUDA uint8 tensors")
     dev = AN.device
     dt = out.dtype if out is not None else (out_dtype or torch.bfloat16)
     if dt not in (torch.bfloat16, torch.float32):
@@ -117,12 +145,13 @@ def matmul(AN, BN, AS, BS, AO, BO, SFAN, SFBN, SFAS, SFBS, SFAO, SFBO, out=None,
     D = out if out is not None else torch.empty((M, N), dtype=dt, device=dev)
     if D.size(0) != M or D.size(1) != N or D.stride(1) != 1:
         raise RuntimeError("matmul: out must be [M,N] with unit column stride")
-    fn = lib.mg_matmul if dt == torch.bfloat16 else lib.mg_matmul_f32
+    pitches = _pitches((AN, BN, AS, BS, AO, BO))
     with torch.cuda.device(dev):
-        ws, wsb = _workspace(dev, lib.mg_matmul_workspace_bytes(M, N, KN, KS, KO))
-        st = fn(_ptr(AN), _ptr(BN), _ptr(AS), _ptr(BS), _ptr(AO), _ptr(BO), M, N, KN, KS, KO,
-                           _ptr(C), _ptr(D), D.stride(0), _ptr(SFAN), _ptr(SFBN), _ptr(SFAS), _ptr(SFBS),
-                           _ptr(SFAO), _ptr(SFBO), ws, wsb, _stream())
+        ws, wsb = _workspace(dev, lib.mg_matmul_pitched_workspace_bytes(M, N, KN, KS, KO, pitches))
+        st = lib.mg_matmul_pitched(_ptr(AN), _ptr(BN), _ptr(AS), _ptr(BS), _ptr(AO), _ptr(BO), pitches,
+                                   int(dt == torch.float32), M, N, KN, KS, KO, _ptr(C), _ptr(D), D.stride(0),
+                                   _ptr(SFAN), _ptr(SFBN), _ptr(SFAS), _ptr(SFBS), _ptr(SFAO), _ptr(SFBO), ws, wsb,
+                                   _stream())
     _capi.check(st, "matmul")
     return D
 

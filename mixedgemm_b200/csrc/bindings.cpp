@@ -31,10 +31,19 @@ void check(int status, const char* where) {
 
 uint8_t* u8(const torch::Tensor& t) { return t.numel() ? t.data_ptr<uint8_t>() : nullptr; }
 
-void check_u8(const torch::Tensor& t, const char* name) {
-  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kUInt8 && t.is_contiguous(), "matmul: ", name,
-              " must be a contiguous CUDA uint8 tensor");
+// Code tensors may be row-pitched views (what the quantisers of this module return); scale
+// tensors are flat.
+void check_u8(const torch::Tensor& t, const char* name, bool codes) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kUInt8, "matmul: ", name, " must be a CUDA uint8 tensor");
+  if (codes) {
+    TORCH_CHECK(t.dim() == 2 && (t.size(1) == 0 || t.stride(1) == 1), "matmul: ", name,
+                " must be 2-D with unit column stride");
+  } else {
+    TORCH_CHECK(t.is_contiguous(), "matmul: ", name, " must be contiguous");
+  }
 }
+
+size_t pitch_of(const torch::Tensor& t) { return t.size(1) ? (size_t)t.stride(0) : 0; }
 
 using Six = std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor>;
 
@@ -44,16 +53,15 @@ torch::Tensor matmul(const torch::Tensor& AN, const torch::Tensor& BN, const tor
                      const torch::Tensor& SFBS, const torch::Tensor& SFAO, const torch::Tensor& SFBO) {
   const torch::Tensor* all[] = {&AN, &BN, &AS, &BS, &AO, &BO, &SFAN, &SFBN, &SFAS, &SFBS, &SFAO, &SFBO};
   const char* names[] = {"AN", "BN", "AS", "BS", "AO", "BO", "SFAN", "SFBN", "SFAS", "SFBS", "SFAO", "SFBO"};
-  for (int i = 0; i < 12; ++i) check_u8(*all[i], names[i]);
-  TORCH_CHECK(AN.dim() == 2 && BN.dim() == 2 && AS.dim() == 2 && BS.dim() == 2 && AO.dim() == 2 && BO.dim() == 2,
-              "matmul: code tensors must be 2-D");
+  for (int i = 0; i < 12; ++i) check_u8(*all[i], names[i], i < 6);
   // shape inference as in the reference (src/bindings.cpp:30-34)
   const int M = (int)AN.size(0), N = (int)BN.size(0);
   const int KN = (int)AN.size(1) * 2, KS = (int)(AS.size(1) * 4 / 3), KO = (int)AO.size(1);
   c10::cuda::CUDAGuard guard(AN.device());
   auto stream = at::cuda::getCurrentCUDAStream();
   auto C = torch::empty({M, N}, torch::dtype(torch::kBFloat16).device(AN.device()));
-  const size_t wsb = mg_matmul_workspace_bytes(M, N, KN, KS, KO);
+  const size_t pitches[6] = {pitch_of(AN), pitch_of(BN), pitch_of(AS), pitch_of(BS), pitch_of(AO), pitch_of(BO)};
+  const size_t wsb = mg_matmul_pitched_workspace_bytes(M, N, KN, KS, KO, pitches);
   torch::Tensor ws;
   uint8_t* wsp = nullptr;
   if (wsb) {
@@ -61,8 +69,9 @@ torch::Tensor matmul(const torch::Tensor& AN, const torch::Tensor& BN, const tor
     wsp = ws.data_ptr<uint8_t>();
     wsp += (1024 - reinterpret_cast<uintptr_t>(wsp) % 1024) % 1024;
   }
-  check(mg_matmul(u8(AN), u8(BN), u8(AS), u8(BS), u8(AO), u8(BO), M, N, KN, KS, KO, nullptr, C.data_ptr(), N,
-                  u8(SFAN), u8(SFBN), u8(SFAS), u8(SFBS), u8(SFAO), u8(SFBO), wsp, wsb, stream.stream()),
+  check(mg_matmul_pitched(u8(AN), u8(BN), u8(AS), u8(BS), u8(AO), u8(BO), pitches, 0, M, N, KN, KS, KO, nullptr,
+                          C.data_ptr(), N, u8(SFAN), u8(SFBN), u8(SFAS), u8(SFBS), u8(SFAO), u8(SFBO), wsp, wsb,
+                          stream.stream()),
         "matmul");
   return C;
 }
@@ -85,13 +94,19 @@ Six reorder_quantize(bool weights, const torch::Tensor& X, const torch::Tensor& 
     const int64_t ref = weights ? (int64_t)R * k / 32 : (int64_t)(R / 128 + 1) * 128 * k / 32;
     return std::max<int64_t>(ref, (int64_t)mg_sf_bytes(R, k));
   };
-  auto c4 = torch::empty({R, KN / 2}, o);
-  auto c6 = torch::empty({R, weights ? KS / 2 : KS / 4 * 3}, o);
-  auto c8 = torch::empty({R, weights ? KO / 2 : KO}, o);
+  // the reference's shapes, as views of buffers whose row pitch the GEMM can read in place
+  auto codes = [&](int seg, int64_t logical, int k) {
+    const int64_t pitch = (int64_t)mg_code_pitch(weights, seg, k);
+    auto buf = torch::empty({R, pitch}, o);
+    return pitch == logical ? buf : buf.narrow(1, 0, logical);
+  };
+  auto c4 = codes(0, KN / 2, KN);
+  auto c6 = codes(1, weights ? KS / 2 : KS / 4 * 3, KS);
+  auto c8 = codes(2, weights ? KO / 2 : KO, KO);
   auto s4 = torch::empty({sf_len(KN)}, o), s6 = torch::empty({sf_len(KS)}, o), s8 = torch::empty({sf_len(KO)}, o);
-  auto fn = weights ? mg_reorder_quantize_w : mg_reorder_quantize_x;
-  check(fn(X.data_ptr(), R, K, reorder_index.data_ptr<int16_t>(), KN, KS, KO, u8(c4), u8(c6), u8(c8), u8(s4), u8(s6),
-           u8(s8), stream.stream()),
+  const size_t pitches[3] = {pitch_of(c4), pitch_of(c6), pitch_of(c8)};
+  check(mg_reorder_quantize_pitched(weights, X.data_ptr(), R, K, reorder_index.data_ptr<int16_t>(), KN, KS, KO, u8(c4),
+                                    u8(c6), u8(c8), pitches, u8(s4), u8(s6), u8(s8), stream.stream()),
         where);
   return std::make_tuple(c4, c6, c8, s4, s6, s8);
 }

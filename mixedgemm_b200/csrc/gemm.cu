@@ -615,7 +615,7 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
 struct RepackJob {
   const uint8_t* src;
   uint8_t* dst;
-  int rows, src_pitch, dst_pitch;
+  int rows, src_pitch, dst_pitch, copy_bytes;  // copy_bytes of every source row are real data
 };
 struct RepackJobs {
   RepackJob j[4];
@@ -623,7 +623,7 @@ struct RepackJobs {
 
 __global__ void repack_rows_kernel(const RepackJobs jobs) {
   const RepackJob jb = blockIdx.y == 0 ? jobs.j[0] : blockIdx.y == 1 ? jobs.j[1] : blockIdx.y == 2 ? jobs.j[2] : jobs.j[3];
-  const int words = jb.dst_pitch >> 2, src_words = jb.src_pitch >> 2;
+  const int words = jb.dst_pitch >> 2, src_words = jb.copy_bytes >> 2;
   const size_t total = (size_t)jb.rows * words;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int r = (int)(i / words), w = (int)(i - (size_t)r * words);
@@ -671,26 +671,52 @@ int make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, uint64_t k
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-struct Workspace {
-  size_t as, bs, ao, bo, total;
-  int ksp, kop;  // padded segment sizes
+// Where each of the six code buffers (AN, BN, AS, BS, AO, BO) is read from and with which row
+// pitch.  The tensor-map types that unpack FP6 / FP4 for kind::mxf8f6f4 need a pitch that is a
+// multiple of 32 bytes and covers the segment rounded up to 128 elements; a buffer that does
+// not offer that (the dense layout of a segment that is only a multiple of 64) is first copied
+// to such a pitch in the workspace.
+struct Plan {
+  size_t pitch[6];   // pitch the GEMM reads with
+  bool repack[6];
+  size_t off[6];     // workspace offset of the padded copy
+  size_t dense[6];   // bytes of real data per row
+  size_t total;      // workspace bytes
+  int ksp, kop;      // segment sizes rounded up to 128
+  int status;
 };
 
-Workspace plan_workspace(int M, int N, int KS, int KO) {
-  Workspace w{};
-  w.ksp = round_up(KS, 128);
-  w.kop = round_up(KO, 128);
+Plan make_plan(int M, int N, int KN, int KS, int KO, const size_t* pitches) {
+  Plan pl{};
+  pl.ksp = round_up(KS, 128);
+  pl.kop = round_up(KO, 128);
+  const size_t dense[6] = {(size_t)KN / 2, (size_t)KN / 2, (size_t)KS / 4 * 3, (size_t)KS / 2, (size_t)KO, (size_t)KO / 2};
+  const size_t need[6] = {(size_t)KN / 2, (size_t)KN / 2, (size_t)pl.ksp / 4 * 3, (size_t)pl.ksp / 2, (size_t)pl.kop,
+                          (size_t)pl.kop / 2};
+  const size_t align[6] = {16, 16, 32, 32, 16, 32};
+  const int rows[6] = {M, N, M, N, M, N};
+  const int kseg[6] = {KN, KN, KS, KS, KO, KO};
   size_t off = 0;
-  if (w.ksp != KS) {
-    w.as = off; off = align_up(off + (size_t)M * (w.ksp / 4 * 3), 1024);
-    w.bs = off; off = align_up(off + (size_t)N * (w.ksp / 2), 1024);
+  pl.status = MG_OK;
+  for (int i = 0; i < 6; ++i) {
+    pl.dense[i] = dense[i];
+    const size_t given = pitches ? pitches[i] : dense[i];
+    if (kseg[i] == 0) { pl.pitch[i] = 0; continue; }
+    if (given < dense[i]) { pl.status = MG_ERR_SHAPE; return pl; }
+    if (given % align[i] == 0 && given >= need[i]) {
+      pl.pitch[i] = given;
+    } else if (i < 2) {
+      pl.status = MG_ERR_ALIGN;  // the FP4 segment is a multiple of 128: only a bad pitch gets here
+      return pl;
+    } else {
+      pl.repack[i] = true;
+      pl.pitch[i] = need[i];
+      pl.off[i] = off;
+      off = align_up(off + (size_t)rows[i] * need[i], 1024);
+    }
   }
-  if (w.kop != KO) {
-    w.ao = off; off = align_up(off + (size_t)M * w.kop, 1024);
-    w.bo = off; off = align_up(off + (size_t)N * (w.kop / 2), 1024);
-  }
-  w.total = off;
-  return w;
+  pl.total = off;
+  return pl;
 }
 
 int choose_bn(int M, int N, int sms) {
@@ -723,13 +749,12 @@ int launch_gemm(const GemmParams& p, const CUtensorMap* maps, int sms, cudaStrea
 }  // namespace
 
 extern "C" size_t mg_matmul_workspace_bytes(int M, int N, int KN, int KS, int KO) {
-  (void)KN;
-  if (M <= 0 || N <= 0 || KS < 0 || KO < 0) return 0;
-  return plan_workspace(M, N, KS, KO).total;
+  if (M <= 0 || N <= 0 || KN < 0 || KS < 0 || KO < 0) return 0;
+  return make_plan(M, N, KN, KS, KO, nullptr).total;
 }
 
 static int matmul_impl(bool f32_out, const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
-                       const uint8_t* AO, const uint8_t* BO, int M, int N, int KN, int KS, int KO,
+                       const uint8_t* AO, const uint8_t* BO, const size_t* pitches, int M, int N, int KN, int KS, int KO,
                        const void* C_bf16, void* D_bf16, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
                        const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
                        void* workspace, size_t workspace_bytes, void* stream) {
@@ -753,29 +778,26 @@ static int matmul_impl(bool f32_out, const uint8_t* AN, const uint8_t* BN_, cons
   if (rc != MG_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-  // Segments that are not a multiple of 128 go through a 128-padded copy in the workspace.
-  const Workspace ws = plan_workspace(M, N, KS, KO);
-  if (ws.total) {
-    if (!workspace || workspace_bytes < ws.total) return MG_ERR_WORKSPACE;
+  // Buffers whose pitch the unpacking tensor maps cannot take go through a padded copy.
+  const Plan pl = make_plan(M, N, KN, KS, KO, pitches);
+  if (pl.status != MG_OK) return pl.status;
+  const uint8_t* src[6] = {AN, BN_, AS, BS, AO, BO};
+  if (pl.total) {
+    if (!workspace || workspace_bytes < pl.total) return MG_ERR_WORKSPACE;
     if (!mg::aligned(workspace, 1024)) return MG_ERR_ALIGN;
     uint8_t* w = static_cast<uint8_t*>(workspace);
     RepackJobs jobs{};
     int nj = 0;
-    if (ws.ksp != KS) {
-      jobs.j[nj++] = {AS, w + ws.as, M, KS / 4 * 3, ws.ksp / 4 * 3};
-      jobs.j[nj++] = {BS, w + ws.bs, N, KS / 2, ws.ksp / 2};
-      AS = w + ws.as;
-      BS = w + ws.bs;
-    }
-    if (ws.kop != KO) {
-      jobs.j[nj++] = {AO, w + ws.ao, M, KO, ws.kop};
-      jobs.j[nj++] = {BO, w + ws.bo, N, KO / 2, ws.kop / 2};
-      AO = w + ws.ao;
-      BO = w + ws.bo;
+    for (int i = 2; i < 6; ++i) {
+      if (!pl.repack[i]) continue;
+      jobs.j[nj++] = {src[i], w + pl.off[i], (i & 1) ? N : M, (int)(pitches ? pitches[i] : pl.dense[i]),
+                      (int)pl.pitch[i], (int)pl.dense[i]};
+      src[i] = w + pl.off[i];
     }
     repack_rows_kernel<<<dim3(di.sm_count * 2, nj), 256, 0, st>>>(jobs);
     MG_CUDA_TRY(cudaGetLastError());
   }
+  AS = src[2]; BS = src[3]; AO = src[4]; BO = src[5];
 
   // The CTA-pair kernel wants enough 256 x 256 tiles to occupy most SM pairs; smaller problems
   // spread better as 128-row tiles over single SMs.
@@ -812,14 +834,14 @@ static int matmul_impl(bool f32_out, const uint8_t* AN, const uint8_t* BN_, cons
   for (int seg = 0; seg < 3; ++seg) {
     const int s = (seg == 0 ? KN : seg == 1 ? KS : KO) ? seg : first;
     if (s == 0) {
-      if ((rc = make_map(&maps[seg * 2], CU_TENSOR_MAP_DATA_TYPE_UINT8, AN, KN / 2, M, KN / 2, 128, BM))) return rc;
-      if ((rc = make_map(&maps[seg * 2 + 1], CU_TENSOR_MAP_DATA_TYPE_UINT8, BN_, KN / 2, N, KN / 2, 128, bn))) return rc;
+      if ((rc = make_map(&maps[seg * 2], CU_TENSOR_MAP_DATA_TYPE_UINT8, AN, KN / 2, M, pl.pitch[0], 128, BM))) return rc;
+      if ((rc = make_map(&maps[seg * 2 + 1], CU_TENSOR_MAP_DATA_TYPE_UINT8, BN_, KN / 2, N, pl.pitch[1], 128, bn))) return rc;
     } else if (s == 1) {
-      if ((rc = make_map(&maps[seg * 2], CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, AS, ws.ksp, M, ws.ksp / 4 * 3, 128, BM))) return rc;
-      if ((rc = make_map(&maps[seg * 2 + 1], CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, BS, ws.ksp, N, ws.ksp / 2, 128, bn))) return rc;
+      if ((rc = make_map(&maps[seg * 2], CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, AS, pl.ksp, M, pl.pitch[2], 128, BM))) return rc;
+      if ((rc = make_map(&maps[seg * 2 + 1], CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, BS, pl.ksp, N, pl.pitch[3], 128, bn))) return rc;
     } else {
-      if ((rc = make_map(&maps[seg * 2], CU_TENSOR_MAP_DATA_TYPE_UINT8, AO, ws.kop, M, ws.kop, 128, BM))) return rc;
-      if ((rc = make_map(&maps[seg * 2 + 1], CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, BO, ws.kop, N, ws.kop / 2, 128, bn))) return rc;
+      if ((rc = make_map(&maps[seg * 2], CU_TENSOR_MAP_DATA_TYPE_UINT8, AO, pl.kop, M, pl.pitch[4], 128, BM))) return rc;
+      if ((rc = make_map(&maps[seg * 2 + 1], CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, BO, pl.kop, N, pl.pitch[5], 128, bn))) return rc;
     }
   }
   if (use_pair) {
@@ -851,8 +873,22 @@ extern "C" int mg_matmul(const uint8_t* AN, const uint8_t* BN_, const uint8_t* A
                          const void* C_bf16, void* D_bf16, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
                          const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
                          void* workspace, size_t workspace_bytes, void* stream) {
-  return matmul_impl(false, AN, BN_, AS, BS, AO, BO, M, N, KN, KS, KO, C_bf16, D_bf16, ldd, SFAN, SFBN, SFAS, SFBS,
-                     SFAO, SFBO, workspace, workspace_bytes, stream);
+  return matmul_impl(false, AN, BN_, AS, BS, AO, BO, nullptr, M, N, KN, KS, KO, C_bf16, D_bf16, ldd, SFAN, SFBN, SFAS,
+                     SFBS, SFAO, SFBO, workspace, workspace_bytes, stream);
+}
+
+extern "C" int mg_matmul_pitched(const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
+                                 const uint8_t* AO, const uint8_t* BO, const size_t* pitches, int out_f32, int M, int N,
+                                 int KN, int KS, int KO, const void* C_bf16, void* D, int ldd, const uint8_t* SFAN,
+                                 const uint8_t* SFBN, const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO,
+                                 const uint8_t* SFBO, void* workspace, size_t workspace_bytes, void* stream) {
+  return matmul_impl(out_f32 != 0, AN, BN_, AS, BS, AO, BO, pitches, M, N, KN, KS, KO, C_bf16, D, ldd, SFAN, SFBN, SFAS,
+                     SFBS, SFAO, SFBO, workspace, workspace_bytes, stream);
+}
+
+extern "C" size_t mg_matmul_pitched_workspace_bytes(int M, int N, int KN, int KS, int KO, const size_t* pitches) {
+  if (M <= 0 || N <= 0 || KN < 0 || KS < 0 || KO < 0) return 0;
+  return make_plan(M, N, KN, KS, KO, pitches).total;
 }
 
 extern "C" int mg_matmul_f32(const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
@@ -860,8 +896,8 @@ extern "C" int mg_matmul_f32(const uint8_t* AN, const uint8_t* BN_, const uint8_
                              const void* C_bf16, float* D_f32, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
                              const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
                              void* workspace, size_t workspace_bytes, void* stream) {
-  return matmul_impl(true, AN, BN_, AS, BS, AO, BO, M, N, KN, KS, KO, C_bf16, D_f32, ldd, SFAN, SFBN, SFAS, SFBS,
-                     SFAO, SFBO, workspace, workspace_bytes, stream);
+  return matmul_impl(true, AN, BN_, AS, BS, AO, BO, nullptr, M, N, KN, KS, KO, C_bf16, D_f32, ldd, SFAN, SFBN, SFAS,
+                     SFBS, SFAO, SFBO, workspace, workspace_bytes, stream);
 }
 
 extern "C" int mg_matmul_fp4(const uint8_t* A, const uint8_t* B, int M, int N, int K, const void* C_bf16,
@@ -903,7 +939,7 @@ extern "C" int mg_matmul_static_ws(const uint8_t* AN, const uint8_t* BN_, const 
                                    const uint8_t* SFBN, const uint8_t* SFAS, const uint8_t* SFBS,
                                    const uint8_t* SFAO, const uint8_t* SFBO, void* stream) {
   if (M < 0 || N <= 0 || KN < 0 || KS < 0 || KO < 0) return MG_ERR_SHAPE;
-  const size_t need = plan_workspace(M, N, KS, KO).total;
+  const size_t need = make_plan(M, N, KN, KS, KO, nullptr).total;
   if (need > (size_t)MG_STATIC_WS_BYTES) return MG_ERR_WORKSPACE;  // beyond the built-in scratch
   int dev = 0;
   MG_CUDA_TRY(cudaGetDevice(&dev));
@@ -920,6 +956,6 @@ extern "C" int mg_matmul_static_ws(const uint8_t* AN, const uint8_t* BN_, const 
     }
     ws = g_static_ws_ptr[dev];
   }
-  return matmul_impl(false, AN, BN_, AS, BS, AO, BO, M, N, KN, KS, KO, C_bf16, D_bf16, ldd, SFAN, SFBN, SFAS, SFBS,
-                     SFAO, SFBO, ws, (size_t)MG_STATIC_WS_BYTES, stream);
+  return matmul_impl(false, AN, BN_, AS, BS, AO, BO, nullptr, M, N, KN, KS, KO, C_bf16, D_bf16, ldd, SFAN, SFBN, SFAS,
+                     SFBS, SFAO, SFBO, ws, (size_t)MG_STATIC_WS_BYTES, stream);
 }

@@ -292,8 +292,8 @@ int launch(const ReorderParams& p, int grid, size_t smem, cudaStream_t st) {
 }
 
 int reorder_quantize(bool weights, const void* X, int rows, int K, const int16_t* idx, int KN, int KS,
-                     int KO, uint8_t* o4, uint8_t* o6, uint8_t* o8, uint8_t* s4, uint8_t* s6, uint8_t* s8,
-                     void* stream) {
+                     int KO, uint8_t* o4, uint8_t* o6, uint8_t* o8, const size_t* pitches, uint8_t* s4, uint8_t* s6,
+                     uint8_t* s8, void* stream) {
   if (rows < 0 || K <= 0 || KN < 0 || KS < 0 || KO < 0 || KN + KS + KO != K) return MG_ERR_SHAPE;
   if ((KN | KS | KO) & 31) return MG_ERR_SHAPE;
   if (K > 32736) return MG_ERR_SHAPE;  // int16 index
@@ -314,9 +314,17 @@ int reorder_quantize(bool weights, const void* X, int rows, int K, const int16_t
   p.K = K;
   p.g4 = KN / 32;
   p.g46 = (KN + KS) / 32;
-  p.seg[0] = {o4, s4, (KN + 127) / 128, KN / 2};
-  p.seg[1] = {o6, s6, (KS + 127) / 128, weights ? KS / 2 : KS / 4 * 3};
-  p.seg[2] = {o8, s8, (KO + 127) / 128, weights ? KO / 2 : KO};
+  const size_t dense[3] = {(size_t)KN / 2, (size_t)(weights ? KS / 2 : KS / 4 * 3), (size_t)(weights ? KO / 2 : KO)};
+  const size_t align[3] = {16, (size_t)(weights ? 16 : 8), 16};
+  size_t pitch[3];
+  for (int i = 0; i < 3; ++i) {
+    pitch[i] = pitches ? pitches[i] : dense[i];
+    if (pitch[i] < dense[i] || pitch[i] > 0x7fffffffu) return MG_ERR_SHAPE;
+    if (pitch[i] % align[i]) return MG_ERR_ALIGN;
+  }
+  p.seg[0] = {o4, s4, (KN + 127) / 128, (int)pitch[0]};
+  p.seg[1] = {o6, s6, (KS + 127) / 128, (int)pitch[1]};
+  p.seg[2] = {o8, s8, (KO + 127) / 128, (int)pitch[2]};
 
   // Rows per stage: as many as fit twice (double buffering) beside the index, but no more than
   // half of a CTA's share so that its last stage is not mostly empty.  Then as many stages as
@@ -355,11 +363,24 @@ int reorder_quantize(bool weights, const void* X, int rows, int K, const int16_t
 extern "C" int mg_reorder_quantize_x(const void* X, int M, int K, const int16_t* idx, int KN, int KS, int KO,
                                      uint8_t* AN, uint8_t* AS, uint8_t* AO, uint8_t* SFAN, uint8_t* SFAS,
                                      uint8_t* SFAO, void* stream) {
-  return reorder_quantize(false, X, M, K, idx, KN, KS, KO, AN, AS, AO, SFAN, SFAS, SFAO, stream);
+  return reorder_quantize(false, X, M, K, idx, KN, KS, KO, AN, AS, AO, nullptr, SFAN, SFAS, SFAO, stream);
 }
 
 extern "C" int mg_reorder_quantize_w(const void* W, int N, int K, const int16_t* idx, int KN, int KS, int KO,
                                      uint8_t* BN, uint8_t* BS, uint8_t* BO, uint8_t* SFBN, uint8_t* SFBS,
                                      uint8_t* SFBO, void* stream) {
-  return reorder_quantize(true, W, N, K, idx, KN, KS, KO, BN, BS, BO, SFBN, SFBS, SFBO, stream);
+  return reorder_quantize(true, W, N, K, idx, KN, KS, KO, BN, BS, BO, nullptr, SFBN, SFBS, SFBO, stream);
+}
+
+extern "C" int mg_reorder_quantize_pitched(int weights, const void* X, int rows, int K, const int16_t* idx, int KN,
+                                           int KS, int KO, uint8_t* C4, uint8_t* C6, uint8_t* C8,
+                                           const size_t* pitches, uint8_t* SF4, uint8_t* SF6, uint8_t* SF8,
+                                           void* stream) {
+  return reorder_quantize(weights != 0, X, rows, K, idx, KN, KS, KO, C4, C6, C8, pitches, SF4, SF6, SF8, stream);
+}
+
+extern "C" size_t mg_code_pitch(int weights, int segment, int kseg) {
+  const int kp = (kseg + 127) / 128 * 128;
+  if (segment == 0 || weights) return (size_t)kp / 2;
+  return segment == 1 ? (size_t)kp / 4 * 3 : (size_t)kp;
 }

@@ -133,6 +133,34 @@ def test_segments_with_64_tails():
     _check(A, B, M, N, split)
 
 
+def test_dense_buffers_take_the_padded_copy_and_agree():
+    """Row-pitched buffers (what the quantisers return) are read in place; the reference's dense
+    buffers of a 64-tail segment go through the padded copy in the workspace.  Same result."""
+    import mixedgemm_b200 as mg
+    M, N, split = 384, 512, (8960, 4928, 448)
+    K = sum(split)
+    X = H.make_x(M, K, seed=8).cuda()
+    W = H.make_w(N, K, seed=9).cuda()
+    idx = H.reorder_index(X.cpu()).cuda()
+    A = mg.reorder_quantize_x(X, idx, *split, M, N)
+    B = mg.reorder_quantize_w(W, idx, *split, M, N)
+    assert not A[1].is_contiguous() and A[1].shape == (M, split[1] // 4 * 3)
+    Ad = mg.reorder_quantize_x(X, idx, *split, M, N, out=mg.alloc_quantized_x(M, *split, X.device, padded=False))
+    Bd = mg.reorder_quantize_w(W, idx, *split, M, N, out=mg.alloc_quantized_w(N, *split, X.device, padded=False))
+    assert Ad[1].is_contiguous()
+    for i in range(3):
+        assert torch.equal(A[i], Ad[i]) and torch.equal(B[i], Bd[i])
+    lib = __import__("mixedgemm_b200._capi", fromlist=["load"]).load()
+    assert lib.mg_matmul_workspace_bytes(M, N, *split) > 0
+    y0 = mg.matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+    y1 = mg.matmul(Ad[0], Bd[0], Ad[1], Bd[1], Ad[2], Bd[2], Ad[3], Bd[3], Ad[4], Bd[4], Ad[5], Bd[5])
+    y2 = mg.matmul(A[0], Bd[0], A[1], Bd[1], A[2], Bd[2], A[3], Bd[3], A[4], Bd[4], A[5], Bd[5])
+    torch.cuda.synchronize()
+    assert torch.equal(y0.view(torch.int16), y1.view(torch.int16))
+    assert torch.equal(y0.view(torch.int16), y2.view(torch.int16))
+    _check(Ad, Bd, M, N, split)
+
+
 def test_accumulate_into_c():
     M, N, split = 256, 256, (512, 256, 128)
     A, B = _quantise(M, N, sum(split), split, seed=6)

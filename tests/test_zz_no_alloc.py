@@ -22,8 +22,9 @@ def _operands(M, N, split, seed):
     X = H.make_x(M, K, seed=seed)
     W = H.make_w(N, K, seed=seed + 1)
     idx = H.reorder_index(X).cuda()
-    A = mg.reorder_quantize_x(X.cuda(), idx, KN, KS, KO, M, N)
-    B = mg.reorder_quantize_w(W.cuda(), idx, KN, KS, KO, M, N)
+    # the reference's dense layout: these are the buffers that need the padded copy, i.e. scratch
+    A = mg.reorder_quantize_x(X.cuda(), idx, KN, KS, KO, M, N, out=mg.alloc_quantized_x(M, KN, KS, KO, "cuda", padded=False))
+    B = mg.reorder_quantize_w(W.cuda(), idx, KN, KS, KO, M, N, out=mg.alloc_quantized_w(N, KN, KS, KO, "cuda", padded=False))
     return A, B
 
 
