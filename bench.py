@@ -242,10 +242,8 @@ class Job:
         self.mg.reorder_quantize_x(gr["X"], gr["idx"], KN, KS, KO, self.M, 0, out=gr["A"])
 
     def exchange_a(self, gr):
-        import torch.distributed as dist
-        for t in gr["A"]:
-            if t.numel():
-                dist.broadcast(t, src=0)
+        from mixedgemm_b200 import dist as mgd
+        mgd.broadcast_activations(gr["A"], src=0)
 
     def gemms(self, gr):
         A = gr["A"]

@@ -1,0 +1,86 @@
+"""world_size-2 CPU (gloo) test of the N-sharded path's host logic: shard ranges, slicing of the
+swizzled scale buffers, broadcast of quantised activations, gather of output shards.  The compute
+on each rank is the CPU oracle, so the check is on the bookkeeping: shards recombine to exactly
+the unsharded result."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import mx_oracle as orc
+from tests import helpers as H
+
+M, N, SPLIT = 48, 512, (256, 192, 64)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, ret):
+    from mixedgemm_b200 import dist as mgd
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        KN, KS, KO = SPLIT
+        K = sum(SPLIT)
+        X = H.make_x(M, K, seed=3)
+        W = H.make_w(N, K, seed=4)
+        idx = H.reorder_index(X).numpy()
+        # every rank holds the full quantised weight here only to cut its shard out of it
+        Bfull = [torch.from_numpy(np.ascontiguousarray(a)) for a in H.oracle_outputs(H.bits(W), idx, KN, KS, KO, True)]
+        Bl = mgd.shard_weights(Bfull, N, KN, KS, KO, world, rank)
+        # rank 0 quantises, the others receive
+        if rank == 0:
+            A = [torch.from_numpy(np.ascontiguousarray(a)) for a in H.oracle_outputs(H.bits(X), idx, KN, KS, KO)]
+        else:
+            A = [torch.zeros((M, KN // 2), dtype=torch.uint8), torch.zeros((M, KS // 4 * 3), dtype=torch.uint8),
+                 torch.zeros((M, KO), dtype=torch.uint8)] + [torch.zeros(orc.sf_bytes(M, k), dtype=torch.uint8)
+                                                              for k in SPLIT]
+        mgd.broadcast_activations(A, src=0)
+        r0, n = mgd.shard_range(N, world, rank)
+        Yl = orc.gemm_f64([t.numpy() for t in A], [t.numpy() for t in Bl], M, n, KN, KS, KO)
+        Y = mgd.all_gather_output(torch.from_numpy(Yl), world)
+        if rank == 0:
+            Yref = orc.gemm_f64([t.numpy() for t in A], [t.numpy() for t in Bfull], M, N, KN, KS, KO)
+            ret["equal"] = bool(np.array_equal(Y.numpy(), Yref))
+            ret["shape"] = tuple(Y.shape)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_sharding_recombines_exactly():
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert ret["shape"] == (M, N)
+    assert ret["equal"]
+
+
+def test_shard_helpers():
+    from mixedgemm_b200 import dist as mgd
+    assert mgd.shard_range(1024, 8, 3) == (384, 128)
+    with pytest.raises(ValueError):
+        mgd.shard_range(1024, 3, 0)
+    with pytest.raises(ValueError):
+        mgd.shard_range(512, 8, 0)  # 64-row shards would split scale atoms
+    # scale slices: rows [256, 512) of a 512-row buffer, K segment of 448 (4 atoms per row block)
+    sf = torch.arange(4 * 4 * 512, dtype=torch.int32)
+    s = mgd.sf_shard(sf, 512, 448, 2, 1)
+    assert s[0] == 2 * 4 * 512 and s.numel() == 2 * 4 * 512
+    # and the slice holds exactly the scales of those rows
+    full = np.arange(orc.sf_bytes(512, 448))
+    r = np.arange(256, 512)[:, None]
+    kb = np.arange(448 // 32)[None, :]
+    want = full[orc.sf_offset(r, kb, 448)]
+    got = mgd.sf_shard(torch.from_numpy(full), 512, 448, 2, 1).numpy()[orc.sf_offset(r - 256, kb, 448)]
+    assert np.array_equal(got, want)
