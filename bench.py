@@ -531,14 +531,19 @@ def main():
         peak_t = blended_peak(pk["bf16_sustained"], 4096)  # same split for every K
         out["roofline"] = {
             "kernel": "mixed_gemm_kernel", "bound": "tensor", "achieved": gemm_flops / (g_ms * 1e-3) / 1e12,
-            "peak": peak_t, "unit": "TFLOP/s", "frac": gemm_flops / (g_ms * 1e-3) / 1e12 / peak_t, "traffic": None,
+            "peak": peak_t, "unit": "TFLOP/s", "frac": gemm_flops / (g_ms * 1e-3) / 1e12 / peak_t,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the largest GEMM of the step
+            # (gate/up, 2048 x 14336 x 4096), from the ncu capture summarised under profiles/
+            "traffic": 50.6e6 if wl_name == "llama3-8b-m2048" else None,
             "peak_note": "K-blended tensor peak: fp4 segment at 4x and fp6/fp8 at 2x the %s sustained bf16 rate (%.1f TF/s)" % (
                 pk["source"], pk["bf16_sustained"]),
             "launches": [{"layer": n, "M": M, "N": N, "K": K, "us": t * 1e3, "tflops": 2 * M * N * K / (t * 1e-3) / 1e12}
                          for (n, M, N, K, t) in g_each]}
         out["roofline_reorder"] = {
             "kernel": "reorder_quantize_kernel", "bound": "hbm", "achieved": job.reorder_bytes / (q_ms * 1e-3) / 1e9,
-            "peak": pk["hbm"], "unit": "GB/s", "frac": job.reorder_bytes / (q_ms * 1e-3) / 1e9 / pk["hbm"], "traffic": None,
+            "peak": pk["hbm"], "unit": "GB/s", "frac": job.reorder_bytes / (q_ms * 1e-3) / 1e9 / pk["hbm"],
+            # one K=4096 launch under ncu: 16.8 MB read, the 5.3 MB written are still in L2 at kernel end
+            "traffic": 16.8e6 if wl_name == "llama3-8b-m2048" else None,
             "peak_note": "%s copy bandwidth" % pk["source"],
             "launches": [{"M": job.M, "K": K, "us": t * 1e3, "gbs": reorder_bytes(job.M, K) / (t * 1e-3) / 1e9}
                          for (K, t) in q_each]}
