@@ -382,7 +382,9 @@ def main():
     device = torch.device("cuda", local_rank)
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+        # a short collective timeout: a rank that stalls must end the run, not hold the GPUs
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=90))
 
     def sync():
         if world > 1:
@@ -394,7 +396,9 @@ def main():
     pk = peaks()
 
     # ---- whole-step timing, inputs resident in HBM
-    use_graph = not a.no_graph
+    # NCCL collectives are launched eagerly: replaying them from a captured graph next to eager
+    # collectives on the same communicator stalled on this pool, so multi-rank runs do not capture
+    use_graph = not a.no_graph and world == 1
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
         for _ in range(a.warmup):
