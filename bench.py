@@ -215,7 +215,7 @@ class Job:
             Xb = X.to(torch.bfloat16)
             del X
             idx = torch.sort(Xb.float().abs().amax(0), stable=True).indices.to(torch.int16)
-            A = mg.alloc_quantized_x(M, KN, KS, KO, device)
+            A = mg.alloc_quantized_x(M, KN, KS, KO, device, one_buffer=world > 1)
             Ls = []
             for li, (name, N) in enumerate(layers):
                 assert N % (128 * world) == 0, "every shard must be a multiple of 128 columns"
@@ -305,6 +305,9 @@ def single_kernel(a):
                                      A[5], Bs[i][5], out=Ys[i]) for i in range(nb)]
         work, unit, bound = 2.0 * M * N * K / 1e12, "TFLOP/s", "tensor"
         peak = blended_peak(pk["bf16"], K)
+        if M <= 128:  # decode shapes are bound by reading the weights once
+            work = (wbytes + M * (KN // 2 + KS // 4 * 3 + KO + K // 32) + 2 * M * N) / 1e9
+            unit, bound, peak = "GB/s", "hbm", pk["hbm"]
     for i in range(max(a.warmup, 1)):
         fns[i % nb]()
     torch.cuda.synchronize()

@@ -43,16 +43,33 @@ def _alloc_codes(rows, logical, pitch, device):
     return buf[:, :logical] if pitch != logical else buf
 
 
-def alloc_quantized_x(M, KN, KS, KO, device, padded=True):
+def alloc_quantized_x(M, KN, KS, KO, device, padded=True, one_buffer=False):
     """Output buffers of reorder_quantize_x with the reference's shapes (bindings.cpp:88-93).
     With padded=True the code tensors are row-pitched views (same shape, same contents) whose pitch
-    the GEMM can read in place even when a segment is only a multiple of 64."""
+    the GEMM can read in place even when a segment is only a multiple of 64.  With one_buffer=True
+    all six are carved out of a single allocation, so that one transfer moves them together."""
     lib = _capi.load()
     u8 = dict(dtype=torch.uint8, device=device)
     logical = (KN // 2, KS // 4 * 3, KO)
     pitch = [lib.mg_code_pitch(0, i, k) if padded else l for i, (k, l) in enumerate(zip((KN, KS, KO), logical))]
-    return tuple(_alloc_codes(M, l, p, device) for l, p in zip(logical, pitch)) + tuple(
-        torch.empty(max(lib.mg_sf_bytes(M, k), (M // 128 + 1) * 128 * k // 32), **u8) for k in (KN, KS, KO))
+    sf_len = [max(lib.mg_sf_bytes(M, k), (M // 128 + 1) * 128 * k // 32) for k in (KN, KS, KO)]
+    if not one_buffer:
+        return tuple(_alloc_codes(M, l, p, device) for l, p in zip(logical, pitch)) + tuple(
+            torch.empty(n, **u8) for n in sf_len)
+    sizes = [M * p for p in pitch] + sf_len
+    offs, off = [], 0
+    for n in sizes:
+        offs.append(off)
+        off += (n + 1023) // 1024 * 1024
+    buf = torch.empty(off + 1024, **u8)
+    base = (-buf.data_ptr()) % 1024
+    out = []
+    for i in range(3):
+        v = buf[base + offs[i]: base + offs[i] + sizes[i]].view(M, pitch[i])
+        out.append(v[:, :logical[i]] if pitch[i] != logical[i] else v)
+    for i in range(3):
+        out.append(buf[base + offs[3 + i]: base + offs[3 + i] + sizes[3 + i]])
+    return tuple(out)
 
 
 def alloc_quantized_w(N, KN, KS, KO, device, padded=True):

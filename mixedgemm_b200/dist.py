@@ -38,10 +38,18 @@ def shard_weights(B, N, KN, KS, KO, world, rank):
 
 def broadcast_activations(A, src=0, group=None):
     """Broadcast the six quantised-activation buffers from `src` into every rank's own memory.
-    Row-pitched views are sent with their padding (one contiguous transfer per buffer)."""
-    for t in A:
-        if t.numel() == 0:
-            continue
+    Buffers carved from one allocation (alloc_quantized_x(one_buffer=True)) go as a single
+    transfer; otherwise each buffer is sent on its own, row-pitched views with their padding."""
+    live = [t for t in A if t.numel()]
+    if not live:
+        return
+    storages = {t.untyped_storage().data_ptr() for t in live}
+    if len(storages) == 1 and len(live) > 1:
+        st = live[0].untyped_storage()
+        flat = torch.empty(0, dtype=torch.uint8, device=live[0].device).set_(st, 0, (st.nbytes(),))
+        dist.broadcast(flat, src=src, group=group)
+        return
+    for t in live:
         base = t
         if not t.is_contiguous():
             # a pitched view [rows, logical] of a [rows, pitch] buffer: send the whole buffer

@@ -47,6 +47,18 @@ def _worker(rank, world, port, ret):
                  torch.zeros((M, KO), dtype=torch.uint8)] + [torch.zeros(orc.sf_bytes(M, k), dtype=torch.uint8)
                                                               for k in SPLIT]
         mgd.broadcast_activations(A, src=0)
+        # the same six buffers carved from one allocation travel as one transfer
+        sizes = [t.numel() for t in A]
+        flat = torch.zeros(sum(sizes), dtype=torch.uint8)
+        views, o = [], 0
+        for t_, n_ in zip(A, sizes):
+            views.append(flat[o:o + n_].view(t_.shape))
+            o += n_
+        if rank == 0:
+            for v, t_ in zip(views, A):
+                v.copy_(t_)
+        mgd.broadcast_activations(views, src=0)
+        ret["one_buffer_%d" % rank] = all(bool(torch.equal(v, t_)) for v, t_ in zip(views, A))
         r0, n = mgd.shard_range(N, world, rank)
         Yl = orc.gemm_f64([t.numpy() for t in A], [t.numpy() for t in Bl], M, n, KN, KS, KO)
         Y = mgd.all_gather_output(torch.from_numpy(Yl), world)
@@ -64,6 +76,7 @@ def test_two_rank_sharding_recombines_exactly():
     mp.spawn(_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
     assert ret["shape"] == (M, N)
     assert ret["equal"]
+    assert ret["one_buffer_0"] and ret["one_buffer_1"]
 
 
 def test_shard_helpers():
