@@ -1,4 +1,5 @@
 // Status, device queries and small helpers of the C ABI.
+#include <cstdlib>
 #include <mutex>
 
 #include "mg_common.h"
@@ -17,6 +18,14 @@ std::mutex g_mu;
 }  // namespace
 
 namespace mg {
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("MG_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
 
 int note_cuda_error(cudaError_t e) {
   tl_last_cuda_error = (int)e;

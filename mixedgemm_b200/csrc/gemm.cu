@@ -135,10 +135,12 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
     ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
     ptx::tmem_relinquish();
   }
+  ptx::grid_dep_launch_dependents();
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  ptx::grid_dep_wait();  // the prologue above touched no global memory
 
   const int total_tiles = p.tiles_m * p.tiles_n;
 
@@ -409,10 +411,12 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), kTmemCols);
     ptx::tmem_relinquish_pair();
   }
+  ptx::grid_dep_launch_dependents();
   ptx::tc_fence_before();
   ptx::cluster_sync();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  ptx::grid_dep_wait();  // the prologue above touched no global memory
 
   const int tiles_m2 = (p.M + 255) / 256;
   const int total_tiles = tiles_m2 * (p.N / 256);
@@ -741,8 +745,8 @@ int launch_gemm(const GemmParams& p, const CUtensorMap* maps, int sms, cudaStrea
   MG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, kThreads, C::SMEM, st>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]);
-  MG_CUDA_TRY(cudaGetLastError());
+  MG_CUDA_TRY(mg::launch_kernel(kern, dim3(grid), dim3(kThreads), C::SMEM, st, p, maps[0], maps[1], maps[2], maps[3],
+                                maps[4], maps[5]));
   return MG_OK;
 }
 
@@ -854,13 +858,13 @@ static int matmul_impl(bool f32_out, const uint8_t* AN, const uint8_t* BN_, cons
     if (variant == 0) {
       using PC = PairCfgT<4, 4>;
       MG_CUDA_TRY(cudaFuncSetAttribute(mixed_gemm_pair_kernel<PC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PC::SMEM));
-      mixed_gemm_pair_kernel<PC><<<2 * clusters, PC::THREADS, PC::SMEM, st>>>(p, maps[0], maps[1], maps[2], maps[3],
-                                                                            maps[4], maps[5], mapD);
+      MG_CUDA_TRY(mg::launch_kernel(mixed_gemm_pair_kernel<PC>, dim3(2 * clusters), dim3(PC::THREADS), PC::SMEM, st, p,
+                                    maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], mapD));
     } else {
       using PC = PairCfgT<5, 2>;
       MG_CUDA_TRY(cudaFuncSetAttribute(mixed_gemm_pair_kernel<PC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PC::SMEM));
-      mixed_gemm_pair_kernel<PC><<<2 * clusters, PC::THREADS, PC::SMEM, st>>>(p, maps[0], maps[1], maps[2], maps[3],
-                                                                            maps[4], maps[5], mapD);
+      MG_CUDA_TRY(mg::launch_kernel(mixed_gemm_pair_kernel<PC>, dim3(2 * clusters), dim3(PC::THREADS), PC::SMEM, st, p,
+                                    maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], mapD));
     }
     MG_CUDA_TRY(cudaGetLastError());
     return MG_OK;

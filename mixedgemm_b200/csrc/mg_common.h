@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #include "mixedgemm_c.h"
 
 namespace mg {
@@ -27,6 +29,28 @@ int device_info(DeviceInfo* out);
 // Address of the device-side error word (one per device, set by kernels whose bounded
 // waits expire).  Resolved with cudaGetSymbolAddress in capi.cu.
 int device_status_word(int** dev_ptr);
+
+// True unless MG_PDL=0: kernels are launched with programmatic stream serialisation, so that a
+// kernel's prologue (barrier set-up, TMEM allocation, descriptor prefetch) overlaps the tail of
+// the kernel before it; every kernel waits (griddepcontrol.wait) before it touches global memory.
+bool pdl_enabled();
+
+// <<<grid, block, smem, stream>>> with the programmatic-dependent-launch attribute when enabled.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                          Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 static inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 

@@ -212,11 +212,7 @@ __global__ void __launch_bounds__(kThreads, 1) reorder_quantize_kernel(const Reo
   const uint32_t bar0 = ptx::smem_u32(tail);
   volatile int* stop = reinterpret_cast<volatile int*>(tail + 16 * 8);
 
-  for (int i = tid; i < K; i += kThreads) {
-    unsigned v = (uint16_t)p.idx[i];
-    v = min(v, (unsigned)(K - 1));
-    idx2[i] = (uint16_t)(v * 2);
-  }
+  ptx::grid_dep_launch_dependents();
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       ptx::mbar_init(bar0 + 8 * s, 1);                     // full: one expect_tx arrival + bytes
@@ -226,6 +222,7 @@ __global__ void __launch_bounds__(kThreads, 1) reorder_quantize_kernel(const Reo
     ptx::fence_mbar_init();
   }
   __syncthreads();
+  ptx::grid_dep_wait();  // nothing before this line reads or writes global memory
 
   // This CTA's contiguous share of the rows, walked in stages of up to R rows.
   const int row_begin = (int)((long long)p.rows * blockIdx.x / gridDim.x);
@@ -251,6 +248,13 @@ __global__ void __launch_bounds__(kThreads, 1) reorder_quantize_kernel(const Reo
     }
   } else {
     // ---------------------------------------------------------------- consumers
+    // the consumers bring the index in while the producer's first rows are already in flight
+    for (int i = tid; i < K; i += kConsumers) {
+      unsigned v = (uint16_t)p.idx[i];
+      v = min(v, (unsigned)(K - 1));
+      idx2[i] = (uint16_t)(v * 2);
+    }
+    ptx::named_barrier_sync(1, kConsumers);
     const int r = tid % R;          // kConsumers is a multiple of R: a thread keeps its row
     const int g0 = tid / R;
     constexpr int kGStep = kConsumers / R;
@@ -286,8 +290,7 @@ template <int R, bool WEIGHTS>
 int launch(const ReorderParams& p, int grid, size_t smem, cudaStream_t st) {
   auto kern = reorder_quantize_kernel<R, WEIGHTS>;
   if (smem > 48 * 1024) MG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<grid, kThreads, smem, st>>>(p);
-  MG_CUDA_TRY(cudaGetLastError());
+  MG_CUDA_TRY(mg::launch_kernel(kern, dim3(grid), dim3(kThreads), smem, st, p));
   return MG_OK;
 }
 
