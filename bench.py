@@ -231,8 +231,8 @@ class Job:
                 self.flops_local += 2 * M * Nl * K
                 self.flops_total += 2 * M * N * K
                 self.gemm_shapes.append((M, Nl, K))
-                self.n_kernels += 1  # row-pitched buffers: no padded copy before the GEMM
-            self.n_kernels += 1
+            grouped = M > 128 and len(layers) <= 4 and all((N // world) % 256 == 0 for (_, N) in layers)
+            self.n_kernels += 1 + (1 if grouped else len(layers))  # the quantiser + one or several GEMM launches
             self.reorder_bytes += reorder_bytes(M, K)
             self.groups.append(dict(K=K, split=(KN, KS, KO), X=Xb, idx=idx, A=A, layers=Ls))
         torch.cuda.synchronize()
@@ -246,9 +246,8 @@ class Job:
         mgd.broadcast_activations(gr["A"], src=0)
 
     def gemms(self, gr):
-        A = gr["A"]
-        for name, Nl, B, Y in gr["layers"]:
-            self.mg.matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5], out=Y)
+        # weights that consume the same activation go out as one grouped launch where the kernel takes them
+        self.mg.matmul_group(gr["A"], [B for (_, _, B, _) in gr["layers"]], outs=[Y for (_, _, _, Y) in gr["layers"]])
 
     def step(self):
         for gr in self.groups:
@@ -459,13 +458,11 @@ def main():
                     job.quantize(gr)
                     e1.record()
                     marks.append((("q", gi), e0, e1))
-                    A = gr["A"]
-                    for li, (name, Nl, B, Y) in enumerate(gr["layers"]):
-                        e0, e1 = ev(), ev()
-                        e0.record()
-                        job.mg.matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5], out=Y)
-                        e1.record()
-                        marks.append((("g", gi, li), e0, e1))
+                    e0, e1 = ev(), ev()
+                    e0.record()
+                    job.gemms(gr)
+                    e1.record()
+                    marks.append((("g", gi), e0, e1))
             torch.cuda.synchronize()
             acc = {}
             for key, e0, e1 in marks:
@@ -473,9 +470,10 @@ def main():
             for gi, gr in enumerate(job.groups):
                 q_each.append((gr["K"], acc[("q", gi)]))
                 q_ms += acc[("q", gi)]
-                for li, (name, Nl, B, Y) in enumerate(gr["layers"]):
-                    g_each.append((name, job.M, Nl, gr["K"], acc[("g", gi, li)]))
-                    g_ms += acc[("g", gi, li)]
+                names = "+".join(n for (n, _, _, _) in gr["layers"])
+                Nsum = sum(Nl for (_, Nl, _, _) in gr["layers"])
+                g_each.append((names, job.M, Nsum, gr["K"], acc[("g", gi)]))
+                g_ms += acc[("g", gi)]
 
         # ---- end to end: activations from pinned host memory, results back to pinned host memory
         hX = [gr["X"].cpu().pin_memory() for gr in job.groups]

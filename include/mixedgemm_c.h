@@ -134,6 +134,23 @@ int mg_matmul_pitched(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, c
                       const uint8_t* SFBO, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Several weight matrices that consume the same quantised activation (q/k/v; gate/up) in ONE
+ * launch: D[j] = bf16(A * B[j]^T), j < nprob <= 4.  The reference calls matmul_host once per weight
+ * (main.py:59 per layer); sharing the launch lets small projections fill SMs that a large one
+ * leaves idle in its last wave.  Restrictions: M > 128, every N[j] a multiple of 256, bf16 output,
+ * and every code buffer row-pitched so that it is read in place (mg_code_pitch) - otherwise
+ * MG_ERR_SHAPE / MG_ERR_ALIGN is returned and the caller issues mg_matmul per weight instead.
+ *   pitches_a[3] = {AN, AS, AO};  pitches_b[3*j + s] = pitch of weight j, segment s
+ *   BN/BS/BO/SFBN/SFBS/SFBO/D/N/ldd are arrays of nprob entries.  Results equal mg_matmul's bit for bit.
+ */
+int mg_matmul_group_pitched(int nprob, const uint8_t* AN, const uint8_t* AS, const uint8_t* AO,
+                            const size_t* pitches_a, const uint8_t* const* BN, const uint8_t* const* BS,
+                            const uint8_t* const* BO, const size_t* pitches_b, int M, const int* N, int KN, int KS,
+                            int KO, void* const* D_bf16, const int* ldd, const uint8_t* SFAN, const uint8_t* SFAS,
+                            const uint8_t* SFAO, const uint8_t* const* SFBN, const uint8_t* const* SFBS,
+                            const uint8_t* const* SFBO, void* stream);
+
+/*
  * Same product with the fp32 accumulator written unrounded: D_f32 [M,N] float, pitch `ldd`
  * elements (ldd % 4 == 0).  The reference has no such output (its GEMMs write bf16,
  * src/fp4.cu:175-179); it exists so that the accumulation can be checked against a

@@ -173,6 +173,38 @@ def matmul(AN, BN, AS, BS, AO, BO, SFAN, SFBN, SFAS, SFBS, SFAO, SFBO, out=None,
     return D
 
 
+def matmul_group(A, Bs, outs=None):
+    """Products of one quantised activation A = (AN, AS, AO, SFAN, SFAS, SFAO) with several quantised
+    weights Bs = [(BN, BS, BO, SFBN, SFBS, SFBO), ...] (q/k/v, gate/up) in one launch where the
+    grouped kernel applies, otherwise one matmul per weight.  Returns the list of [M, N_j] bf16 tensors."""
+    import ctypes
+    lib = _capi.load()
+    M = A[0].size(0)
+    KN, KS, KO = A[0].size(1) * 2, A[1].size(1) * 4 // 3, A[2].size(1)
+    dev = A[0].device
+    n = len(Bs)
+    Ns = [B[0].size(0) for B in Bs]
+    if outs is None:
+        outs = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for N in Ns]
+    st = 1
+    if 1 <= n <= 4 and all(o.dtype == torch.bfloat16 and o.stride(1) == 1 for o in outs):
+        _check_codes(tuple(A[:3]) + tuple(t for B in Bs for t in B[:3]), "matmul_group")
+        vp = lambda ts: (ctypes.c_void_p * n)(*[_ptr(t) for t in ts])
+        pb = (ctypes.c_size_t * (3 * n))(*[B[s].stride(0) if B[s].size(1) else 0 for B in Bs for s in range(3)])
+        with torch.cuda.device(dev):
+            st = lib.mg_matmul_group_pitched(
+                n, _ptr(A[0]), _ptr(A[1]), _ptr(A[2]), _pitches(A[:3]), vp([B[0] for B in Bs]),
+                vp([B[1] for B in Bs]), vp([B[2] for B in Bs]), pb, M, (ctypes.c_int * n)(*Ns), KN, KS, KO, vp(outs),
+                (ctypes.c_int * n)(*[o.stride(0) for o in outs]), _ptr(A[3]), _ptr(A[4]), _ptr(A[5]),
+                vp([B[3] for B in Bs]), vp([B[4] for B in Bs]), vp([B[5] for B in Bs]), _stream())
+    if st in (1, 3):  # shape or pitch the grouped kernel does not take: one launch per weight
+        for B, o in zip(Bs, outs):
+            matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5], out=o)
+    else:
+        _capi.check(st, "matmul_group")
+    return outs
+
+
 def device_status():
     """Reads and clears the device error word (non-zero after a kernel gave up on a wait)."""
     import ctypes

@@ -50,6 +50,17 @@ struct GemmParams {
   int* status;
   uint32_t tx_a[3], tx_b[3];  // bytes one A / B tile load of the segment signals
   int dbg;  // timing experiments only (MG_GEMM_DEBUG): 1 = no MMAs, 2 = no loads, 4 = no stores
+  // CTA-pair kernel only: up to four weight matrices that share the activation ("fused N": q/k/v,
+  // gate/up).  Problem j owns pair tiles [tile_end[j-1], tile_end[j]) and its own scales / output.
+  int nprob;
+  int tile_end[4];
+  const uint8_t* sfb_g[4][3];
+};
+
+constexpr int kMaxGroup = 4;
+struct GroupMaps {
+  CUtensorMap b[kMaxGroup][3];  // weight codes per problem and K segment
+  CUtensorMap d[kMaxGroup];     // outputs
 };
 
 // Bounded mbarrier wait.  Control flow stays warp-uniform: when the limit expires the lane
@@ -367,9 +378,8 @@ struct PairCfgT {
 template <class C>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C::THREADS, 1)
 mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
-                       const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmA1,
-                       const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmA2,
-                       const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmD) {
+                       const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
+                       const __grid_constant__ GroupMaps gm) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // staging first, then the stage ring, then barriers
@@ -399,12 +409,14 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     *stop = 0;
     ptx::fence_mbar_init();
     ptx::prefetch_tmap(&tmA0);
-    ptx::prefetch_tmap(&tmB0);
     ptx::prefetch_tmap(&tmA1);
-    ptx::prefetch_tmap(&tmB1);
     ptx::prefetch_tmap(&tmA2);
-    ptx::prefetch_tmap(&tmB2);
-    ptx::prefetch_tmap(&tmD);
+    for (int j = 0; j < p.nprob; ++j) {
+      ptx::prefetch_tmap(&gm.b[j][0]);
+      ptx::prefetch_tmap(&gm.b[j][1]);
+      ptx::prefetch_tmap(&gm.b[j][2]);
+      ptx::prefetch_tmap(&gm.d[j]);
+    }
   }
   ptx::cluster_sync();  // both CTAs' barriers exist before anything arrives on them
   if (warp == 1) {
@@ -419,8 +431,17 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
   ptx::grid_dep_wait();  // the prologue above touched no global memory
 
   const int tiles_m2 = (p.M + 255) / 256;
-  const int total_tiles = tiles_m2 * (p.N / 256);
+  const int total_tiles = p.tile_end[p.nprob - 1];
   const int first_tile = (int)ptx::cluster_id_x(), tile_step = (int)ptx::nclusters_x();
+  // pair tile t -> (problem, 256-row block, 256-column block of that problem); rows vary fastest
+  auto locate = [&](int t, int& prob, int& m_pt, int& n_tile) {
+    prob = 0;
+    int start = 0;
+    while (prob + 1 < p.nprob && t >= p.tile_end[prob]) start = p.tile_end[prob++];
+    const int lt = t - start;
+    m_pt = lt % tiles_m2;
+    n_tile = lt / tiles_m2;
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -428,20 +449,21 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     int stage = 0;
     uint32_t phase = 0;
     for (int t = first_tile; t < total_tiles; t += tile_step) {
-      const int m_pt = t % tiles_m2, n_tile = t / tiles_m2;
+      int prob, m_pt, n_tile;
+      locate(t, prob, m_pt, n_tile);
       const int m_row0 = m_pt * 256 + (int)rank * 128, n_row0 = n_tile * 256 + (int)rank * 128;
 #pragma unroll 1
       for (int seg = 0; seg < 3; ++seg) {
         const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
         const CUtensorMap* ta = seg == 0 ? &tmA0 : (seg == 1 ? &tmA1 : &tmA2);
-        const CUtensorMap* tb = seg == 0 ? &tmB0 : (seg == 1 ? &tmB1 : &tmB2);
+        const CUtensorMap* tb = &gm.b[prob][seg];
         const uint32_t tx_ab = seg == 0 ? p.tx_a[0] + p.tx_b[0]
                                         : (seg == 1 ? p.tx_a[1] + p.tx_b[1] : p.tx_a[2] + p.tx_b[2]);
         // a CTA whose 128 rows lie wholly beyond M reads the last real row block's scales (its
         // accumulator rows are never stored), so that no copy leaves the scale buffer
         const int row_blk = min(m_pt * 2 + (int)rank, (p.M + 127) / 128 - 1);
         const uint8_t* sfa_row = sp.sfa + (size_t)row_blk * sp.katoms * 512;
-        const uint8_t* sfb_row = sp.sfb + (size_t)(n_tile * 2) * sp.katoms * 512;
+        const uint8_t* sfb_row = p.sfb_g[prob][seg] + (size_t)(n_tile * 2) * sp.katoms * 512;
 #pragma unroll 1
         for (int s = 0; s < sp.nstages; ++s) {
           wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, 1);
@@ -560,7 +582,8 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     const bool issuer = warp == 3 && lane == 0;
     int it = 0;
     for (int t = first_tile; t < total_tiles; t += tile_step, ++it) {
-      const int m_pt = t % tiles_m2, n_tile = t / tiles_m2;
+      int prob, m_pt, n_tile;
+      locate(t, prob, m_pt, n_tile);
       wait_parity(tfull_bar, (uint32_t)it & 1u, stop, p.status, 8);
       __syncwarp();
       ptx::tc_fence_after();
@@ -595,7 +618,7 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
         ptx::named_barrier_sync(1, 128);
         const int m0 = m_pt * 256 + (int)rank * 128;
         if (issuer) {
-          if (m0 < p.M && !*stop && !(p.dbg & 4)) ptx::tma_store_2d(&tmD, n_tile * 256 + j * 64, m0, slot_addr);
+          if (m0 < p.M && !*stop && !(p.dbg & 4)) ptx::tma_store_2d(&gm.d[prob], n_tile * 256 + j * 64, m0, slot_addr);
           ptx::bulk_commit_group();  // one group per panel, also when nothing was stored
         }
       }
@@ -750,6 +773,26 @@ int launch_gemm(const GemmParams& p, const CUtensorMap* maps, int sms, cudaStrea
   return MG_OK;
 }
 
+int launch_pair(const GemmParams& p, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& a2,
+                const GroupMaps& gm, int sms, cudaStream_t st) {
+  const int tiles = p.tile_end[p.nprob - 1];
+  const int clusters = tiles < sms / 2 ? tiles : sms / 2;
+  int variant = 1;
+  if (const char* e = std::getenv("MG_GEMM_PAIR_VARIANT")) variant = std::atoi(e);
+  if (variant == 0) {
+    using PC = PairCfgT<4, 4>;
+    MG_CUDA_TRY(cudaFuncSetAttribute(mixed_gemm_pair_kernel<PC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PC::SMEM));
+    MG_CUDA_TRY(mg::launch_kernel(mixed_gemm_pair_kernel<PC>, dim3(2 * clusters), dim3(PC::THREADS), PC::SMEM, st, p, a0,
+                                  a1, a2, gm));
+  } else {
+    using PC = PairCfgT<5, 2>;
+    MG_CUDA_TRY(cudaFuncSetAttribute(mixed_gemm_pair_kernel<PC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PC::SMEM));
+    MG_CUDA_TRY(mg::launch_kernel(mixed_gemm_pair_kernel<PC>, dim3(2 * clusters), dim3(PC::THREADS), PC::SMEM, st, p, a0,
+                                  a1, a2, gm));
+  }
+  return MG_OK;
+}
+
 }  // namespace
 
 extern "C" size_t mg_matmul_workspace_bytes(int M, int N, int KN, int KS, int KO) {
@@ -849,25 +892,15 @@ static int matmul_impl(bool f32_out, const uint8_t* AN, const uint8_t* BN_, cons
     }
   }
   if (use_pair) {
-    CUtensorMap mapD;
-    if ((rc = make_map(&mapD, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D_bf16, N, M, (uint64_t)ldd * 2, 64, 128))) return rc;
-    const int tiles = ((M + 255) / 256) * (N / 256);
-    const int clusters = tiles < di.sm_count / 2 ? tiles : di.sm_count / 2;
-    int variant = 1;
-    if (const char* e = std::getenv("MG_GEMM_PAIR_VARIANT")) variant = std::atoi(e);
-    if (variant == 0) {
-      using PC = PairCfgT<4, 4>;
-      MG_CUDA_TRY(cudaFuncSetAttribute(mixed_gemm_pair_kernel<PC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PC::SMEM));
-      MG_CUDA_TRY(mg::launch_kernel(mixed_gemm_pair_kernel<PC>, dim3(2 * clusters), dim3(PC::THREADS), PC::SMEM, st, p,
-                                    maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], mapD));
-    } else {
-      using PC = PairCfgT<5, 2>;
-      MG_CUDA_TRY(cudaFuncSetAttribute(mixed_gemm_pair_kernel<PC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PC::SMEM));
-      MG_CUDA_TRY(mg::launch_kernel(mixed_gemm_pair_kernel<PC>, dim3(2 * clusters), dim3(PC::THREADS), PC::SMEM, st, p,
-                                    maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], mapD));
+    GroupMaps gm;
+    if ((rc = make_map(&gm.d[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D_bf16, N, M, (uint64_t)ldd * 2, 64, 128))) return rc;
+    for (int seg = 0; seg < 3; ++seg) {
+      gm.b[0][seg] = maps[seg * 2 + 1];
+      p.sfb_g[0][seg] = p.seg[seg].sfb;
     }
-    MG_CUDA_TRY(cudaGetLastError());
-    return MG_OK;
+    p.nprob = 1;
+    p.tile_end[0] = pair_tiles;
+    return launch_pair(p, maps[0], maps[2], maps[4], gm, di.sm_count, st);
   }
   return bn == 256 ? launch_gemm<256>(p, maps, di.sm_count, st) : launch_gemm<128>(p, maps, di.sm_count, st);
 }
@@ -920,6 +953,74 @@ extern "C" int mg_matmul_fp8(const uint8_t* A, const uint8_t* B, int M, int N, i
   if (K % 128) return MG_ERR_SHAPE;
   return mg_matmul(nullptr, nullptr, nullptr, nullptr, A, B, M, N, 0, 0, K, C_bf16, D_bf16, N, nullptr, nullptr,
                    nullptr, nullptr, SFA, SFB, nullptr, 0, stream);
+}
+
+// ---------------------------------------------------------------- several weights, one activation
+extern "C" int mg_matmul_group_pitched(int nprob, const uint8_t* AN, const uint8_t* AS, const uint8_t* AO,
+                                       const size_t* pitches_a, const uint8_t* const* BN_, const uint8_t* const* BS,
+                                       const uint8_t* const* BO, const size_t* pitches_b, int M, const int* N, int KN,
+                                       int KS, int KO, void* const* D_bf16, const int* ldd, const uint8_t* SFAN,
+                                       const uint8_t* SFAS, const uint8_t* SFAO, const uint8_t* const* SFBN,
+                                       const uint8_t* const* SFBS, const uint8_t* const* SFBO, void* stream) {
+  if (nprob < 1 || nprob > kMaxGroup || M <= 128 || KN < 0 || KS < 0 || KO < 0 || KN + KS + KO <= 0) return MG_ERR_SHAPE;
+  if (KN % 128 || KS % 64 || KO % 64) return MG_ERR_SHAPE;
+  if (!pitches_a || !pitches_b || !N || !D_bf16 || !ldd) return MG_ERR_NULL;
+  if ((KN && (!AN || !SFAN)) || (KS && (!AS || !SFAS)) || (KO && (!AO || !SFAO))) return MG_ERR_NULL;
+  mg::DeviceInfo di;
+  int rc = mg::device_info(&di);
+  if (rc != MG_OK) return rc;
+
+  GemmParams p{};
+  GroupMaps gm;
+  CUtensorMap ma[3];
+  const int ksp = round_up(KS, 128), kop = round_up(KO, 128);
+  const int tiles_m2 = (M + 255) / 256;
+  int tiles = 0;
+  for (int j = 0; j < nprob; ++j) {
+    if (N[j] <= 0 || N[j] % 256 || ldd[j] < N[j] || ldd[j] % 8 || !D_bf16[j] || !mg::aligned(D_bf16[j], 16)) return MG_ERR_SHAPE;
+    const size_t pitches[6] = {pitches_a[0], pitches_b[j * 3 + 0], pitches_a[1], pitches_b[j * 3 + 1], pitches_a[2],
+                               pitches_b[j * 3 + 2]};
+    const Plan pl = make_plan(M, N[j], KN, KS, KO, pitches);
+    if (pl.status != MG_OK) return pl.status;
+    if (pl.total) return MG_ERR_ALIGN;  // grouped calls read every buffer in place: pitched buffers only
+    const uint8_t* b[3] = {BN_ ? BN_[j] : nullptr, BS ? BS[j] : nullptr, BO ? BO[j] : nullptr};
+    const uint8_t* sfb[3] = {SFBN ? SFBN[j] : nullptr, SFBS ? SFBS[j] : nullptr, SFBO ? SFBO[j] : nullptr};
+    const int kseg[3] = {KN, KS, KO};
+    const int first = KN ? 0 : (KS ? 1 : 2);
+    for (int seg = 0; seg < 3; ++seg) {
+      const int sg = kseg[seg] ? seg : first;
+      if (!b[sg] || !sfb[sg]) return MG_ERR_NULL;
+      if (!mg::aligned(b[sg], 32) || !mg::aligned(sfb[sg], 16)) return MG_ERR_ALIGN;
+      const CUtensorMapDataType dt = sg == 0 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B;
+      const uint64_t kd = sg == 0 ? KN / 2 : (sg == 1 ? ksp : kop);
+      if ((rc = make_map(&gm.b[j][seg], dt, b[sg], kd, N[j], pl.pitch[sg * 2 + 1], 128, 128))) return rc;
+      p.sfb_g[j][seg] = sfb[sg];
+      if (j == 0) {
+        const uint8_t* a = sg == 0 ? AN : (sg == 1 ? AS : AO);
+        if (!mg::aligned(a, 32)) return MG_ERR_ALIGN;
+        const CUtensorMapDataType da = sg == 1 ? CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+        const uint64_t ka = sg == 0 ? KN / 2 : (sg == 1 ? ksp : kop);
+        if ((rc = make_map(&ma[seg], da, a, ka, M, pl.pitch[sg * 2], 128, BM))) return rc;
+      }
+    }
+    if ((rc = make_map(&gm.d[j], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D_bf16[j], N[j], M, (uint64_t)ldd[j] * 2, 64, 128)))
+      return rc;
+    tiles += tiles_m2 * (N[j] / 256);
+    p.tile_end[j] = tiles;
+  }
+  p.nprob = nprob;
+  p.M = M;
+  p.N = N[0];
+  p.ldd = ldd[0];
+  p.seg[0] = {KN, (KN + 255) / 256, (KN + 127) / 128, SFAN, nullptr};
+  p.seg[1] = {KS, (KS + 127) / 128, (KS + 127) / 128, SFAS, nullptr};
+  p.seg[2] = {KO, (KO + 127) / 128, (KO + 127) / 128, SFAO, nullptr};
+  rc = mg::device_status_word(&p.status);
+  if (rc != MG_OK) return rc;
+  p.tx_a[0] = BM * 128; p.tx_b[0] = 128 * 128;
+  p.tx_a[1] = BM * 96;  p.tx_b[1] = 128 * 64;
+  p.tx_a[2] = BM * 128; p.tx_b[2] = 128 * 64;
+  return launch_pair(p, ma[0], ma[1], ma[2], gm, di.sm_count, static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------- entry point that allocates nothing

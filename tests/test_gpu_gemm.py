@@ -217,3 +217,25 @@ def test_rejects_bad_arguments():
         mg.matmul(A[0], B[0][:100], A[1], B[1][:100], A[2], B[2][:100], A[3], B[3], A[4], B[4], A[5], B[5])
     with pytest.raises(RuntimeError):
         mg.matmul(A[0].cpu(), B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+
+
+@pytest.mark.parametrize("M,Ns,split", [(512, (512, 256, 256), (1280, 640, 128)), (2048, (4096, 1024, 1024), (2560, 1408, 128)),
+                                        (300, (256, 768), (8960, 4928, 448)), (100, (256, 256), (256, 128, 128))])
+def test_grouped_weights_equal_separate_calls(M, Ns, split):
+    """q/k/v- or gate/up-style groups in one launch give the bytes of one launch per weight
+    (the last case is too small for the grouped kernel and takes the fallback)."""
+    import mixedgemm_b200 as mg
+    KN, KS, KO = split
+    K = sum(split)
+    X = H.make_x(M, K, seed=31)
+    idx = H.reorder_index(X).cuda()
+    A = mg.reorder_quantize_x(X.cuda(), idx, KN, KS, KO, M, 0)
+    Bs = [mg.reorder_quantize_w(H.make_w(N, K, seed=40 + j).cuda(), idx, KN, KS, KO, M, N) for j, N in enumerate(Ns)]
+    outs = mg.matmul_group(A, Bs)
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    for B, N, y in zip(Bs, Ns, outs):
+        ref = mg.matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+        assert y.shape == (M, N)
+        assert torch.equal(y.view(torch.int16), ref.view(torch.int16))
+    _check(A, Bs[-1], M, Ns[-1], split)
