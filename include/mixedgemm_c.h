@@ -134,6 +134,16 @@ int mg_matmul_pitched(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, c
                       const uint8_t* SFBO, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Reorder-index calibration: idx = stable ascending argsort of the per-channel absmax of X.
+ * The reference leaves this to the caller (main.py:29 uses arange; the absmax/argsort variant at
+ * main.py:31-33 is commented out and uses an unstable torch.sort).  Ties are ubiquitous in bf16
+ * maxima, so the order is pinned: equal maxima keep channel order.
+ *   X [M,K] bf16 (K % 8 == 0, K <= 32736);  idx [K] int16 out;
+ *   absmax_bits [K] uint16 out: bf16 bit pattern of each channel's largest magnitude.
+ */
+int mg_reorder_index(const void* X, int M, int K, int16_t* idx, uint16_t* absmax_bits, void* stream);
+
+/*
  * Several weight matrices that consume the same quantised activation (q/k/v; gate/up) in ONE
  * launch: D[j] = bf16(A * B[j]^T), j < nprob <= 4.  The reference calls matmul_host once per weight
  * (main.py:59 per layer); sharing the launch lets small projections fill SMs that a large one

@@ -29,6 +29,7 @@ PROTOTYPES = {
     "mg_reorder_quantize_pitched": (_i, [_i, _vp, _i, _i, _vp, _i, _i, _i] + [_vp] * 3 + [_vp] + [_vp] * 3 + [_vp]),
     "mg_matmul_pitched_workspace_bytes": (_sz, [_i] * 5 + [_vp]),
     "mg_matmul_pitched": (_i, [_vp] * 6 + [_vp, _i] + [_i] * 5 + [_vp, _vp, _i] + [_vp] * 6 + [_vp, _sz, _vp]),
+    "mg_reorder_index": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "mg_matmul_group_pitched": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp,
                                      _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mg_matmul_f32": (_i, [_vp] * 6 + [_i] * 5 + [_vp, _vp, _i] + [_vp] * 6 + [_vp, _sz, _vp]),

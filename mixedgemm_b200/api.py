@@ -173,6 +173,21 @@ def matmul(AN, BN, AS, BS, AO, BO, SFAN, SFBN, SFAS, SFBS, SFAO, SFBO, out=None,
     return D
 
 
+def reorder_index(X, return_absmax=False):
+    """Stable ascending argsort of the per-channel absmax of X [M,K] bf16 -> int16 [K]
+    (what main.py:31-33 sketches with torch.max / torch.sort), computed by the library's kernels."""
+    if not X.is_cuda or X.dtype != torch.bfloat16 or X.dim() != 2 or not X.is_contiguous():
+        raise RuntimeError("reorder_index: expected a contiguous 2-D CUDA bfloat16 tensor")
+    lib = _capi.load()
+    M, K = X.shape
+    idx = torch.empty(K, dtype=torch.int16, device=X.device)
+    amax = torch.empty(K, dtype=torch.int16, device=X.device)
+    with torch.cuda.device(X.device):
+        st = lib.mg_reorder_index(_ptr(X), M, K, _ptr(idx), _ptr(amax), _stream())
+    _capi.check(st, "reorder_index")
+    return (idx, amax.view(torch.bfloat16)) if return_absmax else idx
+
+
 def matmul_group(A, Bs, outs=None):
     """Products of one quantised activation A = (AN, AS, AO, SFAN, SFAS, SFAO) with several quantised
     weights Bs = [(BN, BS, BO, SFBN, SFBS, SFBO), ...] (q/k/v, gate/up) in one launch where the

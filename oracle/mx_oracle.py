@@ -311,3 +311,10 @@ def f32_to_bf16_bits(x):
     f = np.ascontiguousarray(x, np.float32)
     u = f.view(np.uint32)
     return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def np_reorder_index(X_bits):
+    """Stable ascending argsort of the per-channel absmax (main.py:31-33 with the sort made stable):
+    on bf16 bit patterns, the magnitude bits order like the values."""
+    mag = (np.asarray(X_bits, np.uint16) & 0x7FFF).max(axis=0)
+    return np.argsort(mag, kind="stable").astype(np.int16), mag

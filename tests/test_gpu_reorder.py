@@ -145,3 +145,17 @@ def test_rejects_bad_arguments():
         mg.reorder_quantize_x(X.float(), idx, 64, 32, 32, 4, 4)
     out = mg.reorder_quantize_x(X[:0], idx, 64, 32, 32, 0, 0)  # empty input is fine
     assert out[0].shape == (0, 32)
+
+
+@pytest.mark.parametrize("M,K", [(1, 128), (16, 4096), (2048, 4096), (300, 14336), (64, 28672), (5, 136)])
+def test_reorder_index_kernel(M, K):
+    """Index calibration: same permutation as the stable argsort of the oracle and of torch."""
+    import mixedgemm_b200 as mg
+    Xb = H.make_x(M, K, seed=M + K)
+    Xb[:, ::7] = Xb[:, 3:4]  # plenty of exact ties
+    idx, amax = mg.reorder_index(Xb.cuda(), return_absmax=True)
+    want, mag = orc.np_reorder_index(H.bits(Xb))
+    assert np.array_equal(H.bits(amax.cpu()), mag)
+    assert np.array_equal(idx.cpu().numpy(), want)
+    tidx = torch.sort(Xb.float().abs().amax(0), stable=True).indices.to(torch.int16)
+    assert torch.equal(idx.cpu(), tidx)

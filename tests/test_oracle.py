@@ -184,3 +184,14 @@ def test_dequant_and_gemm_c_vs_numpy():
     # quantisation error is bounded: dequantised X is close to the reordered X
     Xf = (X[:, idx.astype(np.uint16)].astype(np.uint32) << 16).view(np.float32)
     assert np.abs(Ad - Xf).max() <= 0.26 * np.abs(Xf).max()
+
+
+def test_reorder_index_oracle_matches_torch_stable_sort():
+    import torch
+    from tests import helpers as H
+    Xb = H.make_x(33, 512, seed=2)
+    Xb[:, ::5] = Xb[:, 1:2]
+    want = torch.sort(Xb.float().abs().amax(0), stable=True).indices.to(torch.int16).numpy()
+    got, mag = orc.np_reorder_index(H.bits(Xb))
+    assert np.array_equal(got, want)
+    assert sorted(got.tolist()) == list(range(512))
