@@ -249,14 +249,26 @@ class Job:
         # weights that consume the same activation go out as one grouped launch where the kernel takes them
         self.mg.matmul_group(gr["A"], [B for (_, _, B, _) in gr["layers"]], outs=[Y for (_, _, _, Y) in gr["layers"]])
 
+    def quantize_and_exchange(self, gr):
+        """bcast: rank 0 quantises, one NCCL broadcast; allgather: every rank quantises M/P rows in
+        place, NCCL all-gathers complete the buffers; replicated: every rank quantises everything."""
+        if self.world == 1 or self.exchange == "replicated":
+            self.quantize(gr)
+        elif self.exchange == "allgather":
+            from mixedgemm_b200 import dist as mgd
+            KN, KS, KO = gr["split"]
+            mp = self.M // self.world
+            sh = mgd.activation_shard(gr["A"], self.M, gr["split"], self.world, self.rank)
+            self.mg.reorder_quantize_x(gr["X"][self.rank * mp:(self.rank + 1) * mp], gr["idx"], KN, KS, KO, mp, 0, out=sh)
+            mgd.all_gather_activations(gr["A"], self.M, gr["split"], self.world, self.rank)
+        else:
+            if self.rank == 0:
+                self.quantize(gr)
+            self.exchange_a(gr)
+
     def step(self):
         for gr in self.groups:
-            if self.world == 1 or self.exchange == "replicated":
-                self.quantize(gr)
-            else:
-                if self.rank == 0:
-                    self.quantize(gr)
-                self.exchange_a(gr)
+            self.quantize_and_exchange(gr)
             self.gemms(gr)
 
 
@@ -340,7 +352,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=list(WORKLOADS))
-    ap.add_argument("--exchange", default="bcast", choices=["bcast", "replicated"])
+    ap.add_argument("--exchange", default="bcast", choices=["bcast", "replicated", "allgather"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--cpu-rows", type=int, default=128)
     ap.add_argument("--kernel", default=None, choices=["gemm", "reorder"],
@@ -484,12 +496,7 @@ def main():
         def e2e_step():
             for gr, hx, hys in zip(job.groups, hX, hY):
                 gr["X"].copy_(hx, non_blocking=True)
-                if world == 1 or a.exchange == "replicated":
-                    job.quantize(gr)
-                else:
-                    if rank == 0:
-                        job.quantize(gr)
-                    job.exchange_a(gr)
+                job.quantize_and_exchange(gr)
                 job.gemms(gr)
                 for (_, _, _, Y), hy in zip(gr["layers"], hys):
                     hy.copy_(Y, non_blocking=True)

@@ -57,6 +57,47 @@ def broadcast_activations(A, src=0, group=None):
         dist.broadcast(base, src=src, group=group)
 
 
+def _pitched_base(t):
+    """[rows, pitch] buffer under a [rows, logical] row-pitched view (or the tensor itself)."""
+    if t.is_contiguous():
+        return t
+    return t.as_strided((t.size(0), t.stride(0)), (t.stride(0), 1), t.storage_offset())
+
+
+def activation_shard(A, M, split, world, rank):
+    """Views of the six full-size activation buffers that hold rows [rank*M/P, (rank+1)*M/P):
+    what this rank's quantiser writes when the quantisation itself is sharded along M.  M/P must
+    be a multiple of 128 so that a shard is whole scale blocks."""
+    if M % (128 * world) != 0:
+        raise ValueError("M = %d cannot be split into %d shards of whole 128-row blocks" % (M, world))
+    mp = M // world
+    r0 = rank * mp
+    out = [A[i][r0:r0 + mp] for i in range(3)]
+    for i, k in enumerate(split):
+        per_block = ((k + 127) // 128) * 512
+        out.append(A[3 + i][(r0 // 128) * per_block:((r0 + mp) // 128) * per_block])
+    return tuple(out)
+
+
+def all_gather_activations(A, M, split, world, rank, group=None):
+    """Every rank has quantised its own M/P rows in place (activation_shard); gather the other
+    ranks' rows so that each GPU holds the whole quantised activation in its own memory."""
+    mp = M // world
+    for i in range(3):
+        if A[i].numel() == 0:
+            continue
+        base = _pitched_base(A[i])
+        dist.all_gather_into_tensor(base.view(-1), base[rank * mp:(rank + 1) * mp].reshape(-1), group=group)
+    for i, k in enumerate(split):
+        if k == 0:
+            continue
+        per_block = ((k + 127) // 128) * 512
+        n = (M // 128) * per_block
+        full = A[3 + i][:n]
+        dist.all_gather_into_tensor(full, full[(rank * mp // 128) * per_block:((rank + 1) * mp // 128) * per_block],
+                                    group=group)
+
+
 def all_gather_output(Y_local, world, group=None):
     """[M, N/P] shards -> [M, N] (only for callers that need the full tensor)."""
     parts = [torch.empty_like(Y_local) for _ in range(world)]

@@ -59,6 +59,18 @@ def _worker(rank, world, port, ret):
                 v.copy_(t_)
         mgd.broadcast_activations(views, src=0)
         ret["one_buffer_%d" % rank] = all(bool(torch.equal(v, t_)) for v, t_ in zip(views, A))
+        # quantisation sharded along M: each rank fills its rows, an all-gather completes the buffers
+        M2 = 256
+        X2 = H.make_x(M2, K, seed=9)
+        full = [np.ascontiguousarray(a) for a in H.oracle_outputs(H.bits(X2), idx, KN, KS, KO)]
+        mine = [torch.zeros_like(torch.from_numpy(a)) for a in full]
+        sh = mgd.activation_shard(mine, M2, SPLIT, world, rank)
+        mp_ = M2 // world
+        part = H.oracle_outputs(H.bits(X2[rank * mp_:(rank + 1) * mp_]), idx, KN, KS, KO)
+        for dst, src in zip(sh, part):
+            dst.copy_(torch.from_numpy(np.ascontiguousarray(src))[:dst.numel()].view(dst.shape))
+        mgd.all_gather_activations(mine, M2, SPLIT, world, rank)
+        ret["allgather_%d" % rank] = all(np.array_equal(m.numpy(), f) for m, f in zip(mine, full))
         r0, n = mgd.shard_range(N, world, rank)
         Yl = orc.gemm_f64([t.numpy() for t in A], [t.numpy() for t in Bl], M, n, KN, KS, KO)
         Y = mgd.all_gather_output(torch.from_numpy(Yl), world)
@@ -77,6 +89,7 @@ def test_two_rank_sharding_recombines_exactly():
     assert ret["shape"] == (M, N)
     assert ret["equal"]
     assert ret["one_buffer_0"] and ret["one_buffer_1"]
+    assert ret["allgather_0"] and ret["allgather_1"]
 
 
 def test_shard_helpers():
