@@ -354,6 +354,7 @@ def main():
     ap.add_argument("--workload", default=None, choices=list(WORKLOADS))
     ap.add_argument("--exchange", default="bcast", choices=["bcast", "replicated", "allgather"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--graph-nccl", action="store_true", help="multi-rank: capture the step, collectives included")
     ap.add_argument("--cpu-rows", type=int, default=128)
     ap.add_argument("--kernel", default=None, choices=["gemm", "reorder"],
                     help="run only this kernel on --shape (for profiling); prints a short JSON line")
@@ -412,7 +413,7 @@ def main():
     # ---- whole-step timing, inputs resident in HBM
     # NCCL collectives are launched eagerly: replaying them from a captured graph next to eager
     # collectives on the same communicator stalled on this pool, so multi-rank runs do not capture
-    use_graph = not a.no_graph and world == 1
+    use_graph = not a.no_graph and (world == 1 or a.graph_nccl)
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
         for _ in range(a.warmup):
@@ -443,8 +444,14 @@ def main():
         # nvidia-smi samples every 100 ms: when the K timed steps are shorter than that, the clocks are
         # read over an identical window of back-to-back steps that follows them immediately
         clock_window = "the timed steps"
-        if t1 - t0 < 0.6:
-            n_extra = int(0.6 / max(ms / 1e3, 1e-6)) + 1
+        # every rank must run the same number of steps (they contain collectives): decide on rank 0's clock
+        plan = torch.tensor([t1 - t0, ms], device=device, dtype=torch.float64)
+        if world > 1:
+            import torch.distributed as dist
+            dist.broadcast(plan, src=0)
+        span, ms_ref = plan.tolist()
+        if span < 0.6:
+            n_extra = int(0.6 / max(ms_ref / 1e3, 1e-6)) + 1
             t0 = time.time()
             timed(run, n_extra, sync)
             t1 = time.time()
