@@ -352,9 +352,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=list(WORKLOADS))
-    ap.add_argument("--exchange", default="bcast", choices=["bcast", "replicated", "allgather"])
+    ap.add_argument("--exchange", default="replicated", choices=["bcast", "replicated", "allgather"])
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--graph-nccl", action="store_true", help="multi-rank: capture the step, collectives included")
     ap.add_argument("--cpu-rows", type=int, default=128)
     ap.add_argument("--kernel", default=None, choices=["gemm", "reorder"],
                     help="run only this kernel on --shape (for profiling); prints a short JSON line")
@@ -411,9 +410,7 @@ def main():
     pk = peaks()
 
     # ---- whole-step timing, inputs resident in HBM
-    # NCCL collectives are launched eagerly: replaying them from a captured graph next to eager
-    # collectives on the same communicator stalled on this pool, so multi-rank runs do not capture
-    use_graph = not a.no_graph and (world == 1 or a.graph_nccl)
+    use_graph = not a.no_graph
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
         for _ in range(a.warmup):
