@@ -2,7 +2,7 @@
 """Benchmark of the hot path: activation reorder-and-quantise + mixed MXFP4/6/8 GEMM.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                  [--workload NAME] [--exchange bcast|replicated] [--no-graph]
+                  [--workload NAME] [--exchange replicated|bcast|allgather] [--no-graph]
 
 One "step" is one pass over a projection set of a Llama-shaped layer stack: every distinct
 activation is reorder-quantised once and multiplied with each weight that consumes it
@@ -11,8 +11,10 @@ timed region, as in deployment.
 
   N = 1 (default)   workload llama3-8b-m2048   (BASELINE configs[1])
   N > 1             workload llama3-70b-m4096  (BASELINE configs[3]): weights sharded along N
-                    over the ranks, quantised activations broadcast from rank 0 with NCCL
-                    (--exchange replicated: every rank quantises locally instead)
+                    over the ranks.  --exchange replicated (default: the fastest measured): every
+                    rank quantises the activations itself; bcast: rank 0 quantises and broadcasts
+                    them with NCCL; allgather: every rank quantises M/P rows and NCCL all-gathers
+                    complete the buffers
 
 Prints ONE JSON line (rank 0).  `value` is the whole-job GEMM throughput with inputs resident
 in HBM; `e2e` is the same metric with the activations starting in pinned host memory and the
