@@ -255,16 +255,18 @@ __global__ void __launch_bounds__(kThreads, 1) reorder_quantize_kernel(const Reo
       idx2[i] = (uint16_t)(v * 2);
     }
     ptx::named_barrier_sync(1, kConsumers);
-    const int r = tid % R;          // kConsumers is a multiple of R: a thread keeps its row
-    const int g0 = tid / R;
+    // a thread keeps its row: R * kGStep consumer threads work (all 512 unless R is 3 or 6)
     constexpr int kGStep = kConsumers / R;
+    const bool worker = tid < R * kGStep;
+    const int r = tid % R;
+    const int g0 = tid / R;
     const uint32_t idx2_addr = ptx::smem_u32(idx2);
     for (int it = 0; it < nstage; ++it) {
       const int s = it % S;
       const uint32_t ph = (uint32_t)(it / S) & 1u;
       wait_parity(bar0 + 8 * s, ph, stop, p.status, 32);
       const int row = row_begin + it * R + r;
-      if (row < row_end && !*stop) {
+      if (worker && row < row_end && !*stop) {
         RowCtx rc;
         rc.smem_row = ptx::smem_u32(tiles + (size_t)s * stage_bytes) + r * pitch;
         rc.sf_row = (uint32_t)(row & 31) * 16 + (uint32_t)((row >> 5) & 3) * 4;
@@ -329,14 +331,16 @@ int reorder_quantize(bool weights, const void* X, int rows, int K, const int16_t
   p.seg[1] = {o6, s6, (KS + 127) / 128, (int)pitch[1]};
   p.seg[2] = {o8, s8, (KO + 127) / 128, (int)pitch[2]};
 
-  // Rows per stage: as many as fit twice (double buffering) beside the index, but no more than
+  // Rows per stage (8, 6, 4, 3, 2 or 1): as many as fit twice (double buffering) beside the index, but no more than
   // half of a CTA's share so that its last stage is not mostly empty.  Then as many stages as
   // fit, up to 4.
   const size_t budget = (size_t)di.smem_optin - 1024;
   const int grid = rows < di.sm_count ? rows : di.sm_count;  // rows are dealt out evenly, at least one per CTA
   const int rows_per_cta = rows / grid;
-  int R = 8;
-  while (R > 1 && (smem_bytes(K, R, 2) > budget || 2 * R > rows_per_cta)) R >>= 1;
+  static const int kRs[] = {8, 4, 2, 1};  // 6 and 3 rows fit more often but measured slower (fewer stages)
+  int R = 1;
+  for (int cand : kRs)
+    if (smem_bytes(K, cand, 2) <= budget && (2 * cand <= rows_per_cta || cand == 1)) { R = cand; break; }
   int S = 2;
   while (S < 4 && smem_bytes(K, R, S + 1) <= budget) ++S;
   if (smem_bytes(K, R, 2) > budget) S = 1;
@@ -353,7 +357,9 @@ int reorder_quantize(bool weights, const void* X, int rows, int K, const int16_t
     return weights ? launch<RR, true>(p, grid, smem, st) : launch<RR, false>(p, grid, smem, st);
   switch (R) {
     MG_LAUNCH_R(8)
+    MG_LAUNCH_R(6)
     MG_LAUNCH_R(4)
+    MG_LAUNCH_R(3)
     MG_LAUNCH_R(2)
     MG_LAUNCH_R(1)
   }
