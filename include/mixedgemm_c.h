@@ -119,8 +119,15 @@ int mg_matmul(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, const uin
  * first K/2 (3K/4, K) bytes are the reference's row; the bytes after them are never interpreted.
  *   pitches of mg_reorder_quantize_pitched: {FP4 buffer, FP6 (or second FP4) buffer, FP8 (or third FP4) buffer}
  *   pitches of mg_matmul_pitched:           {AN, BN, AS, BS, AO, BO}
- * mg_matmul_pitched needs workspace only for operands whose pitch does not qualify
- * (mg_matmul_pitched_workspace_bytes); out_f32 != 0 selects the fp32 output of mg_matmul_f32.
+ * mg_matmul_pitched needs workspace only for operands whose pitch does not qualify; when the
+ * workspace also has the 19 MB that mg_matmul_pitched_workspace_bytes adds for N % 256 == 0, the
+ * CTA-pair kernel runs "stream-K": the launch's (tile, K-stage) units are dealt evenly to the SM
+ * pairs, tiles cut that way are completed from fp32 partials in the workspace, so problems whose
+ * tile count does not fill whole waves (and decode shapes, M <= 128) keep every SM busy.  Results
+ * then differ from the tile-per-cluster order by fp32 re-association only.  The first 1 KB of that
+ * region holds flags: the library clears them the first time it sees a workspace address and
+ * leaves them clear; after a non-zero mg_device_status, clear them yourself or pass a fresh buffer.
+ * out_f32 != 0 selects the fp32 output of mg_matmul_f32.
  */
 size_t mg_code_pitch(int weights, int segment, int kseg);
 int mg_reorder_quantize_pitched(int weights, const void* X, int rows, int K, const int16_t* idx, int KN, int KS,
@@ -151,14 +158,15 @@ int mg_reorder_index(const void* X, int M, int K, int16_t* idx, uint16_t* absmax
  * and every code buffer row-pitched so that it is read in place (mg_code_pitch) - otherwise
  * MG_ERR_SHAPE / MG_ERR_ALIGN is returned and the caller issues mg_matmul per weight instead.
  *   pitches_a[3] = {AN, AS, AO};  pitches_b[3*j + s] = pitch of weight j, segment s
- *   BN/BS/BO/SFBN/SFBS/SFBO/D/N/ldd are arrays of nprob entries.  Results equal mg_matmul's bit for bit.
+ *   BN/BS/BO/SFBN/SFBS/SFBO/D/N/ldd are arrays of nprob entries.  workspace (optional, 1024-aligned,
+ *   mg_matmul_pitched_workspace_bytes of the widest problem) enables stream-K as in mg_matmul_pitched.
  */
 int mg_matmul_group_pitched(int nprob, const uint8_t* AN, const uint8_t* AS, const uint8_t* AO,
                             const size_t* pitches_a, const uint8_t* const* BN, const uint8_t* const* BS,
                             const uint8_t* const* BO, const size_t* pitches_b, int M, const int* N, int KN, int KS,
                             int KO, void* const* D_bf16, const int* ldd, const uint8_t* SFAN, const uint8_t* SFAS,
                             const uint8_t* SFAO, const uint8_t* const* SFBN, const uint8_t* const* SFBS,
-                            const uint8_t* const* SFBO, void* stream);
+                            const uint8_t* const* SFBO, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Same product with the fp32 accumulator written unrounded: D_f32 [M,N] float, pitch `ldd`

@@ -31,7 +31,7 @@ PROTOTYPES = {
     "mg_matmul_pitched": (_i, [_vp] * 6 + [_vp, _i] + [_i] * 5 + [_vp, _vp, _i] + [_vp] * 6 + [_vp, _sz, _vp]),
     "mg_reorder_index": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "mg_matmul_group_pitched": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp,
-                                     _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+                                     _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "mg_matmul_f32": (_i, [_vp] * 6 + [_i] * 5 + [_vp, _vp, _i] + [_vp] * 6 + [_vp, _sz, _vp]),
     "mg_matmul_static_ws": (_i, [_vp] * 6 + [_i] * 5 + [_vp, _vp, _i] + [_vp] * 6 + [_vp]),
     "mg_matmul_fp4": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),

@@ -207,11 +207,12 @@ def matmul_group(A, Bs, outs=None):
         vp = lambda ts: (ctypes.c_void_p * n)(*[_ptr(t) for t in ts])
         pb = (ctypes.c_size_t * (3 * n))(*[B[s].stride(0) if B[s].size(1) else 0 for B in Bs for s in range(3)])
         with torch.cuda.device(dev):
+            ws, wsb = _workspace(dev, lib.mg_matmul_pitched_workspace_bytes(M, max(Ns), KN, KS, KO, None))
             st = lib.mg_matmul_group_pitched(
                 n, _ptr(A[0]), _ptr(A[1]), _ptr(A[2]), _pitches(A[:3]), vp([B[0] for B in Bs]),
                 vp([B[1] for B in Bs]), vp([B[2] for B in Bs]), pb, M, (ctypes.c_int * n)(*Ns), KN, KS, KO, vp(outs),
                 (ctypes.c_int * n)(*[o.stride(0) for o in outs]), _ptr(A[3]), _ptr(A[4]), _ptr(A[5]),
-                vp([B[3] for B in Bs]), vp([B[4] for B in Bs]), vp([B[5] for B in Bs]), _stream())
+                vp([B[3] for B in Bs]), vp([B[4] for B in Bs]), vp([B[5] for B in Bs]), ws, wsb, _stream())
     if st in (1, 3):  # shape or pitch the grouped kernel does not take: one launch per weight
         for B, o in zip(Bs, outs):
             matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5], out=o)
@@ -226,6 +227,10 @@ def device_status():
     lib = _capi.load()
     v = ctypes.c_int(0)
     _capi.check(lib.mg_device_status(ctypes.byref(v), _stream()), "device_status")
+    if v.value != 0:
+        # a kernel that gave up may have left stream-K flags set: start from clean scratch
+        for buf in _workspaces.values():
+            buf.zero_()
     return v.value
 
 

@@ -55,6 +55,12 @@ struct GemmParams {
   int nprob;
   int tile_end[4];
   const uint8_t* sfb_g[4][3];
+  // Stream-K (CTA-pair kernel): the launch's (tile, K-stage) units are dealt to the clusters as equal
+  // contiguous ranges, so a cluster may compute only part of a tile's K.  The cluster that holds a
+  // tile's first stage finishes it, adding the fp32 partials the others leave in sk_partials.
+  int streamk;
+  int* sk_flags;       // [cluster][cta]: 1 when that CTA's partial is complete; the finisher clears it
+  float* sk_partials;  // [cluster][cta][128 rows][256 columns]
 };
 
 constexpr int kMaxGroup = 4;
@@ -442,13 +448,39 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     m_pt = lt % tiles_m2;
     n_tile = lt / tiles_m2;
   };
+  // Work list of this cluster: pieces (tile, K stages [s0, s1)).  Without stream-K a piece is a
+  // whole tile and tiles go round-robin; with it the cluster owns units [u_begin, u_end).
+  const int S_units = p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages;
+  const int seg_off1 = p.seg[0].nstages, seg_off2 = seg_off1 + p.seg[1].nstages;
+  const long long U_total = (long long)total_tiles * S_units;
+  const int u_begin = (int)(U_total * first_tile / tile_step), u_end = (int)(U_total * (first_tile + 1) / tile_step);
+  struct Piece { int tile, s0, s1; };
+  auto next_piece = [&](int& cur, Piece& pc) -> bool {
+    if (p.streamk) {
+      if (cur >= u_end) return false;
+      pc.tile = cur / S_units;
+      pc.s0 = cur - pc.tile * S_units;
+      pc.s1 = min(S_units, pc.s0 + (u_end - cur));
+      cur += pc.s1 - pc.s0;
+      return true;
+    }
+    if (cur >= total_tiles) return false;
+    pc.tile = cur;
+    pc.s0 = 0;
+    pc.s1 = S_units;
+    cur += tile_step;
+    return true;
+  };
+  const int cur0 = p.streamk ? u_begin : first_tile;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     const bool leader = ptx::elect_one();
     int stage = 0;
     uint32_t phase = 0;
-    for (int t = first_tile; t < total_tiles; t += tile_step) {
+    Piece pc;
+    for (int cur = cur0; next_piece(cur, pc);) {
+      const int t = pc.tile;
       int prob, m_pt, n_tile;
       locate(t, prob, m_pt, n_tile);
       const int m_row0 = m_pt * 256 + (int)rank * 128, n_row0 = n_tile * 256 + (int)rank * 128;
@@ -464,8 +496,10 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
         const int row_blk = min(m_pt * 2 + (int)rank, (p.M + 127) / 128 - 1);
         const uint8_t* sfa_row = sp.sfa + (size_t)row_blk * sp.katoms * 512;
         const uint8_t* sfb_row = p.sfb_g[prob][seg] + (size_t)(n_tile * 2) * sp.katoms * 512;
+        const int so = seg == 0 ? 0 : (seg == 1 ? seg_off1 : seg_off2);
+        const int s_lo = max(pc.s0 - so, 0), s_hi = min(pc.s1 - so, sp.nstages);
 #pragma unroll 1
-        for (int s = 0; s < sp.nstages; ++s) {
+        for (int s = s_lo; s < s_hi; ++s) {
           wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, 1);
           const int atom0 = seg == 0 ? 2 * s : s;
           const int natoms = seg == 0 ? min(2, sp.katoms - atom0) : 1;
@@ -491,10 +525,10 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     // ------------------------------------------------------------ relay: stage landed -> leader's ready barrier
     int stage = 0;
     uint32_t phase = 0;
-    const int nst = p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages;
-    for (int t = first_tile; t < total_tiles; t += tile_step) {
+    Piece pc;
+    for (int cur = cur0; next_piece(cur, pc);) {
 #pragma unroll 1
-      for (int s = 0; s < nst; ++s) {
+      for (int s = pc.s0; s < pc.s1; ++s) {
         wait_parity(full_bar(stage), phase, stop, p.status, 64);
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ready_bar(stage), 0));
@@ -512,7 +546,8 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
       int stage = 0;
       uint32_t phase = 0, slot = 0;
       int it = 0;
-      for (int t = first_tile; t < total_tiles; t += tile_step, ++it) {
+      Piece pc;
+      for (int cur = cur0; next_piece(cur, pc); ++it) {
         wait_parity(tempty_bar, ((uint32_t)it & 1u) ^ 1u, stop, p.status, 4);
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base;
@@ -521,8 +556,10 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
         for (int seg = 0; seg < 3; ++seg) {
           const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
           const uint32_t id0 = seg == 0 ? kIdesc[0] : (seg == 1 ? kIdesc[1] : kIdesc[2]);
+          const int so = seg == 0 ? 0 : (seg == 1 ? seg_off1 : seg_off2);
+          const int s_lo = max(pc.s0 - so, 0), s_hi = min(pc.s1 - so, sp.nstages);
 #pragma unroll 1
-          for (int s = 0; s < sp.nstages; ++s) {
+          for (int s = s_lo; s < s_hi; ++s) {
             wait_parity(ready_bar(stage), phase, stop, p.status, 2);
             ptx::tc_fence_after();
             const uint32_t sbase = ring + stage * C::STAGE_BYTES;
@@ -581,12 +618,37 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     const uint32_t tempty_leader = ptx::map_to_cta(tempty_bar, 0);
     const bool issuer = warp == 3 && lane == 0;
     int it = 0;
-    for (int t = first_tile; t < total_tiles; t += tile_step, ++it) {
+    Piece pc;
+    for (int cur = cur0; next_piece(cur, pc); ++it) {
+      const int t = pc.tile;
       int prob, m_pt, n_tile;
       locate(t, prob, m_pt, n_tile);
+      // what this piece is: a whole tile, the head of a tile other clusters complete (this CTA
+      // finishes it with their partials), or a later part of a tile (this CTA leaves a partial)
+      const bool contributor = pc.s0 > 0;
+      const bool head = pc.s0 == 0 && pc.s1 < S_units;
+      const int me = first_tile;  // cluster index
+      int n_contrib = 0;
+      if (head) {
+        // clusters me+1, me+2, ... own the rest of this tile's units
+        const long long tile_end_unit = (long long)(t + 1) * S_units;
+        while (me + 1 + n_contrib < tile_step && U_total * (me + 1 + n_contrib) / tile_step < tile_end_unit) ++n_contrib;
+      }
       wait_parity(tfull_bar, (uint32_t)it & 1u, stop, p.status, 8);
       __syncwarp();
       ptx::tc_fence_after();
+      if (head) {
+        // the other parts were computed first thing by their clusters; wait (bounded) for them
+        for (int k = 0; k < n_contrib; ++k) {
+          const volatile int* f = p.sk_flags + (size_t)(me + 1 + k) * 2 + rank;
+          const long long t0 = clock64();
+          while (*f == 0 && !*stop) {
+            if (clock64() - t0 > kWaitLimitCycles) { *stop = 1; atomicOr(p.status, 128); }
+          }
+        }
+        __threadfence();
+      }
+      float* my_partial = p.sk_partials + ((size_t)(me * 2 + (int)rank) * 128 + trow) * 256;
 #pragma unroll 1
       for (int j = 0; j < 4; ++j) {
         // the store that last used this staging slot has finished reading it
@@ -600,6 +662,33 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader);
+        }
+        if (contributor) {
+          // leave the fp32 partial of this row's 64 columns for the finishing cluster
+          uint4* dst = reinterpret_cast<uint4*>(my_partial + j * 64);
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            dst[v] = make_uint4(r0[v * 4], r0[v * 4 + 1], r0[v * 4 + 2], r0[v * 4 + 3]);
+            dst[8 + v] = make_uint4(r1[v * 4], r1[v * 4 + 1], r1[v * 4 + 2], r1[v * 4 + 3]);
+          }
+          if (issuer) ptx::bulk_commit_group();  // keeps the one-group-per-panel count
+          continue;
+        }
+        for (int k = 0; k < n_contrib; ++k) {
+          const uint4* src = reinterpret_cast<const uint4*>(
+              p.sk_partials + ((size_t)((me + 1 + k) * 2 + (int)rank) * 128 + trow) * 256 + j * 64);
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const uint4 a = __ldcg(src + v), b = __ldcg(src + 8 + v);
+            r0[v * 4] = __float_as_uint(__uint_as_float(r0[v * 4]) + __uint_as_float(a.x));
+            r0[v * 4 + 1] = __float_as_uint(__uint_as_float(r0[v * 4 + 1]) + __uint_as_float(a.y));
+            r0[v * 4 + 2] = __float_as_uint(__uint_as_float(r0[v * 4 + 2]) + __uint_as_float(a.z));
+            r0[v * 4 + 3] = __float_as_uint(__uint_as_float(r0[v * 4 + 3]) + __uint_as_float(a.w));
+            r1[v * 4] = __float_as_uint(__uint_as_float(r1[v * 4]) + __uint_as_float(b.x));
+            r1[v * 4 + 1] = __float_as_uint(__uint_as_float(r1[v * 4 + 1]) + __uint_as_float(b.y));
+            r1[v * 4 + 2] = __float_as_uint(__uint_as_float(r1[v * 4 + 2]) + __uint_as_float(b.z));
+            r1[v * 4 + 3] = __float_as_uint(__uint_as_float(r1[v * 4 + 3]) + __uint_as_float(b.w));
+          }
         }
         const uint32_t slot_addr = base + (uint32_t)(j % C::NSLOT) * C::PANEL_BYTES;
         const uint32_t prow = slot_addr + trow * 128;
@@ -621,6 +710,17 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
           if (m0 < p.M && !*stop && !(p.dbg & 4)) ptx::tma_store_2d(&gm.d[prob], n_tile * 256 + j * 64, m0, slot_addr);
           ptx::bulk_commit_group();  // one group per panel, also when nothing was stored
         }
+      }
+      if (contributor) {
+        __threadfence();  // every thread's partial is visible device-wide before the flag goes up
+        ptx::named_barrier_sync(1, 128);
+        if (issuer) {
+          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.sk_flags + (size_t)me * 2 + rank), "r"(1) : "memory");
+        }
+      } else if (head) {
+        ptx::named_barrier_sync(1, 128);  // all 128 threads have read the partials
+        if (issuer)
+          for (int k = 0; k < n_contrib; ++k) p.sk_flags[(size_t)(me + 1 + k) * 2 + rank] = 0;  // ready for the next launch
       }
     }
     if (issuer) ptx::bulk_wait_group0();
@@ -773,10 +873,49 @@ int launch_gemm(const GemmParams& p, const CUtensorMap* maps, int sms, cudaStrea
   return MG_OK;
 }
 
-int launch_pair(const GemmParams& p, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& a2,
-                const GroupMaps& gm, int sms, cudaStream_t st) {
+// Stream-K scratch: 1 KB of flags, then one 128 x 256 fp32 partial per CTA of up to 74 clusters.
+constexpr int kSkMaxClusters = 74;
+constexpr size_t kSkFlagBytes = 1024;
+constexpr size_t kSkBytes = kSkFlagBytes + (size_t)kSkMaxClusters * 2 * 128 * 256 * sizeof(float);
+
+bool streamk_wanted() {
+  const char* e = std::getenv("MG_GEMM_STREAMK");
+  return !(e && e[0] == '0');
+}
+
+// The flags must read 0 before the first launch that uses a scratch buffer; later launches leave
+// them 0.  A buffer address not seen before on this device is cleared once, on the caller's stream.
+int clear_flags_once(void* flags, cudaStream_t st) {
+  static std::mutex mu;
+  static void* seen[64][8];
+  static int next[64];
+  int dev = 0;
+  MG_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return MG_ERR_DEVICE;
+  std::lock_guard<std::mutex> lk(mu);
+  for (void* q : seen[dev])
+    if (q == flags) return MG_OK;
+  MG_CUDA_TRY(cudaMemsetAsync(flags, 0, kSkFlagBytes, st));
+  seen[dev][next[dev]++ % 8] = flags;
+  return MG_OK;
+}
+
+int launch_pair(GemmParams& p, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& a2,
+                const GroupMaps& gm, int sms, void* sk_ws, size_t sk_bytes, cudaStream_t st) {
   const int tiles = p.tile_end[p.nprob - 1];
-  const int clusters = tiles < sms / 2 ? tiles : sms / 2;
+  const int max_clusters = sms / 2 < kSkMaxClusters ? sms / 2 : kSkMaxClusters;
+  int clusters = tiles < max_clusters ? tiles : max_clusters;
+  const long long units = (long long)tiles * (p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages);
+  p.streamk = 0;
+  if (sk_ws && sk_bytes >= kSkBytes && streamk_wanted() && tiles % max_clusters != 0 && units >= max_clusters) {
+    // the tiles do not fill whole waves: deal out (tile, K-stage) units instead of tiles
+    p.streamk = 1;
+    clusters = max_clusters;
+    p.sk_flags = static_cast<int*>(sk_ws);
+    p.sk_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(sk_ws) + kSkFlagBytes);
+    const int rc = clear_flags_once(sk_ws, st);
+    if (rc != MG_OK) return rc;
+  }
   int variant = 1;
   if (const char* e = std::getenv("MG_GEMM_PAIR_VARIANT")) variant = std::atoi(e);
   if (variant == 0) {
@@ -800,7 +939,7 @@ extern "C" size_t mg_matmul_workspace_bytes(int M, int N, int KN, int KS, int KO
   return make_plan(M, N, KN, KS, KO, nullptr).total;
 }
 
-static int matmul_impl(bool f32_out, const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
+static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
                        const uint8_t* AO, const uint8_t* BO, const size_t* pitches, int M, int N, int KN, int KS, int KO,
                        const void* C_bf16, void* D_bf16, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
                        const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
@@ -848,10 +987,19 @@ static int matmul_impl(bool f32_out, const uint8_t* AN, const uint8_t* BN_, cons
 
   // The CTA-pair kernel wants enough 256 x 256 tiles to occupy most SM pairs; smaller problems
   // spread better as 128-row tiles over single SMs.
-  bool use_pair = !f32_out && C_bf16 == nullptr && N % 256 == 0 && M > 128;
+  // Stream-K scratch sits behind the padded copies, when the caller's workspace has room for it.
+  const size_t sk_off = align_up(pl.total, 1024);
+  void* sk_ws = nullptr;
+  size_t sk_bytes = 0;
+  if (allow_streamk && workspace && mg::aligned(workspace, 1024) && workspace_bytes >= sk_off + kSkBytes &&
+      streamk_wanted()) {
+    sk_ws = static_cast<uint8_t*>(workspace) + sk_off;
+    sk_bytes = workspace_bytes - sk_off;
+  }
+  bool use_pair = !f32_out && C_bf16 == nullptr && N % 256 == 0 && (M > 128 || sk_ws != nullptr);
   const int pair_tiles = ((M + 255) / 256) * (N / 256);
   if (const char* e = std::getenv("MG_GEMM_2CTA")) use_pair = use_pair && std::atoi(e) != 0;
-  else use_pair = use_pair && pair_tiles * 4 >= (di.sm_count / 2) * 3;
+  else use_pair = use_pair && (sk_ws != nullptr || pair_tiles * 4 >= (di.sm_count / 2) * 3);
   const int bn = use_pair ? 128 : choose_bn(M, N, di.sm_count);  // rows of one B tile load
 
   GemmParams p{};
@@ -900,7 +1048,7 @@ static int matmul_impl(bool f32_out, const uint8_t* AN, const uint8_t* BN_, cons
     }
     p.nprob = 1;
     p.tile_end[0] = pair_tiles;
-    return launch_pair(p, maps[0], maps[2], maps[4], gm, di.sm_count, st);
+    return launch_pair(p, maps[0], maps[2], maps[4], gm, di.sm_count, sk_ws, sk_bytes, st);
   }
   return bn == 256 ? launch_gemm<256>(p, maps, di.sm_count, st) : launch_gemm<128>(p, maps, di.sm_count, st);
 }
@@ -910,8 +1058,8 @@ extern "C" int mg_matmul(const uint8_t* AN, const uint8_t* BN_, const uint8_t* A
                          const void* C_bf16, void* D_bf16, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
                          const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
                          void* workspace, size_t workspace_bytes, void* stream) {
-  return matmul_impl(false, AN, BN_, AS, BS, AO, BO, nullptr, M, N, KN, KS, KO, C_bf16, D_bf16, ldd, SFAN, SFBN, SFAS,
-                     SFBS, SFAO, SFBO, workspace, workspace_bytes, stream);
+  return matmul_impl(false, true, AN, BN_, AS, BS, AO, BO, nullptr, M, N, KN, KS, KO, C_bf16, D_bf16, ldd, SFAN, SFBN,
+                     SFAS, SFBS, SFAO, SFBO, workspace, workspace_bytes, stream);
 }
 
 extern "C" int mg_matmul_pitched(const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
@@ -919,13 +1067,15 @@ extern "C" int mg_matmul_pitched(const uint8_t* AN, const uint8_t* BN_, const ui
                                  int KN, int KS, int KO, const void* C_bf16, void* D, int ldd, const uint8_t* SFAN,
                                  const uint8_t* SFBN, const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO,
                                  const uint8_t* SFBO, void* workspace, size_t workspace_bytes, void* stream) {
-  return matmul_impl(out_f32 != 0, AN, BN_, AS, BS, AO, BO, pitches, M, N, KN, KS, KO, C_bf16, D, ldd, SFAN, SFBN, SFAS,
+  return matmul_impl(out_f32 != 0, true, AN, BN_, AS, BS, AO, BO, pitches, M, N, KN, KS, KO, C_bf16, D, ldd, SFAN, SFBN, SFAS,
                      SFBS, SFAO, SFBO, workspace, workspace_bytes, stream);
 }
 
 extern "C" size_t mg_matmul_pitched_workspace_bytes(int M, int N, int KN, int KS, int KO, const size_t* pitches) {
   if (M <= 0 || N <= 0 || KN < 0 || KS < 0 || KO < 0) return 0;
-  return make_plan(M, N, KN, KS, KO, pitches).total;
+  const size_t need = make_plan(M, N, KN, KS, KO, pitches).total;
+  // what the CTA-pair kernel wants on top for stream-K; a smaller workspace still works, without it
+  return N % 256 == 0 ? align_up(need, 1024) + kSkBytes : need;
 }
 
 extern "C" int mg_matmul_f32(const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
@@ -933,7 +1083,7 @@ extern "C" int mg_matmul_f32(const uint8_t* AN, const uint8_t* BN_, const uint8_
                              const void* C_bf16, float* D_f32, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
                              const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
                              void* workspace, size_t workspace_bytes, void* stream) {
-  return matmul_impl(true, AN, BN_, AS, BS, AO, BO, nullptr, M, N, KN, KS, KO, C_bf16, D_f32, ldd, SFAN, SFBN, SFAS,
+  return matmul_impl(true, false, AN, BN_, AS, BS, AO, BO, nullptr, M, N, KN, KS, KO, C_bf16, D_f32, ldd, SFAN, SFBN, SFAS,
                      SFBS, SFAO, SFBO, workspace, workspace_bytes, stream);
 }
 
@@ -961,7 +1111,8 @@ extern "C" int mg_matmul_group_pitched(int nprob, const uint8_t* AN, const uint8
                                        const uint8_t* const* BO, const size_t* pitches_b, int M, const int* N, int KN,
                                        int KS, int KO, void* const* D_bf16, const int* ldd, const uint8_t* SFAN,
                                        const uint8_t* SFAS, const uint8_t* SFAO, const uint8_t* const* SFBN,
-                                       const uint8_t* const* SFBS, const uint8_t* const* SFBO, void* stream) {
+                                       const uint8_t* const* SFBS, const uint8_t* const* SFBO, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
   if (nprob < 1 || nprob > kMaxGroup || M <= 128 || KN < 0 || KS < 0 || KO < 0 || KN + KS + KO <= 0) return MG_ERR_SHAPE;
   if (KN % 128 || KS % 64 || KO % 64) return MG_ERR_SHAPE;
   if (!pitches_a || !pitches_b || !N || !D_bf16 || !ldd) return MG_ERR_NULL;
@@ -1020,7 +1171,8 @@ extern "C" int mg_matmul_group_pitched(int nprob, const uint8_t* AN, const uint8
   p.tx_a[0] = BM * 128; p.tx_b[0] = 128 * 128;
   p.tx_a[1] = BM * 96;  p.tx_b[1] = 128 * 64;
   p.tx_a[2] = BM * 128; p.tx_b[2] = 128 * 64;
-  return launch_pair(p, ma[0], ma[1], ma[2], gm, di.sm_count, static_cast<cudaStream_t>(stream));
+  void* sk_ws = (workspace && mg::aligned(workspace, 1024) && workspace_bytes >= kSkBytes) ? workspace : nullptr;
+  return launch_pair(p, ma[0], ma[1], ma[2], gm, di.sm_count, sk_ws, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------- entry point that allocates nothing
@@ -1061,6 +1213,6 @@ extern "C" int mg_matmul_static_ws(const uint8_t* AN, const uint8_t* BN_, const 
     }
     ws = g_static_ws_ptr[dev];
   }
-  return matmul_impl(false, AN, BN_, AS, BS, AO, BO, nullptr, M, N, KN, KS, KO, C_bf16, D_bf16, ldd, SFAN, SFBN, SFAS,
-                     SFBS, SFAO, SFBO, ws, (size_t)MG_STATIC_WS_BYTES, stream);
+  return matmul_impl(false, false, AN, BN_, AS, BS, AO, BO, nullptr, M, N, KN, KS, KO, C_bf16, D_bf16, ldd, SFAN, SFBN,
+                     SFAS, SFBS, SFAO, SFBO, ws, (size_t)MG_STATIC_WS_BYTES, stream);
 }

@@ -70,8 +70,17 @@ def _check(A, B, M, N, split, rows=None, C=None):
     mx = np.abs(y32s - Yo).max() / rms
     assert fro <= REL_FRO_TOL, "fp32 accumulator: rel-Frobenius %.3e" % fro
     assert mx <= MAX_ABS_TOL, "fp32 accumulator: max-abs %.3e RMS" % mx
-    # the bf16 output is the accumulator rounded once, to nearest even
-    assert np.array_equal(y16, orc.bf16_round(Y32.cpu().numpy())), "bf16 output is not RNE(fp32 accumulator)"
+    # the bf16 output is the accumulator rounded once, to nearest even.  The fp32 entry point adds the
+    # K stages of a tile in order; with stream-K the bf16 entry point may add two or more partial sums
+    # of the same products instead, so a few results may land on the neighbouring bf16 value.
+    rne = orc.bf16_round(Y32.cpu().numpy())
+    if not np.array_equal(y16, rne):
+        import os
+        assert os.environ.get("MG_GEMM_STREAMK", "1") != "0", "bf16 output is not RNE(fp32 accumulator)"
+        bad = y16 != rne
+        assert bad.mean() < 2e-3, "too many results off the rounded accumulator: %.2e" % bad.mean()
+        ulp = np.abs(rne[bad]).astype(np.float64) * 2.0 ** -7 + 1e-30
+        assert np.all(np.abs(y16[bad].astype(np.float64) - rne[bad]) <= ulp), "off by more than one bf16 step"
     # against the bf16-rounded float64 product: Frobenius bound, and max-abs up to one-ulp flips
     yo16 = orc.bf16_round(Yo).astype(np.float64)
     fro16 = np.linalg.norm(y16s - yo16) / np.linalg.norm(yo16)
@@ -109,6 +118,7 @@ def test_cta_pair_kernel_equals_single_cta_kernel(M, N, split, monkeypatch):
     """The CTA-pair kernel (256 x 256 tiles over two SMs, TMA-store epilogue) and the single-CTA
     kernel accumulate the same products in the same order: same bytes, and both pass the oracle."""
     import mixedgemm_b200 as mg
+    monkeypatch.setenv("MG_GEMM_STREAMK", "0")  # same summation order in both kernels
     A, B = _quantise(M, N, sum(split), split, seed=M)
     args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
     monkeypatch.setenv("MG_GEMM_2CTA", "1")
@@ -221,10 +231,11 @@ def test_rejects_bad_arguments():
 
 @pytest.mark.parametrize("M,Ns,split", [(512, (512, 256, 256), (1280, 640, 128)), (2048, (4096, 1024, 1024), (2560, 1408, 128)),
                                         (300, (256, 768), (8960, 4928, 448)), (100, (256, 256), (256, 128, 128))])
-def test_grouped_weights_equal_separate_calls(M, Ns, split):
+def test_grouped_weights_equal_separate_calls(M, Ns, split, monkeypatch):
     """q/k/v- or gate/up-style groups in one launch give the bytes of one launch per weight
     (the last case is too small for the grouped kernel and takes the fallback)."""
     import mixedgemm_b200 as mg
+    monkeypatch.setenv("MG_GEMM_STREAMK", "0")  # tile-per-cluster order in both, so the bytes agree
     KN, KS, KO = split
     K = sum(split)
     X = H.make_x(M, K, seed=31)
@@ -239,3 +250,30 @@ def test_grouped_weights_equal_separate_calls(M, Ns, split):
         assert y.shape == (M, N)
         assert torch.equal(y.view(torch.int16), ref.view(torch.int16))
     _check(A, Bs[-1], M, Ns[-1], split)
+
+
+@pytest.mark.parametrize("M,N,split", [(2048, 4096, (2560, 1408, 128)), (2048, 1024, (2560, 1408, 128)),
+                                       (1000, 768, (8960, 4928, 448)), (16, 4096, (2560, 1408, 128)),
+                                       (1, 1024, (256, 128, 128)), (128, 14336, (2560, 1408, 128)),
+                                       (300, 256, (128, 0, 0))])
+def test_stream_k(M, N, split, monkeypatch):
+    """Stream-K on the CTA-pair kernel (tiles cut along K between clusters, fp32 partials through the
+    workspace), including decode shapes: within the oracle's tolerance, within one bf16 step of the
+    tile-per-cluster result, and repeatable (the flags are left clear)."""
+    import mixedgemm_b200 as mg
+    A, B = _quantise(M, N, sum(split), split, seed=M + N)
+    args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+    monkeypatch.setenv("MG_GEMM_STREAMK", "1")
+    y1 = mg.matmul(*args)
+    y2 = mg.matmul(*args)
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    assert torch.equal(y1.view(torch.int16), y2.view(torch.int16))
+    monkeypatch.setenv("MG_GEMM_STREAMK", "0")
+    y0 = mg.matmul(*args)
+    d = (y1.float() - y0.float()).abs()
+    assert torch.all(d <= y0.float().abs() * 2.0 ** -7 + 1e-30)
+    assert (d > 0).float().mean().item() < 2e-3
+    monkeypatch.setenv("MG_GEMM_STREAMK", "1")
+    rows = None if M * N <= 1 << 20 else np.unique(np.concatenate([[0, M - 1], np.random.default_rng(0).integers(0, M, 30)]))
+    _check(A, B, M, N, split, rows=rows)
