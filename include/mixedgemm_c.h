@@ -124,8 +124,8 @@ int mg_matmul(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, const uin
  * CTA-pair kernel runs "stream-K": the launch's (tile, K-stage) units are dealt evenly to the SM
  * pairs, tiles cut that way are completed from fp32 partials in the workspace, so problems whose
  * tile count does not fill whole waves (and decode shapes, M <= 128) keep every SM busy.  Results
- * then differ from the tile-per-cluster order by fp32 re-association only.  The first 1 KB of that
- * region holds flags: the library clears them the first time it sees a workspace address and
+ * then differ from the tile-per-cluster order by fp32 re-association only.  The first 19 KB of that
+ * region hold flags: the library clears them the first time it sees a workspace address and
  * leaves them clear; after a non-zero mg_device_status, clear them yourself or pass a fresh buffer.
  * out_f32 != 0 selects the fp32 output of mg_matmul_f32.
  */

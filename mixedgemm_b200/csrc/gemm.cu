@@ -49,7 +49,8 @@ struct GemmParams {
   float* Df32;  // when set, the fp32 accumulator is stored here instead of D
   int* status;
   uint32_t tx_a[3], tx_b[3];  // bytes one A / B tile load of the segment signals
-  int dbg;  // timing experiments only (MG_GEMM_DEBUG): 1 = no MMAs, 2 = no loads, 4 = no stores
+  int dbg;  // timing experiments only (MG_GEMM_DEBUG): 1 = no MMAs, 2 = no loads, 4 = no stores,
+            // 8 = stream-K epilogues leave globaltimer stamps behind the flags (8 per CTA, from byte 20480)
   // CTA-pair kernel only: up to four weight matrices that share the activation ("fused N": q/k/v,
   // gate/up).  Problem j owns pair tiles [tile_end[j-1], tile_end[j]) and its own scales / output.
   int nprob;
@@ -60,10 +61,11 @@ struct GemmParams {
   // tile's first stage finishes it, adding the fp32 partials the others leave in sk_partials.
   int streamk;
   int* sk_flags;       // [cluster][cta]: 1 when that CTA's partial is complete; the finisher clears it
-  float* sk_partials;  // [cluster][cta][128 rows][256 columns]
+  float* sk_partials;  // [cluster][cta][4 panels][16 column groups][128 rows][4 columns]
 };
 
 constexpr int kMaxGroup = 4;
+constexpr int kSkFlagStride = 32;  // ints between stream-K flags: one 128-byte line each
 struct GroupMaps {
   CUtensorMap b[kMaxGroup][3];  // weight codes per problem and K segment
   CUtensorMap d[kMaxGroup];     // outputs
@@ -619,6 +621,17 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     const bool issuer = warp == 3 && lane == 0;
     int it = 0;
     Piece pc;
+    unsigned long long* trace = nullptr;
+    if (issuer && p.sk_flags && (p.dbg & 8))
+      trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.sk_flags) + 20480) + (first_tile * 2 + (int)rank) * 8;
+    auto stamp = [&](int i) {
+      if (trace) {
+        unsigned long long ns;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+        trace[i] = ns;
+      }
+    };
+    stamp(0);
     for (int cur = cur0; next_piece(cur, pc); ++it) {
       const int t = pc.tile;
       int prob, m_pt, n_tile;
@@ -637,18 +650,76 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
       wait_parity(tfull_bar, (uint32_t)it & 1u, stop, p.status, 8);
       __syncwarp();
       ptx::tc_fence_after();
+      if (it == 0) stamp(1);
+      if (head) stamp(3);
       if (head) {
-        // the other parts were computed first thing by their clusters; wait (bounded) for them
-        for (int k = 0; k < n_contrib; ++k) {
-          const volatile int* f = p.sk_flags + (size_t)(me + 1 + k) * 2 + rank;
-          const long long t0 = clock64();
-          while (*f == 0 && !*stop) {
-            if (clock64() - t0 > kWaitLimitCycles) { *stop = 1; atomicOr(p.status, 128); }
+        // The other parts were computed first thing by their clusters; wait (bounded) for them.  One
+        // thread polls, with back-off: many threads spinning on a flag starve the store that sets it.
+        if (issuer) {
+          for (int k = 0; k < n_contrib; ++k) {
+            const int* f = p.sk_flags + ((size_t)(me + 1 + k) * 2 + rank) * kSkFlagStride;
+            const long long t0 = clock64();
+            for (;;) {
+              int v;
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+              if (v != 0 || *stop) break;
+              __nanosleep(100);
+              if (clock64() - t0 > kWaitLimitCycles) { *stop = 1; atomicOr(p.status, 128); }
+            }
           }
         }
+        ptx::named_barrier_sync(1, 128);
         __threadfence();
+        stamp(4);
       }
-      float* my_partial = p.sk_partials + ((size_t)(me * 2 + (int)rank) * 128 + trow) * 256;
+      if (!contributor && !head) {
+        // Whole tile.  Drain the accumulator in one go: every 32-column chunk is rounded to bf16 as it
+        // arrives, so the whole 256-column row fits in 128 registers and TMEM goes back to the MMA
+        // warp before the first byte is staged; the staging and the stores then overlap the next
+        // tile's MMAs instead of holding them up.
+        uint32_t pk[128];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r0[32], r1[32];
+          ptx::tmem_ld_32x32(taddr + c * 64, r0);
+          ptx::tmem_ld_32x32(taddr + c * 64 + 32, r1);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r0[k * 2]), __uint_as_float(r0[k * 2 + 1]));
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r1[k * 2]), __uint_as_float(r1[k * 2 + 1]));
+            pk[c * 32 + k] = *reinterpret_cast<uint32_t*>(&h0);
+            pk[c * 32 + 16 + k] = *reinterpret_cast<uint32_t*>(&h1);
+          }
+        }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader);
+        const int m0 = m_pt * 256 + (int)rank * 128;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (issuer) ptx::bulk_wait_group_read<C::NSLOT - 1>();  // the slot's last store has read it
+          ptx::named_barrier_sync(1, 128);
+          const uint32_t slot_addr = base + (uint32_t)(j % C::NSLOT) * C::PANEL_BYTES;
+          const uint32_t prow = slot_addr + trow * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            ptx::sts_v4(prow + ((uint32_t)(c ^ (trow & 7)) << 4), pk[j * 32 + c * 4], pk[j * 32 + c * 4 + 1],
+                        pk[j * 32 + c * 4 + 2], pk[j * 32 + c * 4 + 3]);
+          ptx::fence_proxy_async_smem();
+          ptx::named_barrier_sync(1, 128);
+          if (issuer) {
+            if (m0 < p.M && !*stop && !(p.dbg & 4)) ptx::tma_store_2d(&gm.d[prob], n_tile * 256 + j * 64, m0, slot_addr);
+            ptx::bulk_commit_group();  // one group per panel, also when nothing was stored
+          }
+        }
+        if (it == 0) stamp(7);
+        continue;
+      }
+      // Partials are private scratch, laid out [panel][4-column group][row] in 16-byte units so that a
+      // warp's store (and the finisher's load) covers 512 contiguous bytes; rows beyond M are skipped.
+      uint4* my_partial = reinterpret_cast<uint4*>(p.sk_partials + (size_t)(me * 2 + (int)rank) * 128 * 256) + trow;
+      const bool row_live = m_pt * 256 + (int)rank * 128 + trow < p.M;
 #pragma unroll 1
       for (int j = 0; j < 4; ++j) {
         // the store that last used this staging slot has finished reading it
@@ -665,29 +736,33 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
         }
         if (contributor) {
           // leave the fp32 partial of this row's 64 columns for the finishing cluster
-          uint4* dst = reinterpret_cast<uint4*>(my_partial + j * 64);
+          if (row_live) {
+            uint4* dst = my_partial + (size_t)j * 16 * 128;
 #pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            dst[v] = make_uint4(r0[v * 4], r0[v * 4 + 1], r0[v * 4 + 2], r0[v * 4 + 3]);
-            dst[8 + v] = make_uint4(r1[v * 4], r1[v * 4 + 1], r1[v * 4 + 2], r1[v * 4 + 3]);
+            for (int v = 0; v < 8; ++v) {
+              __stcg(dst + v * 128, make_uint4(r0[v * 4], r0[v * 4 + 1], r0[v * 4 + 2], r0[v * 4 + 3]));
+              __stcg(dst + (8 + v) * 128, make_uint4(r1[v * 4], r1[v * 4 + 1], r1[v * 4 + 2], r1[v * 4 + 3]));
+            }
           }
           if (issuer) ptx::bulk_commit_group();  // keeps the one-group-per-panel count
           continue;
         }
-        for (int k = 0; k < n_contrib; ++k) {
-          const uint4* src = reinterpret_cast<const uint4*>(
-              p.sk_partials + ((size_t)((me + 1 + k) * 2 + (int)rank) * 128 + trow) * 256 + j * 64);
+        if (row_live) {
+          for (int k = 0; k < n_contrib; ++k) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.sk_partials + (size_t)((me + 1 + k) * 2 + (int)rank) * 128 * 256) +
+                               (size_t)j * 16 * 128 + trow;
 #pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            const uint4 a = __ldcg(src + v), b = __ldcg(src + 8 + v);
-            r0[v * 4] = __float_as_uint(__uint_as_float(r0[v * 4]) + __uint_as_float(a.x));
-            r0[v * 4 + 1] = __float_as_uint(__uint_as_float(r0[v * 4 + 1]) + __uint_as_float(a.y));
-            r0[v * 4 + 2] = __float_as_uint(__uint_as_float(r0[v * 4 + 2]) + __uint_as_float(a.z));
-            r0[v * 4 + 3] = __float_as_uint(__uint_as_float(r0[v * 4 + 3]) + __uint_as_float(a.w));
-            r1[v * 4] = __float_as_uint(__uint_as_float(r1[v * 4]) + __uint_as_float(b.x));
-            r1[v * 4 + 1] = __float_as_uint(__uint_as_float(r1[v * 4 + 1]) + __uint_as_float(b.y));
-            r1[v * 4 + 2] = __float_as_uint(__uint_as_float(r1[v * 4 + 2]) + __uint_as_float(b.z));
-            r1[v * 4 + 3] = __float_as_uint(__uint_as_float(r1[v * 4 + 3]) + __uint_as_float(b.w));
+            for (int v = 0; v < 8; ++v) {
+              const uint4 a = __ldcg(src + v * 128), b = __ldcg(src + (8 + v) * 128);
+              r0[v * 4] = __float_as_uint(__uint_as_float(r0[v * 4]) + __uint_as_float(a.x));
+              r0[v * 4 + 1] = __float_as_uint(__uint_as_float(r0[v * 4 + 1]) + __uint_as_float(a.y));
+              r0[v * 4 + 2] = __float_as_uint(__uint_as_float(r0[v * 4 + 2]) + __uint_as_float(a.z));
+              r0[v * 4 + 3] = __float_as_uint(__uint_as_float(r0[v * 4 + 3]) + __uint_as_float(a.w));
+              r1[v * 4] = __float_as_uint(__uint_as_float(r1[v * 4]) + __uint_as_float(b.x));
+              r1[v * 4 + 1] = __float_as_uint(__uint_as_float(r1[v * 4 + 1]) + __uint_as_float(b.y));
+              r1[v * 4 + 2] = __float_as_uint(__uint_as_float(r1[v * 4 + 2]) + __uint_as_float(b.z));
+              r1[v * 4 + 3] = __float_as_uint(__uint_as_float(r1[v * 4 + 3]) + __uint_as_float(b.w));
+            }
           }
         }
         const uint32_t slot_addr = base + (uint32_t)(j % C::NSLOT) * C::PANEL_BYTES;
@@ -711,19 +786,24 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
           ptx::bulk_commit_group();  // one group per panel, also when nothing was stored
         }
       }
+      if (it == 0) stamp(7);
       if (contributor) {
         __threadfence();  // every thread's partial is visible device-wide before the flag goes up
         ptx::named_barrier_sync(1, 128);
         if (issuer) {
-          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.sk_flags + (size_t)me * 2 + rank), "r"(1) : "memory");
+          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.sk_flags + ((size_t)me * 2 + rank) * kSkFlagStride), "r"(1)
+                       : "memory");
+          stamp(2);
         }
       } else if (head) {
+        stamp(5);
         ptx::named_barrier_sync(1, 128);  // all 128 threads have read the partials
         if (issuer)
-          for (int k = 0; k < n_contrib; ++k) p.sk_flags[(size_t)(me + 1 + k) * 2 + rank] = 0;  // ready for the next launch
+          for (int k = 0; k < n_contrib; ++k) p.sk_flags[((size_t)(me + 1 + k) * 2 + rank) * kSkFlagStride] = 0;  // for the next launch
       }
     }
     if (issuer) ptx::bulk_wait_group0();
+    stamp(6);
   }
 
   // ------------------------------------------------------------ teardown
@@ -873,14 +953,18 @@ int launch_gemm(const GemmParams& p, const CUtensorMap* maps, int sms, cudaStrea
   return MG_OK;
 }
 
-// Stream-K scratch: 1 KB of flags, then one 128 x 256 fp32 partial per CTA of up to 74 clusters.
+// Stream-K scratch: one flag per CTA (a cache line each), then one 128 x 256 fp32 partial per CTA of up to 74 clusters.
 constexpr int kSkMaxClusters = 74;
-constexpr size_t kSkFlagBytes = 1024;
+constexpr size_t kSkFlagBytes = 32 * 1024;  // 18.5 KB of flags, then (from 20 KB) the debug time stamps
 constexpr size_t kSkBytes = kSkFlagBytes + (size_t)kSkMaxClusters * 2 * 128 * 256 * sizeof(float);
 
+// Off unless MG_GEMM_STREAMK=1.  Measured on B200, a cluster pays about 5 us for the partial it
+// leaves (its accumulator drains to global memory before the next MMAs may start) and 1.5 us per
+// partial it adds, which is more than the part of a wave stream-K saves on the shapes of a
+// Llama-3 layer (2 to 8 us per GEMM), so whole tiles stay the default.
 bool streamk_wanted() {
   const char* e = std::getenv("MG_GEMM_STREAMK");
-  return !(e && e[0] == '0');
+  return e && e[0] == '1';
 }
 
 // The flags must read 0 before the first launch that uses a scratch buffer; later launches leave
@@ -907,14 +991,16 @@ int launch_pair(GemmParams& p, const CUtensorMap& a0, const CUtensorMap& a1, con
   int clusters = tiles < max_clusters ? tiles : max_clusters;
   const long long units = (long long)tiles * (p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages);
   p.streamk = 0;
-  if (sk_ws && sk_bytes >= kSkBytes && streamk_wanted() && tiles % max_clusters != 0 && units >= max_clusters) {
-    // the tiles do not fill whole waves: deal out (tile, K-stage) units instead of tiles
-    p.streamk = 1;
-    clusters = max_clusters;
-    p.sk_flags = static_cast<int*>(sk_ws);
+  if (sk_ws && sk_bytes >= kSkBytes) {
+    p.sk_flags = static_cast<int*>(sk_ws);  // also where the debug time stamps go
     p.sk_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(sk_ws) + kSkFlagBytes);
-    const int rc = clear_flags_once(sk_ws, st);
-    if (rc != MG_OK) return rc;
+    if (streamk_wanted() && tiles % max_clusters != 0 && units >= max_clusters) {
+      // the tiles do not fill whole waves: deal out (tile, K-stage) units instead of tiles
+      p.streamk = 1;
+      clusters = max_clusters;
+      const int rc = clear_flags_once(sk_ws, st);
+      if (rc != MG_OK) return rc;
+    }
   }
   int variant = 1;
   if (const char* e = std::getenv("MG_GEMM_PAIR_VARIANT")) variant = std::atoi(e);
@@ -991,15 +1077,15 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
   const size_t sk_off = align_up(pl.total, 1024);
   void* sk_ws = nullptr;
   size_t sk_bytes = 0;
-  if (allow_streamk && workspace && mg::aligned(workspace, 1024) && workspace_bytes >= sk_off + kSkBytes &&
-      streamk_wanted()) {
+  if (allow_streamk && workspace && mg::aligned(workspace, 1024) && workspace_bytes >= sk_off + kSkBytes) {
     sk_ws = static_cast<uint8_t*>(workspace) + sk_off;
     sk_bytes = workspace_bytes - sk_off;
   }
-  bool use_pair = !f32_out && C_bf16 == nullptr && N % 256 == 0 && (M > 128 || sk_ws != nullptr);
+  const bool sk = sk_ws != nullptr && streamk_wanted();  // then small problems also fill every SM pair
+  bool use_pair = !f32_out && C_bf16 == nullptr && N % 256 == 0 && (M > 128 || sk);
   const int pair_tiles = ((M + 255) / 256) * (N / 256);
   if (const char* e = std::getenv("MG_GEMM_2CTA")) use_pair = use_pair && std::atoi(e) != 0;
-  else use_pair = use_pair && (sk_ws != nullptr || pair_tiles * 4 >= (di.sm_count / 2) * 3);
+  else use_pair = use_pair && (sk || pair_tiles * 4 >= (di.sm_count / 2) * 3);
   const int bn = use_pair ? 128 : choose_bn(M, N, di.sm_count);  // rows of one B tile load
 
   GemmParams p{};

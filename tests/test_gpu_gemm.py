@@ -76,7 +76,7 @@ def _check(A, B, M, N, split, rows=None, C=None):
     rne = orc.bf16_round(Y32.cpu().numpy())
     if not np.array_equal(y16, rne):
         import os
-        assert os.environ.get("MG_GEMM_STREAMK", "1") != "0", "bf16 output is not RNE(fp32 accumulator)"
+        assert os.environ.get("MG_GEMM_STREAMK", "0") == "1", "bf16 output is not RNE(fp32 accumulator)"
         bad = y16 != rne
         assert bad.mean() < 2e-3, "too many results off the rounded accumulator: %.2e" % bad.mean()
         ulp = np.abs(rne[bad]).astype(np.float64) * 2.0 ** -7 + 1e-30
