@@ -274,12 +274,16 @@ class Job:
             self.gemms(gr)
 
 
-def timed(fn, steps, sync):
+def timed(fn, steps, sync, finish=None):
+    """ms per step by CUDA events on the current stream; `finish` (optional) makes that stream wait
+    for work the step put on other streams before the closing event is recorded."""
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync()
     e0.record()
     for _ in range(steps):
         fn()
+    if finish is not None:
+        finish()
     e1.record()
     sync()
     return e0.elapsed_time(e1) / steps  # ms per step
@@ -499,17 +503,45 @@ def main():
         h2d = sum(t.numel() * 2 for t in hX)
         d2h = sum(t.numel() * 2 for ys in hY for t in ys)
 
+        # Three streams, as a caller with host buffers would run it: uploads, compute and downloads
+        # overlap (PCIe is full duplex), ordered per buffer by events.  Every step uploads all its
+        # activations and downloads all its outputs; the closing event waits for the last download.
+        main_s = torch.cuda.current_stream()
+        in_s, out_s = torch.cuda.Stream(), torch.cuda.Stream()
+        ng = len(job.groups)
+        ev_in = [torch.cuda.Event() for _ in range(ng)]      # activation g is on the device
+        ev_xfree = [torch.cuda.Event() for _ in range(ng)]   # activation g has been quantised
+        ev_done = [torch.cuda.Event() for _ in range(ng)]    # outputs of group g are complete
+        ev_yfree = [torch.cuda.Event() for _ in range(ng)]   # outputs of group g are on the host
+        for g in range(ng):
+            ev_xfree[g].record(main_s)
+            ev_yfree[g].record(main_s)
+
         def e2e_step():
-            for gr, hx, hys in zip(job.groups, hX, hY):
-                gr["X"].copy_(hx, non_blocking=True)
+            for g, (gr, hx, hys) in enumerate(zip(job.groups, hX, hY)):
+                in_s.wait_event(ev_xfree[g])
+                with torch.cuda.stream(in_s):
+                    gr["X"].copy_(hx, non_blocking=True)
+                    ev_in[g].record(in_s)
+                main_s.wait_event(ev_in[g])
                 job.quantize_and_exchange(gr)
+                ev_xfree[g].record(main_s)
+                main_s.wait_event(ev_yfree[g])
                 job.gemms(gr)
-                for (_, _, _, Y), hy in zip(gr["layers"], hys):
-                    hy.copy_(Y, non_blocking=True)
+                ev_done[g].record(main_s)
+                out_s.wait_event(ev_done[g])
+                with torch.cuda.stream(out_s):
+                    for (_, _, _, Y), hy in zip(gr["layers"], hys):
+                        hy.copy_(Y, non_blocking=True)
+                    ev_yfree[g].record(out_s)
+
+        def e2e_finish():
+            main_s.wait_stream(in_s)
+            main_s.wait_stream(out_s)
 
         for _ in range(2):
             e2e_step()
-        e2e_ms = timed(e2e_step, max(3, min(a.steps, 10)), sync)
+        e2e_ms = timed(e2e_step, max(3, min(a.steps, 10)), sync, finish=e2e_finish)
 
     # max over ranks
     if world > 1:
