@@ -119,14 +119,20 @@ int mg_matmul(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, const uin
  * first K/2 (3K/4, K) bytes are the reference's row; the bytes after them are never interpreted.
  *   pitches of mg_reorder_quantize_pitched: {FP4 buffer, FP6 (or second FP4) buffer, FP8 (or third FP4) buffer}
  *   pitches of mg_matmul_pitched:           {AN, BN, AS, BS, AO, BO}
- * mg_matmul_pitched needs workspace only for operands whose pitch does not qualify; when the
- * workspace also has the 19 MB that mg_matmul_pitched_workspace_bytes adds for N % 256 == 0, the
- * CTA-pair kernel runs "stream-K": the launch's (tile, K-stage) units are dealt evenly to the SM
- * pairs, tiles cut that way are completed from fp32 partials in the workspace, so problems whose
- * tile count does not fill whole waves (and decode shapes, M <= 128) keep every SM busy.  Results
- * then differ from the tile-per-cluster order by fp32 re-association only.  The first 19 KB of that
- * region hold flags: the library clears them the first time it sees a workspace address and
- * leaves them clear; after a non-zero mg_device_status, clear them yourself or pass a fresh buffer.
+ * mg_matmul_pitched needs workspace only for operands whose pitch does not qualify.  What
+ * mg_matmul_pitched_workspace_bytes reports on top (64 KB + fp32 partials) lets two modes run;
+ * with a smaller workspace the call still works, without them:
+ *  - split-K: a problem whose 128-row tiles occupy at most half of the SMs and whose K has at least
+ *    32 stages of 128 bytes (decode shapes and narrow weight shards at large K) runs up to eight
+ *    CTAs per tile, each over a range of K; the CTA that arrives last adds the fp32 partials in a
+ *    fixed order and stores the tile.  The result is deterministic and differs from the unsplit
+ *    kernel by fp32 re-association only.  The arrival counters carry a per-launch token, so the
+ *    workspace may hold anything when the call starts.  MG_GEMM_SPLITK=0 in the environment turns
+ *    it off.
+ *  - stream-K on the CTA-pair kernel, only with MG_GEMM_STREAMK=1: the launch's (tile, K-stage)
+ *    units are dealt evenly to the SM pairs and tiles cut that way are completed from fp32
+ *    partials.  The library clears the flags it uses on the call's stream before the launch.
+ * A workspace must not be shared by calls that may run at the same time.
  * out_f32 != 0 selects the fp32 output of mg_matmul_f32.
  */
 size_t mg_code_pitch(int weights, int segment, int kseg);

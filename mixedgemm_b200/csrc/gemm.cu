@@ -19,6 +19,9 @@
 #include <cudaTypedefs.h>
 #include <cuda_bf16.h>
 
+#include <algorithm>
+#include <atomic>
+#include <random>
 #include <cstdlib>
 #include <mutex>
 
@@ -59,6 +62,15 @@ struct GemmParams {
   // Stream-K (CTA-pair kernel): the launch's (tile, K-stage) units are dealt to the clusters as equal
   // contiguous ranges, so a cluster may compute only part of a tile's K.  The cluster that holds a
   // tile's first stage finishes it, adding the fp32 partials the others leave in sk_partials.
+  // Split-K (single-CTA kernel): when a problem has too few tiles to occupy the SMs, `splits` CTAs
+  // share a tile, each over a contiguous range of its K stages.  Each leaves its fp32 partial in
+  // sp_partials and bumps the tile's counter; the CTA that arrives last adds the partials in split
+  // order (so the result does not depend on who was last), stores the tile and clears the counter.
+  int splits;
+  int sp_rows;         // rows per tile in sp_partials (128, or M rounded up to 32 when M <= 96)
+  unsigned long long* sp_counters;  // [tile]: (launch token << 8) | arrivals; the last CTA writes 0
+  unsigned long long sp_token;      // 56 bits, unique per launch: a word with another token counts as 0
+  float* sp_partials;  // [split][tile][column group of 4][sp_rows][4]
   int streamk;
   int* sk_flags;       // [cluster][cta]: 1 when that CTA's partial is complete; the finisher clears it
   float* sk_partials;  // [cluster][cta][4 panels][16 column groups][128 rows][4 columns]
@@ -162,6 +174,11 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
   ptx::grid_dep_wait();  // the prologue above touched no global memory
 
   const int total_tiles = p.tiles_m * p.tiles_n;
+  // work item w = (tile w / splits, split w % splits); split j covers K stages [S j / splits, S (j+1) / splits)
+  const int splits = p.splits;
+  const int total_items = total_tiles * splits;
+  const int S_units = p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages;
+  const int seg_off1 = p.seg[0].nstages, seg_off2 = seg_off1 + p.seg[1].nstages;
 
   // Producer and MMA warps run their loops with all 32 lanes, so that addresses and
   // descriptors are warp-uniform values; one elected lane issues the asynchronous operations.
@@ -170,7 +187,9 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
     const bool leader = ptx::elect_one();
     int stage = 0;
     uint32_t phase = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    for (int w = blockIdx.x; w < total_items; w += gridDim.x) {
+      const int t = w / splits, split = w - t * splits;
+      const int u0 = S_units * split / splits, u1 = S_units * (split + 1) / splits;
       const int m_tile = t % p.tiles_m, n_tile = t / p.tiles_m;
 #pragma unroll 1
       for (int seg = 0; seg < 3; ++seg) {
@@ -181,8 +200,10 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
                                         : (seg == 1 ? p.tx_a[1] + p.tx_b[1] : p.tx_a[2] + p.tx_b[2]);
         const uint8_t* sfa_row = sp.sfa + (size_t)m_tile * sp.katoms * 512;
         const uint8_t* sfb_row = sp.sfb + (size_t)n_tile * C::NB * sp.katoms * 512;
+        const int so = seg == 0 ? 0 : (seg == 1 ? seg_off1 : seg_off2);
+        const int s_lo = max(u0 - so, 0), s_hi = min(u1 - so, sp.nstages);
 #pragma unroll 1
-        for (int s = 0; s < sp.nstages; ++s) {
+        for (int s = s_lo; s < s_hi; ++s) {
           wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, 1);
           const int atom0 = seg == 0 ? 2 * s : s;
           const int natoms = seg == 0 ? min(2, sp.katoms - atom0) : 1;
@@ -217,7 +238,9 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
     int stage = 0;
     uint32_t phase = 0, slot = 0;
     int it = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+    for (int w = blockIdx.x; w < total_items; w += gridDim.x, ++it) {
+      const int split = w % splits;
+      const int u0 = S_units * split / splits, u1 = S_units * (split + 1) / splits;
       const int acc = it % C::ACC;
       const uint32_t acc_phase = (uint32_t)(it / C::ACC) & 1u;
       wait_parity(tempty_bar(acc), acc_phase ^ 1u, stop, p.status, 4);
@@ -228,8 +251,10 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
       for (int seg = 0; seg < 3; ++seg) {
         const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
         const uint32_t id0 = seg == 0 ? kIdesc[0] : (seg == 1 ? kIdesc[1] : kIdesc[2]);
+        const int so = seg == 0 ? 0 : (seg == 1 ? seg_off1 : seg_off2);
+        const int s_lo = max(u0 - so, 0), s_hi = min(u1 - so, sp.nstages);
 #pragma unroll 1
-        for (int s = 0; s < sp.nstages; ++s) {
+        for (int s = s_lo; s < s_hi; ++s) {
           wait_parity(full_bar(stage), phase, stop, p.status, 2);
           ptx::tc_fence_after();
           const uint32_t sbase = base + stage * C::STAGE_BYTES;
@@ -284,61 +309,135 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
   } else {
     // ------------------------------------------------------------ epilogue (4 warps)
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const int trow = q * 32 + lane;
+    volatile int* arrivals = reinterpret_cast<volatile int*>(tmem_holder + 2);  // split-K: counter value seen
+    const bool issuer = warp == 2 && lane == 0;
     int it = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+    for (int w = blockIdx.x; w < total_items; w += gridDim.x, ++it) {
+      const int t = w / splits, split = w - t * splits;
       const int m_tile = t % p.tiles_m, n_tile = t / p.tiles_m;
       const int acc = it % C::ACC;
       const uint32_t acc_phase = (uint32_t)(it / C::ACC) & 1u;
       wait_parity(tfull_bar(acc), acc_phase, stop, p.status, 8);
       __syncwarp();
       ptx::tc_fence_after();
-      const int row = m_tile * BM + q * 32 + lane;
+      const int row = m_tile * BM + trow;
       const bool store = row < p.M && !(p.dbg & 4) && !*stop;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * BN;
       const size_t goff = (size_t)row * p.ldd + (size_t)n_tile * BN;
+      // 32 accumulator columns of this thread's row -> (+C) -> fp32 or bf16 output
+      auto emit = [&](uint32_t (&r)[32], int c) {
+        if (p.C != nullptr) {
+          const uint4* cp = reinterpret_cast<const uint4*>(p.C + goff + c * 32);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint4 cv = cp[v];
+            const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              r[v * 8 + k * 2] = __float_as_uint(__uint_as_float(r[v * 8 + k * 2]) + __uint_as_float(cw[k] << 16));
+              r[v * 8 + k * 2 + 1] =
+                  __float_as_uint(__uint_as_float(r[v * 8 + k * 2 + 1]) + __uint_as_float(cw[k] & 0xFFFF0000u));
+            }
+          }
+        }
+        if (p.Df32 != nullptr) {
+          uint4* fp = reinterpret_cast<uint4*>(p.Df32 + goff + c * 32);
+#pragma unroll
+          for (int v = 0; v < 8; ++v) fp[v] = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+        } else {
+          uint4* dp = reinterpret_cast<uint4*>(p.D + goff + c * 32);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint32_t ow[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + k * 2]),
+                                                       __uint_as_float(r[v * 8 + k * 2 + 1]));
+              ow[k] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            dp[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+          }
+        }
+      };
+      if (splits == 1) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(taddr + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (store) emit(r, c);
+        }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+        continue;
+      }
+      // ---- split-K: leave this CTA's partial (16-byte units, [column group][row]: a warp stores 512
+      // contiguous bytes), count the arrival, and let the last CTA of the tile add and store
+      const size_t tile_units = (size_t)(BN / 4) * p.sp_rows;
+      uint4* part = reinterpret_cast<uint4*>(p.sp_partials) + ((size_t)split * total_tiles + t) * tile_units + trow;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(taddr + c * 32, r);
         ptx::tmem_ld_wait();
         if (store) {
-          if (p.C != nullptr) {
-            const uint4* cp = reinterpret_cast<const uint4*>(p.C + goff + c * 32);
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const uint4 cv = cp[v];
-              const uint32_t w[4] = {cv.x, cv.y, cv.z, cv.w};
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                r[v * 8 + k * 2] = __float_as_uint(__uint_as_float(r[v * 8 + k * 2]) + __uint_as_float(w[k] << 16));
-                r[v * 8 + k * 2 + 1] =
-                    __float_as_uint(__uint_as_float(r[v * 8 + k * 2 + 1]) + __uint_as_float(w[k] & 0xFFFF0000u));
-              }
-            }
-          }
-          if (p.Df32 != nullptr) {
-            uint4* fp = reinterpret_cast<uint4*>(p.Df32 + goff + c * 32);
-#pragma unroll
-            for (int v = 0; v < 8; ++v) fp[v] = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
-          } else {
-            uint4* dp = reinterpret_cast<uint4*>(p.D + goff + c * 32);
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint32_t w[4];
-#pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + k * 2]),
-                                                         __uint_as_float(r[v * 8 + k * 2 + 1]));
-                w[k] = *reinterpret_cast<uint32_t*>(&h);
-              }
-              dp[v] = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          }
+          for (int v = 0; v < 8; ++v)
+            __stcg(part + (size_t)(c * 8 + v) * p.sp_rows, make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]));
         }
       }
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+      __threadfence();  // the partial is visible device-wide before the arrival is counted
+      ptx::named_barrier_sync(1, 128);
+      if (issuer) {
+        // count this arrival.  The workspace is the caller's and may hold anything: a word that does
+        // not carry this launch's token is taken as "nobody has arrived yet".
+        unsigned long long* cw = p.sp_counters + t;
+        unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(cw);
+        int idx = -1;
+        for (int tries = 0; tries < 4096; ++tries) {
+          const bool mine = (cur >> 8) == p.sp_token;
+          const unsigned long long want = mine ? cur + 1 : ((p.sp_token << 8) | 1ull);
+          const unsigned long long prev = atomicCAS(cw, cur, want);
+          if (prev == cur) {
+            idx = mine ? (int)(cur & 0xFF) : 0;
+            break;
+          }
+          cur = prev;
+        }
+        if (idx < 0) atomicOr(p.status, 256);
+        *arrivals = idx;
+      }
+      ptx::named_barrier_sync(1, 128);
+      if (*arrivals == splits - 1) {
+        __threadfence();
+        if (store) {
+          const uint4* src0 = reinterpret_cast<const uint4*>(p.sp_partials) + (size_t)t * tile_units + trow;
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0;  // +0.0f
+            for (int sp = 0; sp < splits; ++sp) {
+              const uint4* src = src0 + (size_t)sp * total_tiles * tile_units + (size_t)(c * 8) * p.sp_rows;
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                const uint4 a = __ldcg(src + (size_t)v * p.sp_rows);
+                r[v * 4] = __float_as_uint(__uint_as_float(r[v * 4]) + __uint_as_float(a.x));
+                r[v * 4 + 1] = __float_as_uint(__uint_as_float(r[v * 4 + 1]) + __uint_as_float(a.y));
+                r[v * 4 + 2] = __float_as_uint(__uint_as_float(r[v * 4 + 2]) + __uint_as_float(a.z));
+                r[v * 4 + 3] = __float_as_uint(__uint_as_float(r[v * 4 + 3]) + __uint_as_float(a.w));
+              }
+            }
+            emit(r, c);
+          }
+        }
+        if (issuer) p.sp_counters[t] = 0;  // every split has arrived: ready for the next launch
+      }
     }
   }
 
@@ -946,17 +1045,45 @@ int launch_gemm(const GemmParams& p, const CUtensorMap* maps, int sms, cudaStrea
   using C = Cfg<BN>;
   auto kern = mixed_gemm_kernel<BN>;
   MG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
-  const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sms ? tiles : sms;
+  const int items = p.tiles_m * p.tiles_n * p.splits;
+  const int grid = items < sms ? items : sms;
   MG_CUDA_TRY(mg::launch_kernel(kern, dim3(grid), dim3(kThreads), C::SMEM, st, p, maps[0], maps[1], maps[2], maps[3],
                                 maps[4], maps[5]));
   return MG_OK;
 }
 
-// Stream-K scratch: one flag per CTA (a cache line each), then one 128 x 256 fp32 partial per CTA of up to 74 clusters.
+// Scratch behind the padded copies: a 64 KB zone that must read zero between launches (stream-K
+// flags, one cache line each, from byte 0; debug time stamps from 20 KB; split-K tile counters from
+// 32 KB), then fp32 partials: one 128 x 256 block per CTA of up to 74 clusters for stream-K, or
+// [split][tile][column group][row] for split-K.  A launch uses one of the two, never both.
 constexpr int kSkMaxClusters = 74;
-constexpr size_t kSkFlagBytes = 32 * 1024;  // 18.5 KB of flags, then (from 20 KB) the debug time stamps
+constexpr size_t kSkFlagBytes = 64 * 1024;
+constexpr size_t kSpCounterOff = 32 * 1024;
+constexpr int kSpMaxTiles = (int)((kSkFlagBytes - kSpCounterOff) / sizeof(unsigned long long));
 constexpr size_t kSkBytes = kSkFlagBytes + (size_t)kSkMaxClusters * 2 * 128 * 256 * sizeof(float);
+
+// Split-K plan of the single-CTA kernel: only when the tiles occupy at most half of the SMs, each
+// split keeps at least 16 K stages (below that the partial round trip through L2 costs more than
+// the shorter K loop saves: 12.6 against 8.9 us at 16 x 4096 x 4096), at most eight splits.  MG_GEMM_SPLITK=0 turns it off, =n forces n.
+struct SplitPlan {
+  int splits, rows;
+  size_t bytes;  // fp32 partials
+};
+SplitPlan plan_splitk(int M, int N, int s_units, int bn, int sms) {
+  SplitPlan sp{1, 128, 0};
+  const int tiles_m = (M + BM - 1) / BM, tiles = tiles_m * (N / bn);
+  int want = -1;
+  if (const char* e = std::getenv("MG_GEMM_SPLITK")) want = std::atoi(e);
+  if (want == 0 || tiles > kSpMaxTiles) return sp;
+  int splits = std::min(std::min(sms / tiles, s_units / 16), 8);  // the arrival count has 8 bits
+  if (tiles * 2 > sms) splits = 1;
+  if (want > 0) splits = std::min(std::min(want, s_units), 64);
+  if (splits < 2) return sp;
+  sp.splits = splits;
+  sp.rows = (tiles_m == 1 && M <= 96) ? (M + 31) / 32 * 32 : 128;
+  sp.bytes = (size_t)splits * tiles * sp.rows * bn * sizeof(float);
+  return sp;
+}
 
 // Off unless MG_GEMM_STREAMK=1.  Measured on B200, a cluster pays about 5 us for the partial it
 // leaves (its accumulator drains to global memory before the next MMAs may start) and 1.5 us per
@@ -967,23 +1094,10 @@ bool streamk_wanted() {
   return e && e[0] == '1';
 }
 
-// The flags must read 0 before the first launch that uses a scratch buffer; later launches leave
-// them 0.  A buffer address not seen before on this device is cleared once, on the caller's stream.
-int clear_flags_once(void* flags, cudaStream_t st) {
-  static std::mutex mu;
-  static void* seen[64][8];
-  static int next[64];
-  int dev = 0;
-  MG_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return MG_ERR_DEVICE;
-  std::lock_guard<std::mutex> lk(mu);
-  for (void* q : seen[dev])
-    if (q == flags) return MG_OK;
-  MG_CUDA_TRY(cudaMemsetAsync(flags, 0, kSkFlagBytes, st));
-  seen[dev][next[dev]++ % 8] = flags;
-  return MG_OK;
-}
-
+// Stream-K flags must read 0 when a launch starts.  Kernels leave them 0, but the workspace is the
+// caller's and may have held anything since, so the bytes a launch will use are cleared on its
+// stream every time (a memset node of at most 19 KB).  Split-K counters need no clearing: they
+// carry a per-launch token.
 int launch_pair(GemmParams& p, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& a2,
                 const GroupMaps& gm, int sms, void* sk_ws, size_t sk_bytes, cudaStream_t st) {
   const int tiles = p.tile_end[p.nprob - 1];
@@ -998,8 +1112,7 @@ int launch_pair(GemmParams& p, const CUtensorMap& a0, const CUtensorMap& a1, con
       // the tiles do not fill whole waves: deal out (tile, K-stage) units instead of tiles
       p.streamk = 1;
       clusters = max_clusters;
-      const int rc = clear_flags_once(sk_ws, st);
-      if (rc != MG_OK) return rc;
+      MG_CUDA_TRY(cudaMemsetAsync(sk_ws, 0, (size_t)clusters * 2 * kSkFlagStride * sizeof(int), st));
     }
   }
   int variant = 1;
@@ -1077,11 +1190,12 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
   const size_t sk_off = align_up(pl.total, 1024);
   void* sk_ws = nullptr;
   size_t sk_bytes = 0;
-  if (allow_streamk && workspace && mg::aligned(workspace, 1024) && workspace_bytes >= sk_off + kSkBytes) {
+  if (workspace && mg::aligned(workspace, 1024) && workspace_bytes >= sk_off + kSkFlagBytes) {
     sk_ws = static_cast<uint8_t*>(workspace) + sk_off;
     sk_bytes = workspace_bytes - sk_off;
   }
-  const bool sk = sk_ws != nullptr && streamk_wanted();  // then small problems also fill every SM pair
+  // stream-K: then small problems also fill every SM pair
+  const bool sk = allow_streamk && sk_ws != nullptr && sk_bytes >= kSkBytes && streamk_wanted();
   bool use_pair = !f32_out && C_bf16 == nullptr && N % 256 == 0 && (M > 128 || sk);
   const int pair_tiles = ((M + 255) / 256) * (N / 256);
   if (const char* e = std::getenv("MG_GEMM_2CTA")) use_pair = use_pair && std::atoi(e) != 0;
@@ -1134,7 +1248,19 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
     }
     p.nprob = 1;
     p.tile_end[0] = pair_tiles;
-    return launch_pair(p, maps[0], maps[2], maps[4], gm, di.sm_count, sk_ws, sk_bytes, st);
+    return launch_pair(p, maps[0], maps[2], maps[4], gm, di.sm_count, allow_streamk ? sk_ws : nullptr, sk_bytes, st);
+  }
+  p.splits = 1;
+  if (sk_ws) {
+    const SplitPlan sp = plan_splitk(M, N, p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages, bn, di.sm_count);
+    if (sp.splits > 1 && sk_bytes >= kSkFlagBytes + sp.bytes) {
+      p.splits = sp.splits;
+      p.sp_rows = sp.rows;
+      p.sp_counters = reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(sk_ws) + kSpCounterOff);
+      p.sp_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(sk_ws) + kSkFlagBytes);
+      static std::atomic<unsigned long long> token{std::random_device{}() | 1ull};
+      p.sp_token = (token.fetch_add(0x9E3779B97F4A7C15ull) >> 8) | 1ull;  // 56 bits, never 0
+    }
   }
   return bn == 256 ? launch_gemm<256>(p, maps, di.sm_count, st) : launch_gemm<128>(p, maps, di.sm_count, st);
 }
@@ -1160,8 +1286,15 @@ extern "C" int mg_matmul_pitched(const uint8_t* AN, const uint8_t* BN_, const ui
 extern "C" size_t mg_matmul_pitched_workspace_bytes(int M, int N, int KN, int KS, int KO, const size_t* pitches) {
   if (M <= 0 || N <= 0 || KN < 0 || KS < 0 || KO < 0) return 0;
   const size_t need = make_plan(M, N, KN, KS, KO, pitches).total;
-  // what the CTA-pair kernel wants on top for stream-K; a smaller workspace still works, without it
-  return N % 256 == 0 ? align_up(need, 1024) + kSkBytes : need;
+  // On top: what stream-K (CTA-pair kernel) or split-K (single-CTA kernel, few tiles) would use.
+  // A smaller workspace still works, without them.
+  mg::DeviceInfo di;
+  const int sms = mg::device_info(&di) == MG_OK ? di.sm_count : 148;
+  const int s_units = (KN + 255) / 256 + (KS + 127) / 128 + (KO + 127) / 128;
+  size_t extra = N % 256 == 0 ? kSkBytes - kSkFlagBytes : 0;
+  for (int bn : {128, 256})
+    if (N % bn == 0) extra = std::max(extra, plan_splitk(M, N, s_units, bn, sms).bytes);
+  return align_up(need, 1024) + kSkFlagBytes + extra;
 }
 
 extern "C" int mg_matmul_f32(const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,

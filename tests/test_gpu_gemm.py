@@ -277,3 +277,38 @@ def test_stream_k(M, N, split, monkeypatch):
     monkeypatch.setenv("MG_GEMM_STREAMK", "1")
     rows = None if M * N <= 1 << 20 else np.unique(np.concatenate([[0, M - 1], np.random.default_rng(0).integers(0, M, 30)]))
     _check(A, B, M, N, split, rows=rows)
+
+
+@pytest.mark.parametrize("M,N,split,force", [
+    (16, 4096, (8960, 4928, 448), None), (384, 512, (8960, 4928, 448), None), (16, 4096, (2560, 1408, 128), "4"),
+    (128, 1024, (2560, 1408, 128), "6"), (100, 768, (2560, 1408, 128), "7"), (300, 256, (2560, 1408, 128), "5"),
+    (1, 128, (256, 128, 128), "3"), (97, 512, (1280, 704, 64), "5"), (16, 14336, (2560, 1408, 128), "2")])
+def test_split_k(M, N, split, force, monkeypatch):
+    """Problems with few tiles (decode shapes, narrow weight shards) run several CTAs per tile of the
+    single-CTA kernel, each over a range of K stages; the CTA that arrives last adds the fp32
+    partials in split order.  Same bounds against the oracle, bf16 == RNE(fp32 result) exactly,
+    the same bytes on every call (the counters are left clear, the sum order is fixed), within one
+    bf16 step of the unsplit kernel, with and without the C addend."""
+    import mixedgemm_b200 as mg
+    if force is not None:
+        monkeypatch.setenv("MG_GEMM_SPLITK", force)
+    A, B = _quantise(M, N, sum(split), split, seed=3 * M + N)
+    args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+    _check(A, B, M, N, split)
+    C = (torch.randn(M, N, generator=torch.Generator().manual_seed(5)) * 0.5).to(torch.bfloat16).cuda()
+    _check(A, B, M, N, split, C=C)
+    y1 = mg.matmul(*args)
+    y2 = mg.matmul(*args)
+    # the scratch is the caller's: whatever it holds when a launch starts must not matter
+    from mixedgemm_b200 import api
+    for buf in api._workspaces.values():
+        buf.fill_(0xAB)
+    y3 = mg.matmul(*args)
+    monkeypatch.setenv("MG_GEMM_SPLITK", "0")
+    y0 = mg.matmul(*args)
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    assert torch.equal(y1.view(torch.int16), y2.view(torch.int16))
+    assert torch.equal(y1.view(torch.int16), y3.view(torch.int16))
+    d = (y1.float() - y0.float()).abs()
+    assert torch.all(d <= y0.float().abs() * 2.0 ** -7 + 1e-30)
