@@ -108,9 +108,10 @@ __device__ __forceinline__ void wait_parity(uint32_t bar, uint32_t parity, volat
 
 template <int BN>
 struct Cfg {
-  static constexpr int STAGES = BN == 128 ? 6 : 4;
-  static constexpr int ACC = BN == 128 ? 2 : 1;
-  static constexpr int NB = BN / 128;
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : (BN == 64 ? 8 : 10));
+  static constexpr int ACC = BN == 256 ? 1 : 2;
+  static constexpr int NB = BN >= 128 ? BN / 128 : 1;
+  static constexpr int CHUNKS = (BN + 31) / 32;  // 32-column reads of the accumulator
   static constexpr uint32_t A_BYTES = BM * 128;
   static constexpr uint32_t B_BYTES = BN * 128;
   static constexpr uint32_t SFA_BYTES = 1024;      // up to two atoms
@@ -122,7 +123,12 @@ struct Cfg {
   static_assert(SF_COL0 + 2 * SF_SLOT_COLS <= kTmemCols, "tensor memory budget");
 };
 
-template <int BN>
+// SWAP = true is the decode form (M <= 128): the weights are the MMA's 128-row operand and the
+// activations its BN-column operand (BN = M rounded up to 16 / 32 / 64 / 128), so the tensor core
+// spends N x BN instead of N x 128 work on M real rows and a stage carries BN instead of 128
+// activation rows.  p.tiles_m then counts 128-row weight tiles, p.tiles_n is 1, the host swaps the
+// tensor maps, scale pointers and byte counts, and the epilogue stores the tile transposed.
+template <int BN, bool SWAP>
 __global__ void __launch_bounds__(kThreads, 1)
 mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
                   const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmA1,
@@ -233,8 +239,8 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
     // instruction descriptors: scale type UE8M0, M = 128, N = BN, both operands K-major
     constexpr uint32_t kCommon = ((uint32_t)(BN >> 3) << 17) | (1u << 23) | ((uint32_t)(BM >> 4) << 24);
     constexpr uint32_t kIdesc[3] = {kCommon | (1u << 7) | (1u << 10),   // mxf4: E2M1 x E2M1
-                                    kCommon | (4u << 7) | (5u << 10),   // E3M2 x E2M1
-                                    kCommon | (0u << 7) | (5u << 10)};  // E4M3 x E2M1
+                                    SWAP ? kCommon | (5u << 7) | (4u << 10) : kCommon | (4u << 7) | (5u << 10),   // E3M2, E2M1
+                                    SWAP ? kCommon | (5u << 7) | (0u << 10) : kCommon | (0u << 7) | (5u << 10)};  // E4M3, E2M1
     int stage = 0;
     uint32_t phase = 0, slot = 0;
     int it = 0;
@@ -321,12 +327,27 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
       wait_parity(tfull_bar(acc), acc_phase, stop, p.status, 8);
       __syncwarp();
       ptx::tc_fence_after();
-      const int row = m_tile * BM + trow;
-      const bool store = row < p.M && !(p.dbg & 4) && !*stop;
+      const int row = m_tile * BM + trow;  // output row, or (SWAP) output column
+      const bool store = (SWAP || row < p.M) && !(p.dbg & 4) && !*stop;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * BN;
       const size_t goff = (size_t)row * p.ldd + (size_t)n_tile * BN;
       // 32 accumulator columns of this thread's row -> (+C) -> fp32 or bf16 output
       auto emit = [&](uint32_t (&r)[32], int c) {
+        if constexpr (SWAP) {
+          // r[j] belongs to output row m = c * 32 + j, column `row`: a warp writes 64 contiguous bytes per m
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int m = c * 32 + j;
+            if (m < p.M) {
+              const size_t o = (size_t)m * p.ldd + row;
+              float v = __uint_as_float(r[j]);
+              if (p.C != nullptr) v += __bfloat162float(p.C[o]);
+              if (p.Df32 != nullptr) p.Df32[o] = v;
+              else p.D[o] = __float2bfloat16_rn(v);
+            }
+          }
+          return;
+        }
         if (p.C != nullptr) {
           const uint4* cp = reinterpret_cast<const uint4*>(p.C + goff + c * 32);
 #pragma unroll
@@ -362,7 +383,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
       };
       if (splits == 1) {
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = 0; c < C::CHUNKS; ++c) {
           uint32_t r[32];
           ptx::tmem_ld_32x32(taddr + c * 32, r);
           ptx::tmem_ld_wait();
@@ -378,14 +399,15 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
       const size_t tile_units = (size_t)(BN / 4) * p.sp_rows;
       uint4* part = reinterpret_cast<uint4*>(p.sp_partials) + ((size_t)split * total_tiles + t) * tile_units + trow;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < C::CHUNKS; ++c) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(taddr + c * 32, r);
         ptx::tmem_ld_wait();
         if (store) {
 #pragma unroll
           for (int v = 0; v < 8; ++v)
-            __stcg(part + (size_t)(c * 8 + v) * p.sp_rows, make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]));
+            if (c * 8 + v < BN / 4)
+              __stcg(part + (size_t)(c * 8 + v) * p.sp_rows, make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]));
         }
       }
       ptx::tc_fence_before();
@@ -418,7 +440,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
         if (store) {
           const uint4* src0 = reinterpret_cast<const uint4*>(p.sp_partials) + (size_t)t * tile_units + trow;
 #pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
+          for (int c = 0; c < C::CHUNKS; ++c) {
             uint32_t r[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = 0;  // +0.0f
@@ -426,6 +448,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
               const uint4* src = src0 + (size_t)sp * total_tiles * tile_units + (size_t)(c * 8) * p.sp_rows;
 #pragma unroll
               for (int v = 0; v < 8; ++v) {
+                if (c * 8 + v >= BN / 4) continue;
                 const uint4 a = __ldcg(src + (size_t)v * p.sp_rows);
                 r[v * 4] = __float_as_uint(__uint_as_float(r[v * 4]) + __uint_as_float(a.x));
                 r[v * 4 + 1] = __float_as_uint(__uint_as_float(r[v * 4 + 1]) + __uint_as_float(a.y));
@@ -1040,10 +1063,10 @@ int choose_bn(int M, int N, int sms) {
   return eff(256, 1.0) >= eff(128, 0.92) ? 256 : 128;
 }
 
-template <int BN>
+template <int BN, bool SWAP = false>
 int launch_gemm(const GemmParams& p, const CUtensorMap* maps, int sms, cudaStream_t st) {
   using C = Cfg<BN>;
-  auto kern = mixed_gemm_kernel<BN>;
+  auto kern = mixed_gemm_kernel<BN, SWAP>;
   MG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
   const int items = p.tiles_m * p.tiles_n * p.splits;
   const int grid = items < sms ? items : sms;
@@ -1069,9 +1092,22 @@ struct SplitPlan {
   int splits, rows;
   size_t bytes;  // fp32 partials
 };
-SplitPlan plan_splitk(int M, int N, int s_units, int bn, int sms) {
+// True when the decode form of the single-CTA kernel takes the problem.  Measured on B200 it wins
+// for M <= 32 when there are many weight tiles or a long K (16 x 14336 x 4096: 11.2 against 13.8 us,
+// 16 x 8192 x 28672: 28.1 against 37.5 us) and loses when M > 32, where its element-wise transposed
+// stores dominate (128 x 4096 x 4096: 16.3 against 9.8 us), or when the problem is a handful of
+// short tiles (16 x 4096 x 4096: 9.9 against 8.9 us).  MG_GEMM_SWAP=0 / 1 turns it off / on for every
+// M <= 128.
+bool swap_wanted(int M, int N, int s_units) {
+  if (M > 128 || N % 128 != 0) return false;
+  if (const char* e = std::getenv("MG_GEMM_SWAP")) return e[0] != '0';
+  return M <= 32 && (N / 128 >= 64 || s_units >= 32);
+}
+int swap_bn(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
+
+SplitPlan plan_splitk(int M, int N, int s_units, int bn, int sms, bool swap) {
   SplitPlan sp{1, 128, 0};
-  const int tiles_m = (M + BM - 1) / BM, tiles = tiles_m * (N / bn);
+  const int tiles_m = (M + BM - 1) / BM, tiles = swap ? N / 128 : tiles_m * (N / bn);
   int want = -1;
   if (const char* e = std::getenv("MG_GEMM_SPLITK")) want = std::atoi(e);
   if (want == 0 || tiles > kSpMaxTiles) return sp;
@@ -1080,7 +1116,7 @@ SplitPlan plan_splitk(int M, int N, int s_units, int bn, int sms) {
   if (want > 0) splits = std::min(std::min(want, s_units), 64);
   if (splits < 2) return sp;
   sp.splits = splits;
-  sp.rows = (tiles_m == 1 && M <= 96) ? (M + 31) / 32 * 32 : 128;
+  sp.rows = (!swap && tiles_m == 1 && M <= 96) ? (M + 31) / 32 * 32 : 128;
   sp.bytes = (size_t)splits * tiles * sp.rows * bn * sizeof(float);
   return sp;
 }
@@ -1200,17 +1236,19 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
   const int pair_tiles = ((M + 255) / 256) * (N / 256);
   if (const char* e = std::getenv("MG_GEMM_2CTA")) use_pair = use_pair && std::atoi(e) != 0;
   else use_pair = use_pair && (sk || pair_tiles * 4 >= (di.sm_count / 2) * 3);
-  const int bn = use_pair ? 128 : choose_bn(M, N, di.sm_count);  // rows of one B tile load
+  const bool swap = !use_pair && swap_wanted(M, N, (KN + 255) / 256 + (KS + 127) / 128 + (KO + 127) / 128);
+  // rows of one load of the MMA's column operand: weights, or (decode form) activations
+  const int bn = use_pair ? 128 : (swap ? swap_bn(M) : choose_bn(M, N, di.sm_count));
 
   GemmParams p{};
   p.M = M;
   p.N = N;
   p.ldd = ldd;
-  p.tiles_m = (M + BM - 1) / BM;
-  p.tiles_n = N / bn;
-  p.seg[0] = {KN, (KN + 255) / 256, (KN + 127) / 128, SFAN, SFBN};
-  p.seg[1] = {KS, (KS + 127) / 128, (KS + 127) / 128, SFAS, SFBS};
-  p.seg[2] = {KO, (KO + 127) / 128, (KO + 127) / 128, SFAO, SFBO};
+  p.tiles_m = swap ? N / BM : (M + BM - 1) / BM;
+  p.tiles_n = swap ? 1 : N / bn;
+  p.seg[0] = {KN, (KN + 255) / 256, (KN + 127) / 128, swap ? SFBN : SFAN, swap ? SFAN : SFBN};
+  p.seg[1] = {KS, (KS + 127) / 128, (KS + 127) / 128, swap ? SFBS : SFAS, swap ? SFAS : SFBS};
+  p.seg[2] = {KO, (KO + 127) / 128, (KO + 127) / 128, swap ? SFBO : SFAO, swap ? SFAO : SFBO};
   p.C = static_cast<const __nv_bfloat16*>(C_bf16);
   p.D = f32_out ? nullptr : static_cast<__nv_bfloat16*>(D_bf16);
   p.Df32 = f32_out ? static_cast<float*>(D_bf16) : nullptr;
@@ -1220,6 +1258,10 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
   p.tx_a[0] = BM * 128;       p.tx_b[0] = (uint32_t)bn * 128;
   p.tx_a[1] = BM * 96;        p.tx_b[1] = (uint32_t)bn * 64;
   p.tx_a[2] = BM * 128;       p.tx_b[2] = (uint32_t)bn * 64;
+  if (swap) {  // 128 weight rows (E2M1 in every segment) against bn activation rows
+    p.tx_a[1] = BM * 64;      p.tx_b[1] = (uint32_t)bn * 96;
+    p.tx_a[2] = BM * 64;      p.tx_b[2] = (uint32_t)bn * 128;
+  }
 
   if (const char* e = std::getenv("MG_GEMM_DEBUG")) p.dbg = std::atoi(e);
 
@@ -1228,15 +1270,19 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
   const int first = KN ? 0 : (KS ? 1 : 2);
   for (int seg = 0; seg < 3; ++seg) {
     const int s = (seg == 0 ? KN : seg == 1 ? KS : KO) ? seg : first;
+    // activations go to map 2 seg, weights to 2 seg + 1; the decode form hands them over swapped
+    CUtensorMap* ma = &maps[seg * 2 + (swap ? 1 : 0)];
+    CUtensorMap* mb = &maps[seg * 2 + (swap ? 0 : 1)];
+    const int box_a = swap ? bn : BM, box_b = swap ? BM : bn;
     if (s == 0) {
-      if ((rc = make_map(&maps[seg * 2], CU_TENSOR_MAP_DATA_TYPE_UINT8, AN, KN / 2, M, pl.pitch[0], 128, BM))) return rc;
-      if ((rc = make_map(&maps[seg * 2 + 1], CU_TENSOR_MAP_DATA_TYPE_UINT8, BN_, KN / 2, N, pl.pitch[1], 128, bn))) return rc;
+      if ((rc = make_map(ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, AN, KN / 2, M, pl.pitch[0], 128, box_a))) return rc;
+      if ((rc = make_map(mb, CU_TENSOR_MAP_DATA_TYPE_UINT8, BN_, KN / 2, N, pl.pitch[1], 128, box_b))) return rc;
     } else if (s == 1) {
-      if ((rc = make_map(&maps[seg * 2], CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, AS, pl.ksp, M, pl.pitch[2], 128, BM))) return rc;
-      if ((rc = make_map(&maps[seg * 2 + 1], CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, BS, pl.ksp, N, pl.pitch[3], 128, bn))) return rc;
+      if ((rc = make_map(ma, CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B, AS, pl.ksp, M, pl.pitch[2], 128, box_a))) return rc;
+      if ((rc = make_map(mb, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, BS, pl.ksp, N, pl.pitch[3], 128, box_b))) return rc;
     } else {
-      if ((rc = make_map(&maps[seg * 2], CU_TENSOR_MAP_DATA_TYPE_UINT8, AO, pl.kop, M, pl.pitch[4], 128, BM))) return rc;
-      if ((rc = make_map(&maps[seg * 2 + 1], CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, BO, pl.kop, N, pl.pitch[5], 128, bn))) return rc;
+      if ((rc = make_map(ma, CU_TENSOR_MAP_DATA_TYPE_UINT8, AO, pl.kop, M, pl.pitch[4], 128, box_a))) return rc;
+      if ((rc = make_map(mb, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, BO, pl.kop, N, pl.pitch[5], 128, box_b))) return rc;
     }
   }
   if (use_pair) {
@@ -1252,7 +1298,7 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
   }
   p.splits = 1;
   if (sk_ws) {
-    const SplitPlan sp = plan_splitk(M, N, p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages, bn, di.sm_count);
+    const SplitPlan sp = plan_splitk(M, N, p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages, bn, di.sm_count, swap);
     if (sp.splits > 1 && sk_bytes >= kSkFlagBytes + sp.bytes) {
       p.splits = sp.splits;
       p.sp_rows = sp.rows;
@@ -1260,6 +1306,14 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
       p.sp_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(sk_ws) + kSkFlagBytes);
       static std::atomic<unsigned long long> token{std::random_device{}() | 1ull};
       p.sp_token = (token.fetch_add(0x9E3779B97F4A7C15ull) >> 8) | 1ull;  // 56 bits, never 0
+    }
+  }
+  if (swap) {
+    switch (bn) {
+      case 16: return launch_gemm<16, true>(p, maps, di.sm_count, st);
+      case 32: return launch_gemm<32, true>(p, maps, di.sm_count, st);
+      case 64: return launch_gemm<64, true>(p, maps, di.sm_count, st);
+      default: return launch_gemm<128, true>(p, maps, di.sm_count, st);
     }
   }
   return bn == 256 ? launch_gemm<256>(p, maps, di.sm_count, st) : launch_gemm<128>(p, maps, di.sm_count, st);
@@ -1293,7 +1347,8 @@ extern "C" size_t mg_matmul_pitched_workspace_bytes(int M, int N, int KN, int KS
   const int s_units = (KN + 255) / 256 + (KS + 127) / 128 + (KO + 127) / 128;
   size_t extra = N % 256 == 0 ? kSkBytes - kSkFlagBytes : 0;
   for (int bn : {128, 256})
-    if (N % bn == 0) extra = std::max(extra, plan_splitk(M, N, s_units, bn, sms).bytes);
+    if (N % bn == 0) extra = std::max(extra, plan_splitk(M, N, s_units, bn, sms, false).bytes);
+  if (M <= 128 && N % 128 == 0) extra = std::max(extra, plan_splitk(M, N, s_units, swap_bn(M), sms, true).bytes);
   return align_up(need, 1024) + kSkFlagBytes + extra;
 }
 

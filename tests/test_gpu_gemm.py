@@ -312,3 +312,32 @@ def test_split_k(M, N, split, force, monkeypatch):
     assert torch.equal(y1.view(torch.int16), y3.view(torch.int16))
     d = (y1.float() - y0.float()).abs()
     assert torch.all(d <= y0.float().abs() * 2.0 ** -7 + 1e-30)
+
+
+@pytest.mark.parametrize("M,N,split", [(1, 128, (256, 128, 128)), (8, 1024, (2560, 1408, 128)), (16, 4096, (2560, 1408, 128)),
+                                       (17, 256, (128, 64, 64)), (32, 1024, (8960, 4928, 448)), (33, 384, (1280, 704, 64)),
+                                       (64, 4096, (2560, 1408, 128)), (100, 768, (2560, 1408, 128)),
+                                       (128, 14336, (2560, 1408, 128))])
+def test_decode_form(M, N, split, monkeypatch):
+    """M <= 128 runs the single-CTA kernel with the operand roles swapped (weights as the 128-row
+    operand, activations as a 16/32/64/128-column operand, tile stored transposed).  Same bounds
+    against the oracle, with and without the C addend, and the same bytes as the 128-row form:
+    every output element is the same K-ordered sum either way."""
+    import mixedgemm_b200 as mg
+    monkeypatch.setenv("MG_GEMM_SPLITK", "0")
+    monkeypatch.setenv("MG_GEMM_SWAP", "1")
+    A, B = _quantise(M, N, sum(split), split, seed=7 * M + N)
+    args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+    rows = None if M * N <= 1 << 20 else np.unique(np.concatenate([[0, M - 1], np.random.default_rng(0).integers(0, M, 30)]))
+    _check(A, B, M, N, split, rows=rows)
+    C = (torch.randn(M, N, generator=torch.Generator().manual_seed(5)) * 0.5).to(torch.bfloat16).cuda()
+    _check(A, B, M, N, split, rows=rows, C=C)
+    y1 = mg.matmul(*args)
+    f1 = mg.matmul(*args, out_dtype=torch.float32)
+    monkeypatch.setenv("MG_GEMM_SWAP", "0")
+    y0 = mg.matmul(*args)
+    f0 = mg.matmul(*args, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    assert torch.equal(f1.view(torch.int32), f0.view(torch.int32))
+    assert torch.equal(y1.view(torch.int16), y0.view(torch.int16))
