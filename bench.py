@@ -3,6 +3,8 @@
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                   [--workload NAME] [--exchange replicated|bcast|allgather] [--no-graph]
+  python bench.py --kernel gemm|reorder --shape M,N,K     one kernel, one shape (what profiles/ is made with)
+  python bench.py --sweep decode|square|all               the other benchmark configurations, a line per shape
 
 One "step" is one pass over a projection set of a Llama-shaped layer stack: every distinct
 activation is reorder-quantised once and multiplied with each weight that consumes it
@@ -364,6 +366,9 @@ def main():
     ap.add_argument("--kernel", default=None, choices=["gemm", "reorder"],
                     help="run only this kernel on --shape (for profiling); prints a short JSON line")
     ap.add_argument("--shape", default="2048,4096,4096", help="M,N,K for --kernel")
+    ap.add_argument("--sweep", default=None, choices=["decode", "square", "all"],
+                    help="time every kernel of the decode-shape sweep (M = 1..128 on the Llama-3-8B layers) and/or the "
+                         "large-square and standalone quantiser shapes; one JSON line each")
     ap.add_argument("--buffers", type=int, default=0,
                     help="--kernel: rotate this many operand sets (0 = enough to exceed L2)")
     a = ap.parse_args()
@@ -375,6 +380,20 @@ def main():
     wl_name = a.workload or ("llama3-8b-m2048" if a.gpus == 1 else "llama3-70b-m4096")
     metric, unit = "mixed_mx_gemm_tflops", "TFLOP/s"
 
+    if a.sweep:
+        # the other benchmark configurations, one JSON line per kernel and shape (not the driver's line)
+        shapes = []
+        if a.sweep in ("decode", "all"):
+            for M in (1, 8, 16, 32, 64, 128):
+                shapes += [("reorder", M, 0, 4096), ("reorder", M, 0, 14336)]
+                shapes += [("gemm", M, N, K) for (N, K) in ((4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336))]
+        if a.sweep in ("square", "all"):
+            shapes += [("reorder", 8192, 0, 16384), ("gemm", 8192, 8192, 8192), ("gemm", 16384, 16384, 16384)]
+        for kernel, M, N, K in shapes:
+            a.kernel, a.shape = kernel, "%d,%d,%d" % (M, N, K)
+            single_kernel(a)
+            torch.cuda.empty_cache()
+        return
     if a.kernel:
         return single_kernel(a)
 
