@@ -16,7 +16,8 @@ timed region, as in deployment.
                     over the ranks.  --exchange replicated (default: the fastest measured): every
                     rank quantises the activations itself; bcast: rank 0 quantises and broadcasts
                     them with NCCL; allgather: every rank quantises M/P rows and NCCL all-gathers
-                    complete the buffers
+                    complete the buffers; rows: not N-sharding at all - the ranks split the M tokens
+                    and every rank holds all weights (no exchange, the quantiser is sharded too)
 
 Prints ONE JSON line (rank 0).  `value` is the whole-job GEMM throughput with inputs resident
 in HBM; `e2e` is the same metric with the activations starting in pinned host memory and the
@@ -196,8 +197,13 @@ class Job:
         import mixedgemm_b200 as mg
         self.mg = mg
         wl = WORKLOADS[wl_name]
-        self.M = M = wl["M"]
+        M = wl["M"]
         self.rank, self.world, self.exchange = rank, world, exchange
+        # "rows": the ranks split the tokens instead of the weights (every rank holds all weights)
+        self.by_rows = world > 1 and exchange == "rows"
+        assert not self.by_rows or M % (128 * world) == 0
+        self.M_total = M
+        self.M = Ml = M // world if self.by_rows else M
         g = torch.Generator(device=device).manual_seed(1234)  # same activations on every rank
         self.groups = []
         self.flops_local = 0
@@ -219,25 +225,29 @@ class Job:
             Xb = X.to(torch.bfloat16)
             del X
             idx = torch.sort(Xb.float().abs().amax(0), stable=True).indices.to(torch.int16)
-            A = mg.alloc_quantized_x(M, KN, KS, KO, device, one_buffer=world > 1)
+            if self.by_rows:
+                from mixedgemm_b200 import dist as mgd
+                m0, _ = mgd.shard_range(M, world, rank)
+                Xb = Xb[m0:m0 + Ml].contiguous()
+            A = mg.alloc_quantized_x(Ml, KN, KS, KO, device, one_buffer=world > 1)
             Ls = []
             for li, (name, N) in enumerate(layers):
                 assert N % (128 * world) == 0, "every shard must be a multiple of 128 columns"
-                Nl = N // world
+                Nl = N if self.by_rows else N // world
                 gw = torch.Generator(device=device).manual_seed(977 * gi + 31 * li + 7)
                 W = (torch.randn(N, K, generator=gw, device=device) * wl["wstd"]).to(torch.bfloat16)
-                Wl = W[rank * Nl:(rank + 1) * Nl].contiguous()
+                Wl = W if self.by_rows else W[rank * Nl:(rank + 1) * Nl].contiguous()
                 del W
-                B = mg.reorder_quantize_w(Wl, idx, KN, KS, KO, M, Nl)
+                B = mg.reorder_quantize_w(Wl, idx, KN, KS, KO, Ml, Nl)
                 del Wl
-                Y = torch.empty((M, Nl), dtype=torch.bfloat16, device=device)
+                Y = torch.empty((Ml, Nl), dtype=torch.bfloat16, device=device)
                 Ls.append((name, Nl, B, Y))
-                self.flops_local += 2 * M * Nl * K
+                self.flops_local += 2 * Ml * Nl * K
                 self.flops_total += 2 * M * N * K
-                self.gemm_shapes.append((M, Nl, K))
-            grouped = M > 128 and len(layers) <= 4 and all((N // world) % 256 == 0 for (_, N) in layers)
+                self.gemm_shapes.append((Ml, Nl, K))
+            grouped = Ml > 128 and len(layers) <= 4 and all(Nl % 256 == 0 for (_, Nl, _, _) in Ls)
             self.n_kernels += 1 + (1 if grouped else len(layers))  # the quantiser + one or several GEMM launches
-            self.reorder_bytes += reorder_bytes(M, K)
+            self.reorder_bytes += reorder_bytes(Ml, K)
             self.groups.append(dict(K=K, split=(KN, KS, KO), X=Xb, idx=idx, A=A, layers=Ls))
         torch.cuda.synchronize()
 
@@ -256,7 +266,7 @@ class Job:
     def quantize_and_exchange(self, gr):
         """bcast: rank 0 quantises, one NCCL broadcast; allgather: every rank quantises M/P rows in
         place, NCCL all-gathers complete the buffers; replicated: every rank quantises everything."""
-        if self.world == 1 or self.exchange == "replicated":
+        if self.world == 1 or self.exchange in ("replicated", "rows"):
             self.quantize(gr)
         elif self.exchange == "allgather":
             from mixedgemm_b200 import dist as mgd
@@ -360,7 +370,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=list(WORKLOADS))
-    ap.add_argument("--exchange", default="replicated", choices=["bcast", "replicated", "allgather"])
+    ap.add_argument("--exchange", default="replicated", choices=["bcast", "replicated", "allgather", "rows"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--cpu-rows", type=int, default=128)
     ap.add_argument("--kernel", default=None, choices=["gemm", "reorder"],
@@ -582,9 +592,10 @@ def main():
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
         "vs_baseline": None, "dtype": "mxfp4/mxfp6/mxfp8 x mxfp4, f32 accumulate, bf16 out", "data": "synthetic",
-        "config": {"workload": wl_name, "M": job.M,
-                   "layers": [[gr["K"], [[n, N * world] for (n, N, _, _) in gr["layers"]]] for gr in job.groups],
-                   "k_split": "62.5% fp4 / 34.375% fp6 / 3.125% fp8", "parallelism": "n-shard x%d" % world,
+        "config": {"workload": wl_name, "M": job.M_total,
+                   "layers": [[gr["K"], [[n, N if job.by_rows else N * world] for (n, N, _, _) in gr["layers"]]]
+                              for gr in job.groups],
+                   "k_split": "62.5% fp4 / 34.375% fp6 / 3.125% fp8", "parallelism": ("m-shard x%d" if job.by_rows else "n-shard x%d") % world,
                    "exchange": a.exchange if world > 1 else "none", "cuda_graph": use_graph,
                    "l2": "inputs larger than L2: one step touches ~%d MB of weights, activations and outputs" % (
                        (sum(t.numel() * t.element_size() for gr in job.groups for (_, _, B, Y) in gr["layers"]

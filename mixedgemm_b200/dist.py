@@ -103,3 +103,12 @@ def all_gather_output(Y_local, world, group=None):
     parts = [torch.empty_like(Y_local) for _ in range(world)]
     dist.all_gather(parts, Y_local.contiguous(), group=group)
     return torch.cat(parts, dim=1)
+
+
+def all_gather_rows(Y_local, world, group=None):
+    """Token-sharded use (every rank multiplies its own M/P rows with all weights; nothing is
+    exchanged on the way in): [M/P, N] shards -> [M, N], for callers that need the full tensor."""
+    full = torch.empty((Y_local.size(0) * world,) + tuple(Y_local.shape[1:]), dtype=Y_local.dtype,
+                       device=Y_local.device)
+    dist.all_gather_into_tensor(full, Y_local.contiguous(), group=group)
+    return full

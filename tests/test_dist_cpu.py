@@ -71,6 +71,12 @@ def _worker(rank, world, port, ret):
             dst.copy_(torch.from_numpy(np.ascontiguousarray(src))[:dst.numel()].view(dst.shape))
         mgd.all_gather_activations(mine, M2, SPLIT, world, rank)
         ret["allgather_%d" % rank] = all(np.array_equal(m.numpy(), f) for m, f in zip(mine, full))
+        # token-sharded use: each rank quantises and multiplies its own rows with the whole weight
+        m0, mrows = mgd.shard_range(M2, world, rank)
+        Yrows = orc.gemm_f64([np.ascontiguousarray(a) for a in part], [t.numpy() for t in Bfull], mrows, N, KN, KS, KO)
+        Yall = mgd.all_gather_rows(torch.from_numpy(Yrows), world)
+        Yfull = orc.gemm_f64(full, [t.numpy() for t in Bfull], M2, N, KN, KS, KO)
+        ret["rows_%d" % rank] = bool(np.array_equal(Yall.numpy(), Yfull))
         r0, n = mgd.shard_range(N, world, rank)
         Yl = orc.gemm_f64([t.numpy() for t in A], [t.numpy() for t in Bl], M, n, KN, KS, KO)
         Y = mgd.all_gather_output(torch.from_numpy(Yl), world)
@@ -90,6 +96,7 @@ def test_two_rank_sharding_recombines_exactly():
     assert ret["equal"]
     assert ret["one_buffer_0"] and ret["one_buffer_1"]
     assert ret["allgather_0"] and ret["allgather_1"]
+    assert ret["rows_0"] and ret["rows_1"]
 
 
 def test_shard_helpers():
