@@ -264,6 +264,17 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
     int stage = 0;
     uint32_t phase = 0, slot = 0;
     int it = 0;
+    unsigned long long* trace = nullptr;  // MG_GEMM_DEBUG=8: globaltimer stamps, 8 per CTA, behind the flags
+    if (leader && p.sk_flags && (p.dbg & 8))
+      trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.sk_flags) + 20480) + blockIdx.x * 8;
+    auto stamp = [&](int i) {
+      if (trace) {
+        unsigned long long ns;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+        trace[i] = ns;
+      }
+    };
+    stamp(0);
     for (int w = blockIdx.x; w < total_items; w += gridDim.x, ++it) {
       const int split = w % splits;
       const int u0 = S_units * split / splits, u1 = S_units * (split + 1) / splits;
@@ -283,6 +294,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
         for (int s = s_lo; s < s_hi; ++s) {
           wait_parity(full_bar(stage), phase, stop, p.status, 2);
           ptx::tc_fence_after();
+          if (it == 0 && accumulate == 0) stamp(1);  // first stage of the first item has landed
           const uint32_t sbase = base + stage * C::STAGE_BYTES;
           const uint32_t sfa_lo = ptx::desc_lo(sbase + C::A_BYTES + C::B_BYTES);
           const uint32_t sfb_lo = sfa_lo + (C::SFA_BYTES >> 4);
@@ -331,7 +343,9 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
         }
       }
       if (leader) ptx::tc_commit(tfull_bar(acc));
+      if (it == 0) stamp(2);  // every MMA of the first item has been issued
     }
+    stamp(3);
   } else {
     // ------------------------------------------------------------ epilogue (4 warps)
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
@@ -339,6 +353,16 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
     volatile int* arrivals = reinterpret_cast<volatile int*>(tmem_holder + 2);  // split-K: counter value seen
     const bool issuer = warp == 2 && lane == 0;
     int it = 0;
+    unsigned long long* trace = nullptr;
+    if (issuer && p.sk_flags && (p.dbg & 8))
+      trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.sk_flags) + 20480) + blockIdx.x * 8;
+    auto stamp = [&](int i) {
+      if (trace) {
+        unsigned long long ns;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+        trace[i] = ns;
+      }
+    };
     for (int w = blockIdx.x; w < total_items; w += gridDim.x, ++it) {
       const int t = w / splits, split = w - t * splits;
       int m_tile, n_tile;
@@ -348,6 +372,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
       wait_parity(tfull_bar(acc), acc_phase, stop, p.status, 8);
       __syncwarp();
       ptx::tc_fence_after();
+      if (it == 0) stamp(4);  // the first item's accumulator is complete
       const int row = m_tile * BM + trow;  // output row, or (SWAP) output column
       const bool store = (SWAP || row < p.M) && !(p.dbg & 4) && !*stop;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * BN;
@@ -413,6 +438,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+        if (it == 0) stamp(5);  // the first item is stored
         continue;
       }
       // ---- split-K: leave this CTA's partial (16-byte units, [column group][row]: a warp stores 512
@@ -1316,6 +1342,7 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
     return launch_pair(p, maps[0], maps[2], maps[4], gm, di.sm_count, allow_streamk ? sk_ws : nullptr, sk_bytes, st);
   }
   p.splits = 1;
+  p.sk_flags = static_cast<int*>(sk_ws);  // the debug time stamps go behind them
   if (sk_ws) {
     const SplitPlan sp = plan_splitk(M, N, p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages, bn, di.sm_count, swap);
     if (sp.splits > 1 && sk_bytes >= kSkFlagBytes + sp.bytes) {
