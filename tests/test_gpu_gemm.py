@@ -202,7 +202,8 @@ def test_known_answer_integers():
     (2048, 4096, 4096, "normal", 20.0, 0.02), (2048, 1024, 4096, "normal", 20.0, 0.02),
     (2048, 14336, 4096, "normal", 20.0, 0.02), (2048, 4096, 14336, "normal", 20.0, 0.02),
     (4096, 1024, 8192, "student3", 30.0, 0.015), (64, 4096, 4096, "normal", 20.0, 0.02),
-    (8, 14336, 4096, "normal", 20.0, 0.02)])
+    (8, 14336, 4096, "normal", 20.0, 0.02), (4096, 3584, 8192, "student3", 30.0, 0.015),
+    (2048, 2048, 28672, "student3", 30.0, 0.015), (512, 2048, 28672, "student3", 30.0, 0.015)])
 def test_benchmark_shapes_row_sample(M, N, K, dist, outlier, wstd):
     """Benchmark-size problems: a seeded sample of output rows against the float64 oracle, plus
     linearity in the scales over the whole output (doubling every A scale doubles Y exactly)."""
