@@ -106,6 +106,26 @@ __device__ __forceinline__ void wait_parity(uint32_t bar, uint32_t parity, volat
   }
 }
 
+// The same for a barrier whose phase is completed by other CTAs of the cluster.
+__device__ __forceinline__ void wait_parity_cluster(uint32_t bar, uint32_t parity, volatile int* stop, int* status,
+                                                    int code) {
+  if (ptx::mbar_try_wait_cluster(bar, parity)) return;
+  long long t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    if (ptx::mbar_try_wait_cluster(bar, parity)) return;
+    if ((spin & 63u) == 0) {
+      if (*stop) return;
+      const long long now = clock64();
+      if (spin == 0) t0 = now;
+      if (now - t0 > kWaitLimitCycles) {
+        *stop = 1;
+        atomicOr(status, code);
+        return;
+      }
+    }
+  }
+}
+
 // Tile order: row blocks in groups of eight, all column blocks of a group before the next group.
 // The CTAs (or clusters) running at one time then share about eight A tiles and nine B tiles instead
 // of 74 A tiles and one B tile, which keeps operands of problems with many row blocks (M = 16384:
@@ -125,9 +145,13 @@ __device__ __forceinline__ void raster(int lt, int tiles_m, int tiles_n, int& m_
   }
 }
 
-template <int BN>
+// CS = cluster split-K: four CTAs of a cluster share a tile, each over a quarter of the K stages,
+// and add their accumulators through distributed shared memory (RECV_BYTES: three senders x 128
+// rows x 32 columns of fp32 in every CTA).
+template <int BN, bool CS = false>
 struct Cfg {
-  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : (BN == 64 ? 8 : 10));
+  static constexpr int STAGES = CS ? 5 : (BN == 256 ? 4 : (BN == 128 ? 6 : (BN == 64 ? 8 : 10)));
+  static constexpr uint32_t RECV_BYTES = CS ? 3u * 128u * 32u * 4u : 0u;
   static constexpr int ACC = BN == 256 ? 1 : 2;
   static constexpr int NB = BN >= 128 ? BN / 128 : 1;
   static constexpr int CHUNKS = (BN + 31) / 32;  // 32-column reads of the accumulator
@@ -138,7 +162,8 @@ struct Cfg {
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   static constexpr uint32_t SF_SLOT_COLS = 8 + NB * 8;  // TMEM columns of one scale slot
   static constexpr uint32_t SF_COL0 = ACC * BN;
-  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + RECV_BYTES;
+  static_assert(!CS || BN == 128, "the cluster exchange hands one 32-column chunk to each of four CTAs");
   static_assert(SF_COL0 + 2 * SF_SLOT_COLS <= kTmemCols, "tensor memory budget");
 };
 
@@ -147,13 +172,13 @@ struct Cfg {
 // spends N x BN instead of N x 128 work on M real rows and a stage carries BN instead of 128
 // activation rows.  p.tiles_m then counts 128-row weight tiles, p.tiles_n is 1, the host swaps the
 // tensor maps, scale pointers and byte counts, and the epilogue stores the tile transposed.
-template <int BN, bool SWAP>
+template <int BN, bool SWAP, bool CS = false>
 __global__ void __launch_bounds__(kThreads, 1)
 mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
                   const __grid_constant__ CUtensorMap tmB0, const __grid_constant__ CUtensorMap tmA1,
                   const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmA2,
                   const __grid_constant__ CUtensorMap tmB2) {
-  using C = Cfg<BN>;
+  using C = Cfg<BN, CS>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -163,8 +188,12 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
   auto empty_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
   auto tfull_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + a); };
   auto tempty_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + C::ACC + a); };
+  // cluster split-K: "every partial for this tile has arrived here" / "what this CTA sent has been read"
+  const uint32_t xfull_bar = bar0 + 8u * (2 * C::STAGES + 2 * C::ACC);
+  const uint32_t xfree_bar = xfull_bar + 8u;
+  const uint32_t recv = bar0 + 256u;  // [sender slot 0..2][4-column group 0..7][row 0..127] 16-byte units
   volatile uint32_t* tmem_holder =
-      reinterpret_cast<volatile uint32_t*>(gbase + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 2 * C::ACC));
+      reinterpret_cast<volatile uint32_t*>(gbase + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 2 * C::ACC + 2));
   volatile int* stop = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -177,6 +206,10 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
     for (int a = 0; a < C::ACC; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
       ptx::mbar_init(tempty_bar(a), 4);
+    }
+    if (CS) {
+      ptx::mbar_init(xfull_bar, 12);  // four epilogue warps of each of the three other CTAs
+      ptx::mbar_init(xfree_bar, 12);
     }
     *stop = 0;
     ptx::fence_mbar_init();
@@ -194,6 +227,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
   ptx::grid_dep_launch_dependents();
   ptx::tc_fence_before();
   __syncthreads();
+  if (CS) ptx::cluster_sync();  // the other CTAs' exchange barriers exist before anyone arrives on them
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   ptx::grid_dep_wait();  // the prologue above touched no global memory
@@ -427,6 +461,76 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
           }
         }
       };
+      if constexpr (CS) {
+        // ---- cluster split-K: the four CTAs of the cluster hold partial sums of the same tile.  CTA c
+        // finishes columns [32 c, 32 c + 32): the others store that chunk of their accumulator into
+        // its shared memory, it adds the four in CTA order and stores the result.
+        const uint32_t crank = ptx::cluster_ctarank();
+        if (it > 0) wait_parity_cluster(xfree_bar, (uint32_t)(it - 1) & 1u, stop, p.status, 512);
+        uint32_t mine[32];
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(taddr + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (c == (int)crank) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mine[i] = r[i];
+          } else if (store) {
+            const uint32_t slot = crank - (crank > (uint32_t)c ? 1u : 0u);
+            const uint32_t dst = ptx::map_to_cta(recv + ((slot * 8u) * 128u + (uint32_t)trow) * 16u, (uint32_t)c);
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              ptx::st_cluster_v4(dst + (uint32_t)v * 128u * 16u, r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+          }
+        }
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+        ptx::fence_acq_rel_cluster();
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+          for (uint32_t o = 0; o < 4; ++o)
+            if (o != crank) ptx::mbar_arrive_release_cluster(ptx::map_to_cta(xfull_bar, o));
+        }
+        wait_parity_cluster(xfull_bar, (uint32_t)it & 1u, stop, p.status, 512);
+        if (store && !*stop) {
+          uint32_t r[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0;  // +0.0f
+#pragma unroll 1
+          for (uint32_t sr = 0; sr < 4; ++sr) {
+            if (sr == crank) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(mine[i]));
+            } else {
+              const uint32_t slot = sr - (sr > crank ? 1u : 0u);
+              const uint32_t src = recv + ((slot * 8u) * 128u + (uint32_t)trow) * 16u;
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                uint4 a;
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w)
+                             : "r"(src + (uint32_t)v * 128u * 16u));
+                r[v * 4] = __float_as_uint(__uint_as_float(r[v * 4]) + __uint_as_float(a.x));
+                r[v * 4 + 1] = __float_as_uint(__uint_as_float(r[v * 4 + 1]) + __uint_as_float(a.y));
+                r[v * 4 + 2] = __float_as_uint(__uint_as_float(r[v * 4 + 2]) + __uint_as_float(a.z));
+                r[v * 4 + 3] = __float_as_uint(__uint_as_float(r[v * 4 + 3]) + __uint_as_float(a.w));
+              }
+            }
+          }
+          emit(r, (int)crank);
+        }
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+          for (uint32_t o = 0; o < 4; ++o)
+            if (o != crank) ptx::mbar_arrive_cluster(ptx::map_to_cta(xfree_bar, o));
+        }
+        if (it == 0) stamp(5);
+        continue;
+      }
       if (splits == 1) {
 #pragma unroll 1
         for (int c = 0; c < C::CHUNKS; ++c) {
@@ -514,6 +618,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
   // ------------------------------------------------------------ teardown
   ptx::tc_fence_before();
   __syncthreads();
+  if (CS) ptx::cluster_sync();  // no CTA leaves while another may still store into it or arrive on it
   ptx::tc_fence_after();
   if (*stop) {
     // give copies and MMAs that are still in flight time to land before the CTA goes away
@@ -1120,6 +1225,44 @@ int launch_gemm(const GemmParams& p, const CUtensorMap* maps, int sms, cudaStrea
   return MG_OK;
 }
 
+// Cluster split-K launch: clusters of four CTAs, one tile per cluster at a time.
+int launch_gemm_cs(const GemmParams& p, const CUtensorMap* maps, int sms, cudaStream_t st) {
+  using C = Cfg<128, true>;
+  auto kern = mixed_gemm_kernel<128, false, true>;
+  MG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int clusters = tiles < sms / 4 ? tiles : sms / 4;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(clusters * 4);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 4;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = mg::pdl_enabled() ? 2 : 1;
+  MG_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, p, maps[0], maps[1], maps[2], maps[3], maps[4], maps[5]));
+  return MG_OK;
+}
+
+// Cluster split-K is taken when the 128 x 128 tiles of the problem occupy at most a quarter of the
+// SMs and every quarter of K has at least two stages.  At these sizes a launch is bound by the fixed
+// cost of a K stage on the tensor pipe (about 255 ns, whatever the stage holds), so a quarter of
+// the stages per CTA is what shortens it; the accumulators meet in distributed shared memory, not
+// in L2.  MG_GEMM_CSPLIT=0 turns it off.
+bool csplit_wanted(int M, int N, int s_units, int sms) {
+  if (N % 128 != 0) return false;
+  if (const char* e = std::getenv("MG_GEMM_CSPLIT"))
+    if (e[0] == '0') return false;
+  const int tiles = (M + BM - 1) / BM * (N / 128);
+  return tiles <= sms / 4 && s_units >= 8;
+}
+
 // Scratch behind the padded copies: a 64 KB zone that must read zero between launches (stream-K
 // flags, one cache line each, from byte 0; debug time stamps from 20 KB; split-K tile counters from
 // 32 KB), then fp32 partials: one 128 x 256 block per CTA of up to 74 clusters for stream-K, or
@@ -1281,9 +1424,11 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
   const int pair_tiles = ((M + 255) / 256) * (N / 256);
   if (const char* e = std::getenv("MG_GEMM_2CTA")) use_pair = use_pair && std::atoi(e) != 0;
   else use_pair = use_pair && (sk || pair_tiles * 4 >= (di.sm_count / 2) * 3);
-  const bool swap = !use_pair && swap_wanted(M, N, (KN + 255) / 256 + (KS + 127) / 128 + (KO + 127) / 128);
+  const int s_units = (KN + 255) / 256 + (KS + 127) / 128 + (KO + 127) / 128;
+  const bool csplit = !use_pair && csplit_wanted(M, N, s_units, di.sm_count);
+  const bool swap = !use_pair && !csplit && swap_wanted(M, N, s_units);
   // rows of one load of the MMA's column operand: weights, or (decode form) activations
-  const int bn = use_pair ? 128 : (swap ? swap_bn(M) : choose_bn(M, N, di.sm_count));
+  const int bn = (use_pair || csplit) ? 128 : (swap ? swap_bn(M) : choose_bn(M, N, di.sm_count));
 
   GemmParams p{};
   p.M = M;
@@ -1343,6 +1488,10 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
   }
   p.splits = 1;
   p.sk_flags = static_cast<int*>(sk_ws);  // the debug time stamps go behind them
+  if (csplit) {
+    p.splits = 4;
+    return launch_gemm_cs(p, maps, di.sm_count, st);
+  }
   if (sk_ws) {
     const SplitPlan sp = plan_splitk(M, N, p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages, bn, di.sm_count, swap);
     if (sp.splits > 1 && sk_bytes >= kSkFlagBytes + sp.bytes) {

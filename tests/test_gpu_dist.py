@@ -21,7 +21,10 @@ def _free_port():
 
 def _worker(rank, world, port, ret):
     import torch.distributed as dist
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    # K is never cut across GPUs, but inside a GPU the library cuts it for problems with few tiles,
+    # and a shard has fewer tiles than the whole: compare the uncut kernels
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", MG_GEMM_CSPLIT="0",
+                      MG_GEMM_SPLITK="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:

@@ -103,6 +103,7 @@ def test_small_shapes(M, N, split):
 
 @pytest.mark.parametrize("bn", ["128", "256"])
 def test_both_tile_widths(bn, monkeypatch):
+    monkeypatch.setenv("MG_GEMM_CSPLIT", "0")
     """The single-CTA kernel with 128- and 256-column tiles."""
     monkeypatch.setenv("MG_GEMM_2CTA", "0")
     monkeypatch.setenv("MG_GEMM_BN", bn)
@@ -119,6 +120,7 @@ def test_cta_pair_kernel_equals_single_cta_kernel(M, N, split, monkeypatch):
     kernel accumulate the same products in the same order: same bytes, and both pass the oracle."""
     import mixedgemm_b200 as mg
     monkeypatch.setenv("MG_GEMM_STREAMK", "0")  # same summation order in both kernels
+    monkeypatch.setenv("MG_GEMM_CSPLIT", "0")
     A, B = _quantise(M, N, sum(split), split, seed=M)
     args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
     monkeypatch.setenv("MG_GEMM_2CTA", "1")
@@ -237,6 +239,7 @@ def test_grouped_weights_equal_separate_calls(M, Ns, split, monkeypatch):
     (the last case is too small for the grouped kernel and takes the fallback)."""
     import mixedgemm_b200 as mg
     monkeypatch.setenv("MG_GEMM_STREAMK", "0")  # tile-per-cluster order in both, so the bytes agree
+    monkeypatch.setenv("MG_GEMM_CSPLIT", "0")
     KN, KS, KO = split
     K = sum(split)
     X = H.make_x(M, K, seed=31)
@@ -291,6 +294,7 @@ def test_split_k(M, N, split, force, monkeypatch):
     the same bytes on every call (the counters are left clear, the sum order is fixed), within one
     bf16 step of the unsplit kernel, with and without the C addend."""
     import mixedgemm_b200 as mg
+    monkeypatch.setenv("MG_GEMM_CSPLIT", "0")  # otherwise the cluster form takes these shapes
     if force is not None:
         monkeypatch.setenv("MG_GEMM_SPLITK", force)
     A, B = _quantise(M, N, sum(split), split, seed=3 * M + N)
@@ -326,6 +330,7 @@ def test_decode_form(M, N, split, monkeypatch):
     every output element is the same K-ordered sum either way."""
     import mixedgemm_b200 as mg
     monkeypatch.setenv("MG_GEMM_SPLITK", "0")
+    monkeypatch.setenv("MG_GEMM_CSPLIT", "0")
     monkeypatch.setenv("MG_GEMM_SWAP", "1")
     A, B = _quantise(M, N, sum(split), split, seed=7 * M + N)
     args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
@@ -342,3 +347,34 @@ def test_decode_form(M, N, split, monkeypatch):
     assert mg.device_status() == 0
     assert torch.equal(f1.view(torch.int32), f0.view(torch.int32))
     assert torch.equal(y1.view(torch.int16), y0.view(torch.int16))
+
+
+@pytest.mark.parametrize("M,N,split", [(16, 4096, (2560, 1408, 128)), (128, 1024, (2560, 1408, 128)),
+                                       (64, 4096, (8960, 4928, 448)), (300, 256, (2560, 1408, 128)),
+                                       (100, 768, (2560, 1408, 128)), (4096, 128, (5120, 2816, 256)),
+                                       (1, 128, (1280, 704, 64)), (129, 2304, (640, 256, 128))])
+def test_cluster_split_k(M, N, split, monkeypatch):
+    """Problems whose 128 x 128 tiles occupy at most a quarter of the SMs run as clusters of four
+    CTAs, each over a quarter of the K stages; the accumulators are exchanged through distributed
+    shared memory and added in CTA order.  Same bounds against the oracle, bf16 == RNE(fp32 result)
+    exactly, the same bytes on every call, within one bf16 step of the unsplit kernel, with and
+    without the C addend, and across a tile count that makes clusters loop over several tiles."""
+    import mixedgemm_b200 as mg
+    A, B = _quantise(M, N, sum(split), split, seed=5 * M + N)
+    args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+    rows = None if M * N <= 1 << 20 else np.unique(np.concatenate([[0, M - 1], np.random.default_rng(0).integers(0, M, 30)]))
+    _check(A, B, M, N, split, rows=rows)
+    C = (torch.randn(M, N, generator=torch.Generator().manual_seed(5)) * 0.5).to(torch.bfloat16).cuda()
+    _check(A, B, M, N, split, rows=rows, C=C)
+    y1 = mg.matmul(*args)
+    y2 = mg.matmul(*args)
+    monkeypatch.setenv("MG_GEMM_CSPLIT", "0")
+    monkeypatch.setenv("MG_GEMM_SPLITK", "0")
+    monkeypatch.setenv("MG_GEMM_SWAP", "0")
+    y0 = mg.matmul(*args)
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    assert torch.equal(y1.view(torch.int16), y2.view(torch.int16))
+    d = (y1.float() - y0.float()).abs()
+    assert torch.all(d <= y0.float().abs() * 2.0 ** -7 + 1e-30)
+    assert not torch.equal(y1, torch.zeros_like(y1))
