@@ -573,11 +573,30 @@ def main():
         e2e_ms = timed(e2e_step, max(3, min(a.steps, 10)), sync, finish=e2e_finish)
 
     # max over ranks
+    solo = None
     if world > 1:
         import torch.distributed as dist
         t = torch.tensor([ms, e2e_ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = t.tolist()
+        # The single-GPU figure of the SAME workload, so that the ratio of this line to one GPU does
+        # not have to be taken against the (smaller) default workload of `--gpus 1`: rank 0 alone,
+        # all weights, same graph-replay timing, while the other ranks wait.
+        if rank == 0:
+            job1 = Job(wl_name, 0, 1, device, "replicated")
+            with torch.cuda.stream(stream):
+                for _ in range(a.warmup):
+                    job1.step()
+                torch.cuda.synchronize()
+                g1 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g1, stream=stream):
+                    job1.step()
+                g1.replay()
+                ms1 = timed(g1.replay, a.steps, torch.cuda.synchronize)
+            solo = {"n_gpus": 1, "workload": wl_name, "value": job1.flops_total / (ms1 * 1e-3) / 1e12, "unit": unit,
+                    "ms_per_step": ms1, "note": "rank 0 alone with all weights, same run, same timing"}
+            del job1, g1
+        dist.barrier()
     status = job.mg.device_status()
     if status != 0:
         raise SystemExit("a kernel reported device status %d" % status)
@@ -605,6 +624,8 @@ def main():
         "e2e": {"value": job.flops_total / (e2e_ms * 1e-3) / 1e12, "unit": unit, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
     }
+    if solo is not None:
+        out["same_workload_1gpu"] = solo
     if world == 1:
         Kdom = max(job.groups, key=lambda gr: gr["K"])["K"]
         gemm_flops = job.flops_local
