@@ -1250,6 +1250,37 @@ int launch_gemm_cs(const GemmParams& p, const CUtensorMap* maps, int sms, cudaSt
   return MG_OK;
 }
 
+// Whether this device can hold a cluster of four of these CTAs at all (asked once per device; a
+// partitioned GPU may not have four SMs in one GPC).
+bool cluster_split_possible() {
+  static std::atomic<int> known[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  int k = known[dev].load();
+  if (k == 0) {
+    using C = Cfg<128, true>;
+    auto kern = mixed_gemm_kernel<128, false, true>;
+    int n = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(4);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = C::SMEM;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 4;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const bool ok = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM) == cudaSuccess &&
+                    cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n >= 1;
+    if (!ok) (void)cudaGetLastError();  // the question is allowed to fail; the answer is then "no"
+    k = ok ? 1 : -1;
+    known[dev].store(k);
+  }
+  return k > 0;
+}
+
 // Cluster split-K is taken when the 128 x 128 tiles of the problem occupy at most a quarter of the
 // SMs and every quarter of K has at least two stages.  At these sizes a launch is bound by the fixed
 // cost of a K stage on the tensor pipe (about 255 ns, whatever the stage holds), so a quarter of
@@ -1260,7 +1291,7 @@ bool csplit_wanted(int M, int N, int s_units, int sms) {
   if (const char* e = std::getenv("MG_GEMM_CSPLIT"))
     if (e[0] == '0') return false;
   const int tiles = (M + BM - 1) / BM * (N / 128);
-  return tiles <= sms / 4 && s_units >= 8;
+  return tiles <= sms / 4 && s_units >= 8 && cluster_split_possible();
 }
 
 // Scratch behind the padded copies: a 64 KB zone that must read zero between launches (stream-K
