@@ -1260,12 +1260,12 @@ int launch_gemm_cs(const GemmParams& p, const CUtensorMap* maps, int sms, cudaSt
   return MG_OK;
 }
 
-// Whether this device can hold a cluster of four of these CTAs at all (asked once per device; a
-// partitioned GPU may not have four SMs in one GPC).
-bool cluster_split_possible() {
+// How many clusters of four of these CTAs the device holds at one time (asked once per device; 33
+// on a B200, 0 where no GPC has four free SMs, e.g. on a partitioned GPU).
+int cluster_split_capacity() {
   static std::atomic<int> known[64];
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
   int k = known[dev].load();
   if (k == 0) {
     using C = Cfg<128, true>;
@@ -1285,14 +1285,14 @@ bool cluster_split_possible() {
     const bool ok = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM) == cudaSuccess &&
                     cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n >= 1;
     if (!ok) (void)cudaGetLastError();  // the question is allowed to fail; the answer is then "no"
-    k = ok ? 1 : -1;
+    k = ok ? n : -1;
     known[dev].store(k);
   }
-  return k > 0;
+  return k > 0 ? k : 0;
 }
 
-// Cluster split-K is taken when the 128 x 128 tiles of the problem occupy at most a quarter of the
-// SMs and every quarter of K has at least two stages.  At these sizes a launch is bound by the fixed
+// Cluster split-K is taken when the 128 x 128 tiles of the problem fit the clusters the device
+// holds at one time (at most a quarter of the SMs) and every quarter of K has at least two stages.  At these sizes a launch is bound by the fixed
 // cost of a K stage on the tensor pipe (about 255 ns, whatever the stage holds), so a quarter of
 // the stages per CTA is what shortens it; the accumulators meet in distributed shared memory, not
 // in L2.  MG_GEMM_CSPLIT=0 turns it off.
@@ -1301,7 +1301,7 @@ bool csplit_wanted(int M, int N, int s_units, int sms) {
   if (const char* e = std::getenv("MG_GEMM_CSPLIT"))
     if (e[0] == '0') return false;
   const int tiles = (M + BM - 1) / BM * (N / 128);
-  return tiles <= sms / 4 && s_units >= 8 && cluster_split_possible();
+  return tiles <= sms / 4 && s_units >= 8 && tiles <= cluster_split_capacity();
 }
 
 // Scratch behind the padded copies: a 64 KB zone that must read zero between launches (stream-K
