@@ -19,11 +19,11 @@
 // What runs for a given problem (matmul_impl decides; every choice has an environment switch):
 //   mixed_gemm_pair_kernel            >= 56 tiles of 256 x 256, bf16 output: two CTAs per tile
 //                                     (cta_group::2), TMA-store epilogue, optional grouped launch
-//   mixed_gemm_kernel<128, -, CS>     <= 37 tiles of 128 x 128: clusters of four CTAs split K and add
+//   mixed_gemm_kernel<128, -, CS>     <= 33 tiles of 128 x 128: clusters of four CTAs split K and add
 //                                     their accumulators through distributed shared memory
 //   mixed_gemm_kernel<16..128, SWAP>  M <= 32 with many weight tiles or a long K: weights as the
 //                                     128-row operand, tile stored transposed
-//   mixed_gemm_kernel<128 | 256>      everything else; with 38..74 tiles and a long K several CTAs
+//   mixed_gemm_kernel<128 | 256>      everything else; with 34..74 tiles and a long K several CTAs
 //                                     per tile, partial sums through the caller's workspace
 #include <cuda.h>
 #include <cudaTypedefs.h>
