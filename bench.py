@@ -631,7 +631,7 @@ def main():
         gemm_flops = job.flops_local
         peak_t = blended_peak(pk["bf16_sustained"], 4096)  # same split for every K
         out["roofline"] = {
-            "kernel": "mixed_gemm_kernel", "bound": "tensor", "achieved": gemm_flops / (g_ms * 1e-3) / 1e12,
+            "kernel": "mixed_gemm_pair_kernel", "bound": "tensor", "achieved": gemm_flops / (g_ms * 1e-3) / 1e12,
             "peak": peak_t, "unit": "TFLOP/s", "frac": gemm_flops / (g_ms * 1e-3) / 1e12 / peak_t,
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the largest GEMM of the step
             # (gate/up, 2048 x 14336 x 4096), from the ncu capture summarised under profiles/
