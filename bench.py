@@ -630,13 +630,18 @@ def main():
         Kdom = max(job.groups, key=lambda gr: gr["K"])["K"]
         gemm_flops = job.flops_local
         peak_t = blended_peak(pk["bf16_sustained"], 4096)  # same split for every K
+        achieved_t, unit_t, bound_t, kern_t = gemm_flops / (g_ms * 1e-3) / 1e12, "TFLOP/s", "tensor", "mixed_gemm_pair_kernel"
+        if job.M <= 128:  # decode shapes are bound by reading the weights once
+            gbytes = sum(N * K // 2 + N * K // 32 + reorder_bytes(M, K) - 2 * M * K + 2 * M * N for (M, N, K) in job.gemm_shapes)
+            achieved_t, unit_t, bound_t, kern_t, peak_t = gbytes / (g_ms * 1e-3) / 1e9, "GB/s", "hbm", "mixed_gemm_kernel", pk["hbm"]
         out["roofline"] = {
-            "kernel": "mixed_gemm_pair_kernel", "bound": "tensor", "achieved": gemm_flops / (g_ms * 1e-3) / 1e12,
-            "peak": peak_t, "unit": "TFLOP/s", "frac": gemm_flops / (g_ms * 1e-3) / 1e12 / peak_t,
+            "kernel": kern_t, "bound": bound_t, "achieved": achieved_t,
+            "peak": peak_t, "unit": unit_t, "frac": achieved_t / peak_t,
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the largest GEMM of the step
             # (gate/up, 2048 x 14336 x 4096), from the ncu capture summarised under profiles/
             "traffic": 50.6e6 if wl_name == "llama3-8b-m2048" else None,
-            "peak_note": "K-blended tensor peak: fp4 segment at 4x and fp6/fp8 at 2x the %s sustained bf16 rate (%.1f TF/s)" % (
+            "peak_note": ("%s copy bandwidth" % pk["source"]) if job.M <= 128 else
+            "K-blended tensor peak: fp4 segment at 4x and fp6/fp8 at 2x the %s sustained bf16 rate (%.1f TF/s)" % (
                 pk["source"], pk["bf16_sustained"]),
             "launches": [{"layer": n, "M": M, "N": N, "K": K, "us": t * 1e3, "tflops": 2 * M * N * K / (t * 1e-3) / 1e12}
                          for (n, M, N, K, t) in g_each]}
