@@ -93,6 +93,31 @@ def _check_codes(tensors, what):
             raise RuntimeError("%s: code tensors must be 2-D CUDA uint8 with unit column stride" % what)
 
 
+def _check_operands(A, B, what):
+    """A = (AN, AS, AO, SFAN, SFAS, SFAO), B likewise for the weights.  The reference infers M, N and
+    the K split from AN, BN, AS and AO alone (bindings.cpp:30-34); the kernels build tensor maps and
+    whole-atom scale copies from those sizes, so every other tensor is held to them here."""
+    lib = _capi.load()
+    _check_codes(tuple(A[:3]) + tuple(B[:3]), what)
+    M, N = A[0].size(0), B[0].size(0)
+    KN, KS, KO = A[0].size(1) * 2, A[1].size(1) * 4 // 3, A[2].size(1)
+    if A[1].size(0) != M or A[2].size(0) != M or B[1].size(0) != N or B[2].size(0) != N:
+        raise RuntimeError("%s: the three code tensors of an operand must have the same row count" % what)
+    if A[1].size(1) * 4 != KS * 3 or B[0].size(1) * 2 != KN or B[1].size(1) * 2 != KS or B[2].size(1) * 2 != KO:
+        raise RuntimeError("%s: code widths of the two operands do not describe the same K split" % what)
+    dev = A[0].device
+    for t, rows, k in ((A[3], M, KN), (A[4], M, KS), (A[5], M, KO), (B[3], N, KN), (B[4], N, KS), (B[5], N, KO)):
+        if not t.is_cuda or t.dtype != torch.uint8 or not t.is_contiguous():
+            raise RuntimeError("%s: scale tensors must be contiguous CUDA uint8 tensors" % what)
+        if t.numel() < lib.mg_sf_bytes(rows, k):
+            raise RuntimeError("%s: a scale tensor holds %d bytes, %d are read (whole 512-byte atoms)" % (
+                what, t.numel(), lib.mg_sf_bytes(rows, k)))
+    for t in tuple(A) + tuple(B):
+        if t.device != dev:
+            raise RuntimeError("%s: all operands must be on one device" % what)
+    return M, N, KN, KS, KO
+
+
 def reorder_quantize_x(X, reorder_index, KN, KS, KO, seqlen=None, outfeatures=None, out=None):
     """bindings.cpp:69-186.  Returns (XN[M,KN/2], XS[M,3KS/4], XO[M,KO], SFXN, SFXS, SFXO), all uint8.
     `seqlen` / `outfeatures` are accepted and ignored, as in the reference.  `out` may pass the
@@ -127,17 +152,27 @@ def reorder_quantize_w(W, reorder_index, KN, KS, KO, seqlen=None, outfeatures=No
     return WN, WS, WO, sfs[0], sfs[1], sfs[2]
 
 
-_workspaces = {}
+_workspaces = {}  # (device type, device index, stream) -> scratch buffer in use
+_retired = []     # superseded buffers, kept alive: captured graphs and queued kernels hold their addresses
 
 
 def _workspace(dev, nbytes):
-    """One growing scratch buffer per device (torch's caching allocator hands out 512-byte
-    aligned blocks; the kernel wants 1024, so over-allocate and slice)."""
+    """Scratch for the call being issued: one buffer per (device, stream), because the split-K
+    counters and partials in it must not be shared by kernels that may run at the same time, grown
+    when a call needs more.  A buffer that has been handed out is never freed - a captured CUDA graph
+    replays with the address it was captured with - and growing is refused while the stream is
+    capturing: run the largest shape once before capturing.  (torch's caching allocator hands out
+    512-byte aligned blocks; the kernels want 1024, so over-allocate and slice.)"""
     if nbytes == 0:
         return None, 0
-    key = (dev.type, dev.index)
+    key = (dev.type, dev.index, torch.cuda.current_stream(dev).cuda_stream)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes + 1024:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("mixedgemm: the scratch buffer of this stream would have to grow during stream capture; "
+                               "run the largest shape once on this stream before capturing")
+        if buf is not None:
+            _retired.append(buf)
         buf = torch.empty(nbytes + 1024, dtype=torch.uint8, device=dev)
         _workspaces[key] = buf
     off = (-buf.data_ptr()) % 1024
@@ -149,19 +184,17 @@ def matmul(AN, BN, AS, BS, AO, BO, SFAN, SFBN, SFAS, SFBS, SFAO, SFBO, out=None,
     `out` (optional) receives the result instead; `C` (optional, bf16 [M,N]) is added before
     the single final rounding; `out_dtype=torch.float32` returns the unrounded accumulator."""
     lib = _capi.load()
-    M, N = AN.size(0), BN.size(0)
-    KN, KS, KO = AN.size(1) * 2, AS.size(1) * 4 // 3, AO.size(1)
-    _check_codes((AN, BN, AS, BS, AO, BO), "matmul")
-    for t in (SFAN, SFBN, SFAS, SFBS, SFAO, SFBO):
-        if not t.is_cuda or t.dtype != torch.uint8 or not t.is_contiguous():
-            raise RuntimeError("matmul: scale tensors must be contiguous CUDA uint8 tensors")
+    M, N, KN, KS, KO = _check_operands((AN, AS, AO, SFAN, SFAS, SFAO), (BN, BS, BO, SFBN, SFBS, SFBO), "matmul")
     dev = AN.device
     dt = out.dtype if out is not None else (out_dtype or torch.bfloat16)
     if dt not in (torch.bfloat16, torch.float32):
         raise RuntimeError("matmul: output dtype must be bfloat16 or float32")
     D = out if out is not None else torch.empty((M, N), dtype=dt, device=dev)
-    if D.size(0) != M or D.size(1) != N or D.stride(1) != 1:
-        raise RuntimeError("matmul: out must be [M,N] with unit column stride")
+    if D.dim() != 2 or D.size(0) != M or D.size(1) != N or D.stride(1) != 1 or D.device != dev:
+        raise RuntimeError("matmul: out must be [M,N] on the operands' device with unit column stride")
+    if C is not None and (C.dtype != torch.bfloat16 or tuple(C.shape) != (M, N) or C.device != dev or
+                          C.stride(1) != 1 or C.stride(0) != D.stride(0)):
+        raise RuntimeError("matmul: C must be bf16 [M,N] on the operands' device with out's row pitch")
     pitches = _pitches((AN, BN, AS, BS, AO, BO))
     with torch.cuda.device(dev):
         ws, wsb = _workspace(dev, lib.mg_matmul_pitched_workspace_bytes(M, N, KN, KS, KO, pitches))
@@ -202,8 +235,9 @@ def matmul_group(A, Bs, outs=None):
     if outs is None:
         outs = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for N in Ns]
     st = 1
+    for B in Bs:
+        _check_operands(A, B, "matmul_group")
     if 1 <= n <= 4 and all(o.dtype == torch.bfloat16 and o.stride(1) == 1 for o in outs):
-        _check_codes(tuple(A[:3]) + tuple(t for B in Bs for t in B[:3]), "matmul_group")
         vp = lambda ts: (ctypes.c_void_p * n)(*[_ptr(t) for t in ts])
         pb = (ctypes.c_size_t * (3 * n))(*[B[s].stride(0) if B[s].size(1) else 0 for B in Bs for s in range(3)])
         with torch.cuda.device(dev):
@@ -229,7 +263,7 @@ def device_status():
     _capi.check(lib.mg_device_status(ctypes.byref(v), _stream()), "device_status")
     if v.value != 0:
         # a kernel that gave up may have left stream-K flags set: start from clean scratch
-        for buf in _workspaces.values():
+        for buf in list(_workspaces.values()) + _retired:
             buf.zero_()
     return v.value
 

@@ -57,6 +57,21 @@ torch::Tensor matmul(const torch::Tensor& AN, const torch::Tensor& BN, const tor
   // shape inference as in the reference (src/bindings.cpp:30-34)
   const int M = (int)AN.size(0), N = (int)BN.size(0);
   const int KN = (int)AN.size(1) * 2, KS = (int)(AS.size(1) * 4 / 3), KO = (int)AO.size(1);
+  // The reference infers the sizes from AN, BN, AS and AO and trusts the rest; the tensor maps and
+  // the whole-atom scale copies are built from these sizes, so every other tensor is held to them.
+  TORCH_CHECK(AS.size(0) == M && AO.size(0) == M, "matmul: AS and AO must have AN's row count");
+  TORCH_CHECK(BS.size(0) == N && BO.size(0) == N, "matmul: BS and BO must have BN's row count");
+  TORCH_CHECK(AS.size(1) * 4 == (int64_t)KS * 3, "matmul: AS must hold 3 bytes per 4 elements");
+  TORCH_CHECK(BN.size(1) * 2 == KN && BS.size(1) * 2 == KS && BO.size(1) * 2 == KO,
+              "matmul: weight code widths do not match the activation segments");
+  const torch::Tensor* sfs[] = {&SFAN, &SFBN, &SFAS, &SFBS, &SFAO, &SFBO};
+  const int sf_rows[] = {M, N, M, N, M, N}, sf_k[] = {KN, KN, KS, KS, KO, KO};
+  for (int i = 0; i < 6; ++i)
+    TORCH_CHECK((size_t)sfs[i]->numel() >= mg_sf_bytes(sf_rows[i], sf_k[i]), "matmul: ", names[6 + i], " holds ",
+                sfs[i]->numel(), " bytes, ", mg_sf_bytes(sf_rows[i], sf_k[i]),
+                " are read (whole 512-byte atoms of 128 rows x 128 elements)");
+  for (int i = 1; i < 12; ++i)
+    TORCH_CHECK(all[i]->device() == AN.device(), "matmul: ", names[i], " is on another device than AN");
   c10::cuda::CUDAGuard guard(AN.device());
   auto stream = at::cuda::getCurrentCUDAStream();
   auto C = torch::empty({M, N}, torch::dtype(torch::kBFloat16).device(AN.device()));

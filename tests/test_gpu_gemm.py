@@ -222,6 +222,141 @@ def test_benchmark_shapes_row_sample(M, N, K, dist, outlier, wstd):
     assert torch.equal(Y2, Y1 * 2)
 
 
+def _dequant_sample(codes, sf, rows, kseg, fmt):
+    """float64 [len(rows), kseg] of the sampled rows of a device-resident operand (scale bytes are
+    addressed by absolute row, so the sample is taken before dequantising)."""
+    if kseg == 0:
+        return np.zeros((len(rows), 0))
+    rows = np.asarray(rows)
+    c = codes[torch.from_numpy(rows).cuda()].contiguous().cpu().numpy()
+    c = orc.unpack_fp4(c) if fmt == orc.FMT_E2M1 else orc.unpack_fp6(c) if fmt == orc.FMT_E3M2 else c
+    v = orc.decode_table(fmt)[c[:, :kseg]]
+    offs = orc.sf_offset(rows[:, None], np.arange(kseg // 32)[None, :], kseg).astype(np.int64)
+    s = sf[torch.from_numpy(offs).cuda()].cpu().numpy().astype(np.int32) - 127
+    return v * np.repeat(np.ldexp(1.0, s), 32, axis=1)
+
+
+@pytest.mark.parametrize("M,N,K,dist,outlier,wstd", [
+    (8192, 8192, 8192, "normal", 20.0, 0.02), (16384, 16384, 16384, "normal", 20.0, 0.02),
+    (4096, 28672, 8192, "student3", 30.0, 0.015)])
+def test_largest_shapes_row_and_column_sample(M, N, K, dist, outlier, wstd):
+    """The large squares and the full-width 70B gate/up projection: inputs are drawn on the device,
+    a seeded sample of output rows x 128-column blocks is compared with the float64 oracle of the
+    same packed operands, and over the WHOLE output bf16 == RNE(fp32 accumulator) bit for bit."""
+    import mixedgemm_b200 as mg
+    KN, KS, KO = split = H.split_k(K)
+    g = torch.Generator(device="cuda").manual_seed(77)
+    X = torch.randn(M, K, generator=g, device="cuda")
+    if dist == "student3":
+        chi = torch.zeros(M, K, device="cuda")
+        for _ in range(3):
+            chi += torch.randn(M, K, generator=g, device="cuda").pow_(2)
+        X = X / (chi / 3).sqrt_() / (3 ** 0.5)
+        del chi
+    X[:, torch.randperm(K, generator=g, device="cuda")[:K // 32]] *= outlier
+    Xb = X.to(torch.bfloat16)
+    del X
+    idx = mg.reorder_index(Xb)
+    assert torch.equal(idx, torch.sort(Xb.float().abs().amax(0), stable=True).indices.to(torch.int16))
+    A = mg.reorder_quantize_x(Xb, idx, KN, KS, KO, M, N)
+    del Xb
+    W = (torch.randn(N, K, generator=g, device="cuda") * wstd).to(torch.bfloat16)
+    B = mg.reorder_quantize_w(W, idx, KN, KS, KO, M, N)
+    del W
+    args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+    Y32 = mg.matmul(*args, out_dtype=torch.float32)
+    Y16 = mg.matmul(*args)
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    assert torch.equal(Y16.view(torch.int16), Y32.to(torch.bfloat16).view(torch.int16))
+    rng = np.random.default_rng(M + N)
+    rows = np.unique(np.concatenate([[0, M - 1], rng.integers(0, M, 46)]))
+    blocks = sorted({0, N // 128 - 1, int(rng.integers(0, N // 128)), int(rng.integers(0, N // 128))})
+    cols = np.concatenate([np.arange(b * 128, b * 128 + 128) for b in blocks])
+    fa = (orc.FMT_E2M1, orc.FMT_E3M2, orc.FMT_E4M3)
+    Ao = np.concatenate([_dequant_sample(A[i], A[3 + i], rows, k, fa[i]) for i, k in enumerate(split)], 1)
+    Bo = np.concatenate([_dequant_sample(B[i], B[3 + i], cols, k, orc.FMT_E2M1) for i, k in enumerate(split)], 1)
+    Yo = Ao @ Bo.T
+    sel = Y32[torch.from_numpy(rows).cuda()][:, torch.from_numpy(cols).cuda()].cpu().numpy().astype(np.float64)
+    rms = np.sqrt(np.mean(Yo ** 2))
+    fro = np.linalg.norm(sel - Yo) / np.linalg.norm(Yo)
+    assert fro <= REL_FRO_TOL, "rel-Frobenius %.3e" % fro
+    assert np.abs(sel - Yo).max() <= MAX_ABS_TOL * rms
+
+
+@pytest.mark.parametrize("N,K", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
+def test_decode_sweep_default_dispatch(N, K):
+    """The decode sweep as the benchmark runs it: M in {1, 8, 16, 32, 64, 128} on the four Llama-3-8B
+    layers, whatever kernel the library picks by itself (no switches set)."""
+    import mixedgemm_b200 as mg
+    KN, KS, KO = split = H.split_k(K)
+    Xall = H.make_x(128, K, seed=N + K)
+    idx = H.reorder_index(Xall).cuda()
+    W = H.make_w(N, K, seed=3)
+    B = mg.reorder_quantize_w(W.cuda(), idx, KN, KS, KO, 128, N)
+    b = [t.cpu().numpy() for t in B]
+    Bd = np.concatenate([orc.np_dequantize(b[i], b[3 + i], N, k, orc.FMT_E2M1) for i, k in enumerate(split)], 1)
+    fa = (orc.FMT_E2M1, orc.FMT_E3M2, orc.FMT_E4M3)
+    for M in (1, 8, 16, 32, 64, 128):
+        A = mg.reorder_quantize_x(Xall[:M].cuda().contiguous(), idx, KN, KS, KO, M, N)
+        args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+        Y32 = mg.matmul(*args, out_dtype=torch.float32)
+        Y16 = mg.matmul(*args)
+        torch.cuda.synchronize()
+        assert mg.device_status() == 0
+        a = [t.cpu().numpy() for t in A]
+        Ad = np.concatenate([orc.np_dequantize(a[i], a[3 + i], M, k, fa[i]) for i, k in enumerate(split)], 1)
+        Yo = Ad @ Bd.T
+        y32 = Y32.cpu().numpy().astype(np.float64)
+        rms = np.sqrt(np.mean(Yo ** 2))
+        fro = np.linalg.norm(y32 - Yo) / np.linalg.norm(Yo)
+        assert fro <= REL_FRO_TOL, "M=%d: rel-Frobenius %.3e" % (M, fro)
+        assert np.abs(y32 - Yo).max() <= MAX_ABS_TOL * rms, "M=%d" % M
+        # the bf16 entry point may cut K differently from the fp32 one (split-K needs scratch that only
+        # some calls get), so it is held to one bf16 step of the rounded accumulator, not to its bytes
+        rne = Y32.to(torch.bfloat16).float()
+        d = (Y16.float() - rne).abs()
+        assert torch.all(d <= rne.abs() * 2.0 ** -7 + 1e-30), "M=%d" % M
+
+
+@pytest.mark.parametrize("fmt,with_c", [(4, False), (4, True), (6, False), (6, True), (8, False), (8, True)])
+def test_single_format_entry_points(fmt, with_c):
+    """mg_matmul_fp4 / fp6 / fp8 called directly through the C ABI: the replacements of the
+    reference's matmul_host4 / 6 / 8 (include/fp4.h:46-56 and siblings), with and without the C
+    addend those take."""
+    import ctypes
+    import mixedgemm_b200 as mg
+    from mixedgemm_b200 import _capi
+    lib = _capi.load()
+    M, N, K = 200, 256, 512
+    split = {4: (K, 0, 0), 6: (0, K, 0), 8: (0, 0, K)}[fmt]
+    seg = {4: 0, 6: 1, 8: 2}[fmt]
+    A, B = _quantise(M, N, K, split, seed=fmt)
+    C = (torch.randn(M, N, generator=torch.Generator().manual_seed(fmt)) * 0.5).to(torch.bfloat16).cuda() if with_c else None
+    D = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    vp = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
+    fn = {4: lib.mg_matmul_fp4, 6: lib.mg_matmul_fp6, 8: lib.mg_matmul_fp8}[fmt]
+    assert A[seg].is_contiguous() and B[seg].is_contiguous()
+    st = fn(vp(A[seg]), vp(B[seg]), M, N, K, vp(C), vp(D), vp(A[3 + seg]), vp(B[3 + seg]),
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == 0, st
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    Yo = _oracle(A, B, M, N, split)
+    if with_c:
+        Yo = Yo + C.float().cpu().numpy().astype(np.float64)
+    want = orc.bf16_round(Yo.astype(np.float32))
+    got = D.float().cpu().numpy()
+    rms = np.sqrt(np.mean(Yo ** 2))
+    assert np.linalg.norm(got - Yo) / np.linalg.norm(Yo) <= 3e-3  # bf16 output rounding included
+    diff = np.abs(got - want)
+    assert np.all((diff <= MAX_ABS_TOL * rms) | (diff <= np.abs(want) * 2.0 ** -7 + 1e-30))
+    # and the same bytes as the three-segment entry point given only this segment
+    args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+    ref = mg.matmul(*args, C=C)
+    assert torch.equal(ref.view(torch.int16), D.view(torch.int16))
+
+
 def test_rejects_bad_arguments():
     import mixedgemm_b200 as mg
     M, N, split = 128, 128, (256, 128, 128)
@@ -230,6 +365,41 @@ def test_rejects_bad_arguments():
         mg.matmul(A[0], B[0][:100], A[1], B[1][:100], A[2], B[2][:100], A[3], B[3], A[4], B[4], A[5], B[5])
     with pytest.raises(RuntimeError):
         mg.matmul(A[0].cpu(), B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+
+
+def test_rejects_operands_that_disagree_with_the_inferred_sizes():
+    """M, N and the K split are inferred from AN, BN, AS and AO (as the reference does); tensors that
+    do not fit those sizes are refused before anything is launched, by the Python mirror and by the
+    drop-in module alike - a short scale buffer would otherwise be read past its end on the device."""
+    import os
+    import sys
+    import mixedgemm_b200 as mg
+    from mixedgemm_b200 import build
+    sys.path.insert(0, os.path.dirname(build.ext_path()))
+    import mixedgemm as ext
+    M, N, split = 256, 256, (256, 192, 64)
+    A, B = _quantise(M, N, sum(split), split)
+    good = [A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5]]
+    mg.matmul(*good)
+    ext.matmul(*good)
+    cases = {
+        "AS rows": (2, A[1][:128]), "BO rows": (5, B[2][:128]), "BS width": (3, B[1][:, :64]),
+        "AS width": (2, A[1][:, :96]), "short SFAS": (8, A[4][:512]), "short SFBO": (11, B[5][:256]),
+        # the reference's own size for a 64-wide segment is N*64/32 bytes; whole atoms need N*16
+        "reference-sized SFBO": (11, B[5][:N * 64 // 32]),
+    }
+    for name, (pos, bad) in cases.items():
+        args = list(good)
+        args[pos] = bad
+        for fn in (mg.matmul, ext.matmul):
+            with pytest.raises(RuntimeError):
+                fn(*args)
+    with pytest.raises(RuntimeError):
+        mg.matmul(*good, C=torch.zeros(M, N, dtype=torch.float32, device="cuda"))
+    with pytest.raises(RuntimeError):
+        mg.matmul(*good, out=torch.empty(M, N + 8, dtype=torch.bfloat16, device="cuda"))
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
 
 
 @pytest.mark.parametrize("M,Ns,split", [(512, (512, 256, 256), (1280, 640, 128)), (2048, (4096, 1024, 1024), (2560, 1408, 128)),

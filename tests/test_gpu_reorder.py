@@ -66,7 +66,9 @@ def test_scale_boundaries(weights):
 
 @pytest.mark.parametrize("weights", [False, True])
 @pytest.mark.parametrize("R,K,split", [(114, 3584, (2560, 896, 128)), (300, 4096, (2560, 1408, 128)),
-                                       (64, 14336, (8960, 4928, 448)), (130, 5120, (3200, 1760, 160))])
+                                       (64, 14336, (8960, 4928, 448)), (130, 5120, (3200, 1760, 160)),
+                                       (70, 12288, (7680, 4224, 384)), (66, 13824, (8640, 4736, 448)),
+                                       (34, 18944, (11840, 6528, 576))])
 def test_matches_compiled_reference_kernel(R, K, split, weights):
     """Same bytes as MixedGemm's reorder_bf16_mixed_kernel / reorder_bf16_fp4_kernel run on this GPU."""
     if H.ref_lib() is None or not H.ref_lib().ref_supports_k(K):
