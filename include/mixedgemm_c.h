@@ -51,9 +51,39 @@ int mg_version(void);
 
 /*
  * Reads and clears the device-side error word that kernels set when a bounded wait
- * expires.  Synchronises `stream`.  *status receives 0 or a kernel-specific code.
+ * expires.  Synchronises `stream`.  *status_host receives 0 or the kernel-specific code
+ * (1 / 2 / 4 / 8: the GEMM's producer / MMA / accumulator-free / accumulator-full waits;
+ * 16 / 32: the quantiser's; 64: the CTA pair's relay; 256: split-K arrival counter;
+ * 512: cluster split-K exchange; 1024: a problem's ready flag).  Returns MG_ERR_TIMEOUT when the
+ * word was non-zero: results of the launches since the last call are then not valid, and the
+ * context is still usable (the kernels gave up and returned, nothing trapped).
  */
 int mg_device_status(int* status_host, void* stream);
+
+/*
+ * Limit of every bounded wait inside the kernels, in microseconds of SM clock at 2 GHz
+ * (0 restores the default of about one second).  Applies to launches made after the call.
+ */
+int mg_set_wait_limit_us(long long us);
+
+/*
+ * Switches that choose between kernels or turn a mode off.  Each is read from the environment
+ * once (MG_<NAME>), when the library is first used, and can be changed at run time here;
+ * -1 means "let the library decide".  Names (with or without the MG_ prefix):
+ *   GEMM_BN          128 / 256: tile width of the single-CTA kernel
+ *   GEMM_2CTA        0 / 1: CTA-pair kernel off / on where it applies
+ *   GEMM_CSPLIT      0: cluster split-K off
+ *   GEMM_SPLITK      0: split-K through the workspace off;  n > 0: n splits
+ *   GEMM_SWAP        0 / 1: decode form off / on for every M <= 128
+ *   PDL              0: no programmatic dependent launch
+ *   REORDER_CTAS     n > 0: at most n CTAs for the quantiser (to share the GPU with another kernel)
+ *   FAULT_SKIP_LOAD  n > 0: host-side fault injection for tests - the first CTA of the single-CTA
+ *                    GEMM never issues its n-th stage load, so the wait for it runs out
+ * mg_set_option returns MG_ERR_SHAPE for an unknown name; mg_reset_options re-reads the environment.
+ */
+int mg_set_option(const char* name, int value);
+int mg_get_option(const char* name, int* value);
+void mg_reset_options(void);
 
 /* Bytes of a scale buffer for `rows` rows of a `kseg`-element segment: whole atoms,
  * ceil(rows/128) * ceil(kseg/128) * 512. */
@@ -120,18 +150,14 @@ int mg_matmul(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, const uin
  *   pitches of mg_reorder_quantize_pitched: {FP4 buffer, FP6 (or second FP4) buffer, FP8 (or third FP4) buffer}
  *   pitches of mg_matmul_pitched:           {AN, BN, AS, BS, AO, BO}
  * mg_matmul_pitched needs workspace only for operands whose pitch does not qualify.  What
- * mg_matmul_pitched_workspace_bytes reports on top (64 KB + fp32 partials) lets two modes run;
- * with a smaller workspace the call still works, without them:
- *  - split-K: a problem whose 128-row tiles occupy at most half of the SMs and whose K has at least
- *    32 stages of 128 bytes (decode shapes and narrow weight shards at large K) runs up to eight
- *    CTAs per tile, each over a range of K; the CTA that arrives last adds the fp32 partials in a
- *    fixed order and stores the tile.  The result is deterministic and differs from the unsplit
- *    kernel by fp32 re-association only.  The arrival counters carry a per-launch token, so the
- *    workspace may hold anything when the call starts.  MG_GEMM_SPLITK=0 in the environment turns
- *    it off.
- *  - stream-K on the CTA-pair kernel, only with MG_GEMM_STREAMK=1: the launch's (tile, K-stage)
- *    units are dealt evenly to the SM pairs and tiles cut that way are completed from fp32
- *    partials.  The library clears the flags it uses on the call's stream before the launch.
+ * mg_matmul_pitched_workspace_bytes reports on top (32 KB + fp32 partials, only for problems that
+ * could use it) lets split-K run; with a smaller workspace the call still works, without it:
+ * a problem whose 128-row tiles occupy at most half of the SMs and whose K has at least 32 stages
+ * of 128 bytes (decode shapes and narrow weight shards at large K) runs up to eight CTAs per tile,
+ * each over a range of K; the CTA that arrives last adds the fp32 partials in a fixed order and
+ * stores the tile.  The result is deterministic and differs from the unsplit kernel by fp32
+ * re-association only.  The arrival counters carry a per-launch token, so the workspace may hold
+ * anything when the call starts.  Option GEMM_SPLITK = 0 turns it off.
  * A workspace must not be shared by calls that may run at the same time.
  * out_f32 != 0 selects the fp32 output of mg_matmul_f32.
  */
@@ -158,14 +184,14 @@ int mg_reorder_index(const void* X, int M, int K, int16_t* idx, uint16_t* absmax
 
 /*
  * Several weight matrices that consume the same quantised activation (q/k/v; gate/up) in ONE
- * launch: D[j] = bf16(A * B[j]^T), j < nprob <= 4.  The reference calls matmul_host once per weight
+ * launch: D[j] = bf16(A * B[j]^T), j < nprob <= 8.  The reference calls matmul_host once per weight
  * (main.py:59 per layer); sharing the launch lets small projections fill SMs that a large one
  * leaves idle in its last wave.  Restrictions: M > 128, every N[j] a multiple of 256, bf16 output,
  * and every code buffer row-pitched so that it is read in place (mg_code_pitch) - otherwise
  * MG_ERR_SHAPE / MG_ERR_ALIGN is returned and the caller issues mg_matmul per weight instead.
  *   pitches_a[3] = {AN, AS, AO};  pitches_b[3*j + s] = pitch of weight j, segment s
- *   BN/BS/BO/SFBN/SFBS/SFBO/D/N/ldd are arrays of nprob entries.  workspace (optional, 1024-aligned,
- *   mg_matmul_pitched_workspace_bytes of the widest problem) enables stream-K as in mg_matmul_pitched.
+ *   BN/BS/BO/SFBN/SFBS/SFBO/D/N/ldd are arrays of nprob entries.  workspace / workspace_bytes are
+ *   not used (kept for callers of earlier versions); pass NULL / 0.
  */
 int mg_matmul_group_pitched(int nprob, const uint8_t* AN, const uint8_t* AS, const uint8_t* AO,
                             const size_t* pitches_a, const uint8_t* const* BN, const uint8_t* const* BS,
@@ -173,6 +199,33 @@ int mg_matmul_group_pitched(int nprob, const uint8_t* AN, const uint8_t* AS, con
                             int KO, void* const* D_bf16, const int* ldd, const uint8_t* SFAN, const uint8_t* SFAS,
                             const uint8_t* SFAO, const uint8_t* const* SFBN, const uint8_t* const* SFBS,
                             const uint8_t* const* SFBO, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * A list of INDEPENDENT problems in one launch of the CTA-pair kernel: each has its own quantised
+ * activation, weights, K split and output.  The reference calls matmul_host once per layer
+ * (main.py:59); a layer's projections each leave SM pairs idle in their last wave, and one launch
+ * over the concatenated tile lists (dealt round-robin in the order given) closes those gaps.
+ * Restrictions per problem: M > 128, N a multiple of 256, bf16 output, every code buffer row-pitched
+ * so that it is read in place (mg_code_pitch); nprob <= 8.  Otherwise MG_ERR_SHAPE / MG_ERR_ALIGN is
+ * returned, nothing is launched, and the caller issues mg_matmul per problem instead.
+ *
+ * ready_flag (optional): device address of an int.  The kernel does not read the problem's
+ * activation before *ready_flag - ready_value >= 0 (an acquire load at system scope, bounded
+ * wait, status code 1024 on expiry).  It lets an exchange that is still filling the activation
+ * buffer - a copy engine, another GPU writing over NVLink - overlap the problems listed before it.
+ */
+typedef struct mg_problem {
+  const uint8_t *AN, *AS, *AO, *SFAN, *SFAS, *SFAO; /* activation, as written by mg_reorder_quantize_pitched */
+  size_t pitch_a[3];
+  const uint8_t *BN, *BS, *BO, *SFBN, *SFBS, *SFBO; /* weights */
+  size_t pitch_b[3];
+  int M, N, KN, KS, KO;
+  void* D_bf16; /* [M,N] bf16, row pitch ldd elements */
+  int ldd;
+  const int* ready_flag;
+  int ready_value;
+} mg_problem_t;
+int mg_matmul_multi(int nprob, const mg_problem_t* probs, void* stream);
 
 /*
  * Same product with the fp32 accumulator written unrounded: D_f32 [M,N] float, pitch `ldd`
@@ -202,6 +255,9 @@ int mg_matmul_f32(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, const
  *  - The call itself makes no cudaMalloc / cudaFree and uses no allocating library routine.
  *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress);
  *    make that first call outside any stream capture.
+ *  - Only the padded copies live in the array (split-K through scratch is not taken), so the
+ *    kernel that runs, and with it the result, is that of mg_matmul given a workspace of exactly
+ *    mg_matmul_workspace_bytes() bytes.
  *  - All calls share the one array and it keeps whatever the previous call left there.  Nothing
  *    has to be cleared: each call rewrites every byte it later reads, zero padding included.
  *    Two calls that overlap on the GPU (different streams, no dependency) race on it - order

@@ -20,6 +20,11 @@ PROTOTYPES = {
     "mg_last_cuda_error": (_i, []),
     "mg_version": (_i, []),
     "mg_device_status": (_i, [ctypes.POINTER(_i), _vp]),
+    "mg_set_wait_limit_us": (_i, [ctypes.c_longlong]),
+    "mg_set_option": (_i, [ctypes.c_char_p, _i]),
+    "mg_get_option": (_i, [ctypes.c_char_p, ctypes.POINTER(_i)]),
+    "mg_reset_options": (None, []),
+    "mg_matmul_multi": (_i, [_i, _vp, _vp]),
     "mg_sf_bytes": (_sz, [_i, _i]),
     "mg_reorder_quantize_x": (_i, [_vp, _i, _i, _vp, _i, _i, _i] + [_vp] * 6 + [_vp]),
     "mg_reorder_quantize_w": (_i, [_vp, _i, _i, _vp, _i, _i, _i] + [_vp] * 6 + [_vp]),
@@ -38,6 +43,16 @@ PROTOTYPES = {
     "mg_matmul_fp6": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "mg_matmul_fp8": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
 }
+
+
+
+class Problem(ctypes.Structure):
+    """mg_problem_t of include/mixedgemm_c.h."""
+    _fields_ = ([(n, _vp) for n in ("AN", "AS", "AO", "SFAN", "SFAS", "SFAO")] + [("pitch_a", _sz * 3)] +
+                [(n, _vp) for n in ("BN", "BS", "BO", "SFBN", "SFBS", "SFBO")] + [("pitch_b", _sz * 3)] +
+                [(n, _i) for n in ("M", "N", "KN", "KS", "KO")] + [("D_bf16", _vp), ("ldd", _i),
+                                                                  ("ready_flag", _vp), ("ready_value", _i)])
+
 
 _lib = None
 

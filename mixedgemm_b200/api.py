@@ -237,11 +237,11 @@ def matmul_group(A, Bs, outs=None):
     st = 1
     for B in Bs:
         _check_operands(A, B, "matmul_group")
-    if 1 <= n <= 4 and all(o.dtype == torch.bfloat16 and o.stride(1) == 1 for o in outs):
+    if 1 <= n <= 8 and all(o.dtype == torch.bfloat16 and o.stride(1) == 1 for o in outs):
         vp = lambda ts: (ctypes.c_void_p * n)(*[_ptr(t) for t in ts])
         pb = (ctypes.c_size_t * (3 * n))(*[B[s].stride(0) if B[s].size(1) else 0 for B in Bs for s in range(3)])
         with torch.cuda.device(dev):
-            ws, wsb = _workspace(dev, lib.mg_matmul_pitched_workspace_bytes(M, max(Ns), KN, KS, KO, None))
+            ws, wsb = None, 0
             st = lib.mg_matmul_group_pitched(
                 n, _ptr(A[0]), _ptr(A[1]), _ptr(A[2]), _pitches(A[:3]), vp([B[0] for B in Bs]),
                 vp([B[1] for B in Bs]), vp([B[2] for B in Bs]), pb, M, (ctypes.c_int * n)(*Ns), KN, KS, KO, vp(outs),
@@ -255,16 +255,78 @@ def matmul_group(A, Bs, outs=None):
     return outs
 
 
+def matmul_multi(problems, flags=None):
+    """One launch for a list of independent products (up to 8): problems = [(A, B, out), ...] with
+    A = (AN, AS, AO, SFAN, SFAS, SFAO), B likewise for the weights, out a [M, N] bf16 tensor or None.
+    Each problem has its own activation and K split, unlike matmul_group.  `flags` (optional) gives
+    per problem None or (int32 CUDA tensor of one element, value): the kernel reads that problem's
+    activation only once the flag has reached the value (mg_problem_t.ready_flag).  Problems the
+    CTA-pair kernel does not take (M <= 128, N not a multiple of 256, buffers that need the padded
+    copy) fall back to one matmul per problem; flags are then refused.  Returns the outputs."""
+    import ctypes
+    lib = _capi.load()
+    n = len(problems)
+    outs = []
+    arr = (_capi.Problem * max(n, 1))()
+    dev = problems[0][0][0].device
+    for j, (A, B, out) in enumerate(problems):
+        M, N, KN, KS, KO = _check_operands(A, B, "matmul_multi")
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        if out.dtype != torch.bfloat16 or tuple(out.shape) != (M, N) or out.stride(1) != 1 or out.device != dev:
+            raise RuntimeError("matmul_multi: outputs must be bf16 [M,N] on the operands' device with unit column stride")
+        outs.append(out)
+        q = arr[j]
+        for name, t in zip(("AN", "AS", "AO", "SFAN", "SFAS", "SFAO"), A):
+            setattr(q, name, _ptr(t))
+        for name, t in zip(("BN", "BS", "BO", "SFBN", "SFBS", "SFBO"), B):
+            setattr(q, name, _ptr(t))
+        for i in range(3):
+            q.pitch_a[i] = A[i].stride(0) if A[i].size(1) else 0
+            q.pitch_b[i] = B[i].stride(0) if B[i].size(1) else 0
+        q.M, q.N, q.KN, q.KS, q.KO = M, N, KN, KS, KO
+        q.D_bf16, q.ldd = _ptr(out), out.stride(0)
+        f = flags[j] if flags is not None else None
+        if f is not None:
+            ft, fv = f
+            if not ft.is_cuda or ft.dtype != torch.int32 or ft.numel() < 1 or ft.device != dev:
+                raise RuntimeError("matmul_multi: a ready flag must be an int32 CUDA tensor on the operands' device")
+            q.ready_flag, q.ready_value = ft.data_ptr(), int(fv)
+    st = 1
+    if 1 <= n <= 8:
+        with torch.cuda.device(dev):
+            st = lib.mg_matmul_multi(n, ctypes.cast(arr, ctypes.c_void_p), _stream())
+    if st in (1, 3):  # a shape or pitch the grouped kernel does not take
+        if flags is not None and any(f is not None for f in flags):
+            raise RuntimeError("matmul_multi: ready flags need problems the CTA-pair kernel takes")
+        for (A, B, _), o in zip(problems, outs):
+            matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5], out=o)
+    else:
+        _capi.check(st, "matmul_multi")
+    return outs
+
+
+def set_option(name, value):
+    """mg_set_option: choose between kernels / turn a mode off at run time (names in mixedgemm_c.h)."""
+    _capi.check(_capi.load().mg_set_option(name.encode(), int(value)), "set_option(%s)" % name)
+
+
+def reset_options():
+    _capi.load().mg_reset_options()
+
+
+def set_wait_limit_us(us):
+    _capi.check(_capi.load().mg_set_wait_limit_us(int(us)), "set_wait_limit_us")
+
+
 def device_status():
-    """Reads and clears the device error word (non-zero after a kernel gave up on a wait)."""
+    """Reads and clears the device error word (non-zero after a kernel gave up on a bounded wait)."""
     import ctypes
     lib = _capi.load()
     v = ctypes.c_int(0)
-    _capi.check(lib.mg_device_status(ctypes.byref(v), _stream()), "device_status")
-    if v.value != 0:
-        # a kernel that gave up may have left stream-K flags set: start from clean scratch
-        for buf in list(_workspaces.values()) + _retired:
-            buf.zero_()
+    st = lib.mg_device_status(ctypes.byref(v), _stream())
+    if st != 7:  # MG_ERR_TIMEOUT only says that the word was non-zero
+        _capi.check(st, "device_status")
     return v.value
 
 

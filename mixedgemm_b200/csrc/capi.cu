@@ -1,6 +1,9 @@
 // Status, device queries and small helpers of the C ABI.
+#include <atomic>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
+#include <string>
 
 #include "mg_common.h"
 
@@ -15,17 +18,49 @@ mg::DeviceInfo g_info[kMaxDevices];
 bool g_info_ok[kMaxDevices];
 int* g_status_ptr[kMaxDevices];
 std::mutex g_mu;
+
+constexpr long long kDefaultWaitCycles = 2000000000LL;  // about one second of SM clock
+std::atomic<long long> g_wait_cycles{kDefaultWaitCycles};
+}  // namespace
+
+namespace {
+struct OptionSlot {
+  const char* name;
+  int mg::Options::*field;
+  int fallback;
+};
+const OptionSlot kOptionSlots[] = {
+    {"GEMM_BN", &mg::Options::gemm_bn, -1},         {"GEMM_2CTA", &mg::Options::gemm_2cta, -1},
+    {"GEMM_CSPLIT", &mg::Options::gemm_csplit, -1}, {"GEMM_SPLITK", &mg::Options::gemm_splitk, -1},
+    {"GEMM_SWAP", &mg::Options::gemm_swap, -1},     {"PDL", &mg::Options::pdl, 1},
+    {"REORDER_CTAS", &mg::Options::reorder_ctas, 0}, {"FAULT_SKIP_LOAD", &mg::Options::fault_skip_load, 0},
+};
+mg::Options g_options;
+bool g_options_ready = false;
+std::mutex g_options_mu;
+
+void load_options_locked() {
+  for (const OptionSlot& s : kOptionSlots) {
+    g_options.*(s.field) = s.fallback;
+    const std::string env = std::string("MG_") + s.name;
+    if (const char* e = std::getenv(env.c_str()))
+      if (e[0] != 0) g_options.*(s.field) = std::atoi(e);
+  }
+  g_options_ready = true;
+}
 }  // namespace
 
 namespace mg {
 
-bool pdl_enabled() {
-  static const bool on = [] {
-    const char* e = std::getenv("MG_PDL");
-    return !(e && e[0] == '0');
-  }();
-  return on;
+Options options() {
+  std::lock_guard<std::mutex> lk(g_options_mu);
+  if (!g_options_ready) load_options_locked();
+  return g_options;
 }
+
+bool pdl_enabled() { return options().pdl != 0; }
+
+long long wait_limit_cycles() { return g_wait_cycles.load(std::memory_order_relaxed); }
 
 int note_cuda_error(cudaError_t e) {
   tl_last_cuda_error = (int)e;
@@ -79,6 +114,43 @@ extern "C" const char* mg_strerror(int status) {
   }
 }
 
+extern "C" int mg_set_wait_limit_us(long long us) {
+  if (us < 0) return MG_ERR_SHAPE;
+  // clock64 ticks at the SM clock, at most 2 GHz on this part: 2000 cycles per microsecond
+  g_wait_cycles.store(us == 0 ? kDefaultWaitCycles : us * 2000LL, std::memory_order_relaxed);
+  return MG_OK;
+}
+
+extern "C" int mg_set_option(const char* name, int value) {
+  if (!name) return MG_ERR_NULL;
+  if (std::strncmp(name, "MG_", 3) == 0) name += 3;
+  std::lock_guard<std::mutex> lk(g_options_mu);
+  if (!g_options_ready) load_options_locked();
+  for (const OptionSlot& s : kOptionSlots)
+    if (std::strcmp(name, s.name) == 0) {
+      g_options.*(s.field) = value;
+      return MG_OK;
+    }
+  return MG_ERR_SHAPE;
+}
+
+extern "C" int mg_get_option(const char* name, int* value) {
+  if (!name || !value) return MG_ERR_NULL;
+  if (std::strncmp(name, "MG_", 3) == 0) name += 3;
+  const mg::Options o = mg::options();
+  for (const OptionSlot& s : kOptionSlots)
+    if (std::strcmp(name, s.name) == 0) {
+      *value = o.*(s.field);
+      return MG_OK;
+    }
+  return MG_ERR_SHAPE;
+}
+
+extern "C" void mg_reset_options(void) {
+  std::lock_guard<std::mutex> lk(g_options_mu);
+  load_options_locked();
+}
+
 extern "C" int mg_last_cuda_error(void) { return tl_last_cuda_error; }
 
 extern "C" int mg_version(void) { return 1; }
@@ -96,6 +168,9 @@ extern "C" int mg_device_status(int* status_host, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   MG_CUDA_TRY(cudaStreamSynchronize(st));
   MG_CUDA_TRY(cudaMemcpy(status_host, dptr, sizeof(int), cudaMemcpyDeviceToHost));
-  if (*status_host != 0) MG_CUDA_TRY(cudaMemset(dptr, 0, sizeof(int)));
+  if (*status_host != 0) {
+    MG_CUDA_TRY(cudaMemset(dptr, 0, sizeof(int)));
+    return MG_ERR_TIMEOUT;
+  }
   return MG_OK;
 }

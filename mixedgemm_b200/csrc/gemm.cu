@@ -16,9 +16,9 @@
 // All waits are bounded; on expiry a kernel records a code in the device status word,
 // tells the other roles of its CTA to stop, frees its tensor memory and returns.
 //
-// What runs for a given problem (matmul_impl decides; every choice has an environment switch):
+// What runs for a given problem (matmul_impl decides; every choice has an option, see mg_set_option):
 //   mixed_gemm_pair_kernel            >= 56 tiles of 256 x 256, bf16 output: two CTAs per tile
-//                                     (cta_group::2), TMA-store epilogue, optional grouped launch
+//                                     (cta_group::2), TMA-store epilogue, one launch for a list of problems
 //   mixed_gemm_kernel<128, -, CS>     <= 33 tiles of 128 x 128: clusters of four CTAs split K and add
 //                                     their accumulators through distributed shared memory
 //   mixed_gemm_kernel<16..128, SWAP>  M <= 32 with many weight tiles or a long K: weights as the
@@ -43,7 +43,6 @@ namespace {
 constexpr int BM = 128;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
-constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
 
 struct SegParams {
   int kseg;     // valid elements of the segment
@@ -61,36 +60,18 @@ struct GemmParams {
   __nv_bfloat16* D;
   float* Df32;  // when set, the fp32 accumulator is stored here instead of D
   int* status;
+  long long wait_cycles;      // limit of every bounded wait, in SM clock cycles
   uint32_t tx_a[3], tx_b[3];  // bytes one A / B tile load of the segment signals
-  int dbg;  // timing experiments only (MG_GEMM_DEBUG): 1 = no MMAs, 2 = no loads, 4 = no stores,
-            // 8 = stream-K epilogues leave globaltimer stamps behind the flags (8 per CTA, from byte 20480)
-  // CTA-pair kernel only: up to four weight matrices that share the activation ("fused N": q/k/v,
-  // gate/up).  Problem j owns pair tiles [tile_end[j-1], tile_end[j]) and its own scales / output.
-  int nprob;
-  int tile_end[4];
-  const uint8_t* sfb_g[4][3];
-  // Stream-K (CTA-pair kernel): the launch's (tile, K-stage) units are dealt to the clusters as equal
-  // contiguous ranges, so a cluster may compute only part of a tile's K.  The cluster that holds a
-  // tile's first stage finishes it, adding the fp32 partials the others leave in sk_partials.
-  // Split-K (single-CTA kernel): when a problem has too few tiles to occupy the SMs, `splits` CTAs
-  // share a tile, each over a contiguous range of its K stages.  Each leaves its fp32 partial in
-  // sp_partials and bumps the tile's counter; the CTA that arrives last adds the partials in split
-  // order (so the result does not depend on who was last), stores the tile and clears the counter.
+  int skip_load;  // fault injection for the bounded-wait test: CTA 0 withholds its n-th stage load (0 = off)
+  // Split-K (few tiles): `splits` CTAs share a tile, each over a contiguous range of its K stages.
+  // Each leaves its fp32 partial in sp_partials and bumps the tile's counter; the CTA that arrives
+  // last adds the partials in split order (so the result does not depend on who was last), stores
+  // the tile and clears the counter.
   int splits;
   int sp_rows;         // rows per tile in sp_partials (128, or M rounded up to 32 when M <= 96)
   unsigned long long* sp_counters;  // [tile]: (launch token << 8) | arrivals; the last CTA writes 0
   unsigned long long sp_token;      // 56 bits, unique per launch: a word with another token counts as 0
   float* sp_partials;  // [split][tile][column group of 4][sp_rows][4]
-  int streamk;
-  int* sk_flags;       // [cluster][cta]: 1 when that CTA's partial is complete; the finisher clears it
-  float* sk_partials;  // [cluster][cta][4 panels][16 column groups][128 rows][4 columns]
-};
-
-constexpr int kMaxGroup = 4;
-constexpr int kSkFlagStride = 32;  // ints between stream-K flags: one 128-byte line each
-struct GroupMaps {
-  CUtensorMap b[kMaxGroup][3];  // weight codes per problem and K segment
-  CUtensorMap d[kMaxGroup];     // outputs
 };
 
 // Bounded mbarrier wait.  Control flow stays warp-uniform: when the limit expires the lane
@@ -98,7 +79,7 @@ struct GroupMaps {
 // returns at once, the loops run out (their results are garbage and are not stored) and
 // the kernel ends normally.
 __device__ __forceinline__ void wait_parity(uint32_t bar, uint32_t parity, volatile int* stop, int* status,
-                                            int code) {
+                                            long long limit, int code) {
   if (ptx::mbar_try_wait(bar, parity)) return;
   long long t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
@@ -107,7 +88,7 @@ __device__ __forceinline__ void wait_parity(uint32_t bar, uint32_t parity, volat
       if (*stop) return;
       const long long now = clock64();
       if (spin == 0) t0 = now;
-      if (now - t0 > kWaitLimitCycles) {
+      if (now - t0 > limit) {
         *stop = 1;
         atomicOr(status, code);
         return;
@@ -118,7 +99,7 @@ __device__ __forceinline__ void wait_parity(uint32_t bar, uint32_t parity, volat
 
 // The same for a barrier whose phase is completed by other CTAs of the cluster.
 __device__ __forceinline__ void wait_parity_cluster(uint32_t bar, uint32_t parity, volatile int* stop, int* status,
-                                                    int code) {
+                                                    long long limit, int code) {
   if (ptx::mbar_try_wait_cluster(bar, parity)) return;
   long long t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
@@ -127,7 +108,7 @@ __device__ __forceinline__ void wait_parity_cluster(uint32_t bar, uint32_t parit
       if (*stop) return;
       const long long now = clock64();
       if (spin == 0) t0 = now;
-      if (now - t0 > kWaitLimitCycles) {
+      if (now - t0 > limit) {
         *stop = 1;
         atomicOr(status, code);
         return;
@@ -256,6 +237,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
     const bool leader = ptx::elect_one();
     int stage = 0;
     uint32_t phase = 0;
+    int skip_countdown = p.skip_load;
     for (int w = blockIdx.x; w < total_items; w += gridDim.x) {
       const int t = w / splits, split = w - t * splits;
       const int u0 = S_units * split / splits, u1 = S_units * (split + 1) / splits;
@@ -274,14 +256,14 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
         const int s_lo = max(u0 - so, 0), s_hi = min(u1 - so, sp.nstages);
 #pragma unroll 1
         for (int s = s_lo; s < s_hi; ++s) {
-          wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, 1);
+          wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, p.wait_cycles, 1);
           const int atom0 = seg == 0 ? 2 * s : s;
           const int natoms = seg == 0 ? min(2, sp.katoms - atom0) : 1;
           const uint32_t sbase = base + stage * C::STAGE_BYTES;
           const uint32_t fb = full_bar(stage);
           if (leader) {
-            if (p.dbg & 2) {
-              ptx::mbar_arrive(fb);
+            if (p.skip_load != 0 && blockIdx.x == 0 && --skip_countdown == 0) {
+              // fault injection: this stage is never loaded, so the MMA warp's wait for it runs out
             } else {
               ptx::mbar_expect_tx(fb, tx_ab + (uint32_t)natoms * 512u * (1 + C::NB));
               ptx::tma_load_2d(sbase, ta, s * 128, m_tile * BM, fb);
@@ -308,23 +290,12 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
     int stage = 0;
     uint32_t phase = 0, slot = 0;
     int it = 0;
-    unsigned long long* trace = nullptr;  // MG_GEMM_DEBUG=8: globaltimer stamps, 8 per CTA, behind the flags
-    if (leader && p.sk_flags && (p.dbg & 8))
-      trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.sk_flags) + 20480) + blockIdx.x * 8;
-    auto stamp = [&](int i) {
-      if (trace) {
-        unsigned long long ns;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
-        trace[i] = ns;
-      }
-    };
-    stamp(0);
     for (int w = blockIdx.x; w < total_items; w += gridDim.x, ++it) {
       const int split = w % splits;
       const int u0 = S_units * split / splits, u1 = S_units * (split + 1) / splits;
       const int acc = it % C::ACC;
       const uint32_t acc_phase = (uint32_t)(it / C::ACC) & 1u;
-      wait_parity(tempty_bar(acc), acc_phase ^ 1u, stop, p.status, 4);
+      wait_parity(tempty_bar(acc), acc_phase ^ 1u, stop, p.status, p.wait_cycles, 4);
       ptx::tc_fence_after();
       const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
       uint32_t accumulate = 0;
@@ -336,9 +307,8 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
         const int s_lo = max(u0 - so, 0), s_hi = min(u1 - so, sp.nstages);
 #pragma unroll 1
         for (int s = s_lo; s < s_hi; ++s) {
-          wait_parity(full_bar(stage), phase, stop, p.status, 2);
+          wait_parity(full_bar(stage), phase, stop, p.status, p.wait_cycles, 2);
           ptx::tc_fence_after();
-          if (it == 0 && accumulate == 0) stamp(1);  // first stage of the first item has landed
           const uint32_t sbase = base + stage * C::STAGE_BYTES;
           const uint32_t sfa_lo = ptx::desc_lo(sbase + C::A_BYTES + C::B_BYTES);
           const uint32_t sfb_lo = sfa_lo + (C::SFA_BYTES >> 4);
@@ -347,7 +317,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
           const uint32_t a_lo = ptx::desc_lo(sbase), b_lo = ptx::desc_lo(sbase + C::A_BYTES);
           // K elements left in this segment, in MMA steps (64 for FP4, 32 for FP6 / FP8)
           const int nm = seg == 0 ? min(4, (sp.kseg - s * 256) >> 6) : min(4, (sp.kseg - s * 128) >> 5);
-          if (leader && !(p.dbg & 1)) {
+          if (leader) {
             // scale atoms -> TMEM: atom a of A to columns a*4.., of B (per 128 columns) to a*NB*4 + nb*4..
             ptx::tc_cp_sf(sfa_t, sfa_lo, ptx::kDescHiSf);
 #pragma unroll
@@ -387,9 +357,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
         }
       }
       if (leader) ptx::tc_commit(tfull_bar(acc));
-      if (it == 0) stamp(2);  // every MMA of the first item has been issued
     }
-    stamp(3);
   } else {
     // ------------------------------------------------------------ epilogue (4 warps)
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
@@ -397,28 +365,17 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
     volatile int* arrivals = reinterpret_cast<volatile int*>(tmem_holder + 2);  // split-K: counter value seen
     const bool issuer = warp == 2 && lane == 0;
     int it = 0;
-    unsigned long long* trace = nullptr;
-    if (issuer && p.sk_flags && (p.dbg & 8))
-      trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.sk_flags) + 20480) + blockIdx.x * 8;
-    auto stamp = [&](int i) {
-      if (trace) {
-        unsigned long long ns;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
-        trace[i] = ns;
-      }
-    };
     for (int w = blockIdx.x; w < total_items; w += gridDim.x, ++it) {
       const int t = w / splits, split = w - t * splits;
       int m_tile, n_tile;
       raster(t, p.tiles_m, p.tiles_n, m_tile, n_tile);
       const int acc = it % C::ACC;
       const uint32_t acc_phase = (uint32_t)(it / C::ACC) & 1u;
-      wait_parity(tfull_bar(acc), acc_phase, stop, p.status, 8);
+      wait_parity(tfull_bar(acc), acc_phase, stop, p.status, p.wait_cycles, 8);
       __syncwarp();
       ptx::tc_fence_after();
-      if (it == 0) stamp(4);  // the first item's accumulator is complete
       const int row = m_tile * BM + trow;  // output row, or (SWAP) output column
-      const bool store = (SWAP || row < p.M) && !(p.dbg & 4) && !*stop;
+      const bool store = (SWAP || row < p.M) && !*stop;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)acc * BN;
       const size_t goff = (size_t)row * p.ldd + (size_t)n_tile * BN;
       // 32 accumulator columns of this thread's row -> (+C) -> fp32 or bf16 output
@@ -476,7 +433,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
         // finishes columns [32 c, 32 c + 32): the others store that chunk of their accumulator into
         // its shared memory, it adds the four in CTA order and stores the result.
         const uint32_t crank = ptx::cluster_ctarank();
-        if (it > 0) wait_parity_cluster(xfree_bar, (uint32_t)(it - 1) & 1u, stop, p.status, 512);
+        if (it > 0) wait_parity_cluster(xfree_bar, (uint32_t)(it - 1) & 1u, stop, p.status, p.wait_cycles, 512);
         uint32_t mine[32];
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -504,7 +461,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
           for (uint32_t o = 0; o < 4; ++o)
             if (o != crank) ptx::mbar_arrive_release_cluster(ptx::map_to_cta(xfull_bar, o));
         }
-        wait_parity_cluster(xfull_bar, (uint32_t)it & 1u, stop, p.status, 512);
+        wait_parity_cluster(xfull_bar, (uint32_t)it & 1u, stop, p.status, p.wait_cycles, 512);
         if (store && !*stop) {
           uint32_t r[32];
 #pragma unroll
@@ -538,7 +495,6 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
           for (uint32_t o = 0; o < 4; ++o)
             if (o != crank) ptx::mbar_arrive_cluster(ptx::map_to_cta(xfree_bar, o));
         }
-        if (it == 0) stamp(5);
         continue;
       }
       if (splits == 1) {
@@ -552,7 +508,6 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
-        if (it == 0) stamp(5);  // the first item is stored
         continue;
       }
       // ---- split-K: leave this CTA's partial (16-byte units, [column group][row]: a warp stores 512
@@ -650,6 +605,40 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
 //   warps 3-6   epilogue: TMEM -> registers -> bf16 -> swizzled shared staging -> TMA store;
 //               the accumulator is handed back as soon as it is in registers, so the next
 //               tile's MMAs overlap the stores
+// One launch takes a LIST of problems (up to kMaxProb): each has its own activation, weights,
+// output and K split.  The tile list is the concatenation of the problems' tiles, dealt
+// round-robin to the clusters, so that small problems fill the slots a large one leaves idle in
+// its last wave (q/k/v and gate/up of a layer share the activation; a whole layer's seven
+// projections can share a launch).  A problem may carry a ready flag: the producer then waits
+// (bounded) until the word at that address is >= the given value before it reads the problem's
+// activation - the hook for an exchange that fills the activation buffer while the launch is
+// already running.
+constexpr int kMaxProb = 8;
+
+struct PairProb {
+  SegParams seg[3];
+  int M;          // rows of the activation / output
+  int tiles_m2;   // 256-row blocks
+  int tile_end;   // tiles of problems 0..this one
+  int s_units;    // K stages per tile
+  const int* flag;  // optional: activation is complete when *flag >= flag_value
+  int flag_value;
+};
+
+struct PairParams {
+  int nprob;
+  PairProb prob[kMaxProb];
+  uint32_t tx_a[3], tx_b[3];  // bytes one A / B tile load of the segment signals
+  int* status;
+  long long wait_cycles;
+};
+
+struct PairMaps {
+  CUtensorMap a[kMaxProb][3];  // activation codes per problem and K segment
+  CUtensorMap b[kMaxProb][3];  // weight codes
+  CUtensorMap d[kMaxProb];     // outputs
+};
+
 template <int STAGES_, int NSLOT_>
 struct PairCfgT {
   static constexpr int STAGES = STAGES_;
@@ -666,12 +655,11 @@ struct PairCfgT {
   static constexpr uint32_t SF_SLOT_COLS = 8 + 16;
   static constexpr size_t SMEM = 1024 + STAGING_BYTES + (size_t)STAGES * STAGE_BYTES + 256;
 };
+using PairCfg = PairCfgT<5, 2>;
 
-template <class C>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(C::THREADS, 1)
-mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
-                       const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmA2,
-                       const __grid_constant__ GroupMaps gm) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::THREADS, 1)
+mixed_gemm_pair_kernel(const __grid_constant__ PairParams p, const __grid_constant__ PairMaps gm) {
+  using C = PairCfg;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;  // staging first, then the stage ring, then barriers
@@ -689,6 +677,7 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
+  const long long wait_limit = p.wait_cycles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -700,13 +689,11 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     ptx::mbar_init(tempty_bar, 8);  // four epilogue warps in each CTA (used in the leader only)
     *stop = 0;
     ptx::fence_mbar_init();
-    ptx::prefetch_tmap(&tmA0);
-    ptx::prefetch_tmap(&tmA1);
-    ptx::prefetch_tmap(&tmA2);
     for (int j = 0; j < p.nprob; ++j) {
-      ptx::prefetch_tmap(&gm.b[j][0]);
-      ptx::prefetch_tmap(&gm.b[j][1]);
-      ptx::prefetch_tmap(&gm.b[j][2]);
+      for (int s = 0; s < 3; ++s) {
+        ptx::prefetch_tmap(&gm.a[j][s]);
+        ptx::prefetch_tmap(&gm.b[j][s]);
+      }
       ptx::prefetch_tmap(&gm.d[j]);
     }
   }
@@ -722,76 +709,65 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
   const uint32_t tmem_base = *tmem_holder;
   ptx::grid_dep_wait();  // the prologue above touched no global memory
 
-  const int tiles_m2 = (p.M + 255) / 256;
-  const int total_tiles = p.tile_end[p.nprob - 1];
+  const int total_tiles = p.prob[p.nprob - 1].tile_end;
   const int first_tile = (int)ptx::cluster_id_x(), tile_step = (int)ptx::nclusters_x();
   // pair tile t -> (problem, 256-row block, 256-column block of that problem); rows vary fastest
   auto locate = [&](int t, int& prob, int& m_pt, int& n_tile) {
     prob = 0;
     int start = 0;
-    while (prob + 1 < p.nprob && t >= p.tile_end[prob]) start = p.tile_end[prob++];
-    raster(t - start, tiles_m2, (p.tile_end[prob] - start) / tiles_m2, m_pt, n_tile);
+    while (prob + 1 < p.nprob && t >= p.prob[prob].tile_end) start = p.prob[prob++].tile_end;
+    const int tm2 = p.prob[prob].tiles_m2;
+    raster(t - start, tm2, (p.prob[prob].tile_end - start) / tm2, m_pt, n_tile);
   };
-  // Work list of this cluster: pieces (tile, K stages [s0, s1)).  Without stream-K a piece is a
-  // whole tile and tiles go round-robin; with it the cluster owns units [u_begin, u_end).
-  const int S_units = p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages;
-  const int seg_off1 = p.seg[0].nstages, seg_off2 = seg_off1 + p.seg[1].nstages;
-  const long long U_total = (long long)total_tiles * S_units;
-  const int u_begin = (int)(U_total * first_tile / tile_step), u_end = (int)(U_total * (first_tile + 1) / tile_step);
-  struct Piece { int tile, s0, s1; };
-  auto next_piece = [&](int& cur, Piece& pc) -> bool {
-    if (p.streamk) {
-      if (cur >= u_end) return false;
-      pc.tile = cur / S_units;
-      pc.s0 = cur - pc.tile * S_units;
-      pc.s1 = min(S_units, pc.s0 + (u_end - cur));
-      cur += pc.s1 - pc.s0;
-      return true;
-    }
-    if (cur >= total_tiles) return false;
-    pc.tile = cur;
-    pc.s0 = 0;
-    pc.s1 = S_units;
-    cur += tile_step;
-    return true;
-  };
-  const int cur0 = p.streamk ? u_begin : first_tile;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     const bool leader = ptx::elect_one();
     int stage = 0;
     uint32_t phase = 0;
-    Piece pc;
-    for (int cur = cur0; next_piece(cur, pc);) {
-      const int t = pc.tile;
+    int flag_seen = -1;  // last problem whose ready flag has been seen up
+    for (int t = first_tile; t < total_tiles; t += tile_step) {
       int prob, m_pt, n_tile;
       locate(t, prob, m_pt, n_tile);
+      const PairProb& pp = p.prob[prob];
+      if (pp.flag != nullptr && flag_seen != prob) {
+        // the activation of this problem is being filled by somebody else (a copy engine, another
+        // GPU): wait until its flag says it is complete, then order the tensor-map reads after it
+        const long long t0 = clock64();
+        for (;;) {
+          int v;
+          asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(pp.flag) : "memory");
+          if (v - pp.flag_value >= 0 || *stop) break;
+          __nanosleep(200);
+          if (clock64() - t0 > wait_limit) {
+            *stop = 1;
+            atomicOr(p.status, 1024);
+          }
+        }
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        flag_seen = prob;
+      }
       const int m_row0 = m_pt * 256 + (int)rank * 128, n_row0 = n_tile * 256 + (int)rank * 128;
 #pragma unroll 1
       for (int seg = 0; seg < 3; ++seg) {
-        const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
-        const CUtensorMap* ta = seg == 0 ? &tmA0 : (seg == 1 ? &tmA1 : &tmA2);
+        const SegParams sp = seg == 0 ? pp.seg[0] : (seg == 1 ? pp.seg[1] : pp.seg[2]);
+        const CUtensorMap* ta = &gm.a[prob][seg];
         const CUtensorMap* tb = &gm.b[prob][seg];
         const uint32_t tx_ab = seg == 0 ? p.tx_a[0] + p.tx_b[0]
                                         : (seg == 1 ? p.tx_a[1] + p.tx_b[1] : p.tx_a[2] + p.tx_b[2]);
         // a CTA whose 128 rows lie wholly beyond M reads the last real row block's scales (its
         // accumulator rows are never stored), so that no copy leaves the scale buffer
-        const int row_blk = min(m_pt * 2 + (int)rank, (p.M + 127) / 128 - 1);
+        const int row_blk = min(m_pt * 2 + (int)rank, (pp.M + 127) / 128 - 1);
         const uint8_t* sfa_row = sp.sfa + (size_t)row_blk * sp.katoms * 512;
-        const uint8_t* sfb_row = p.sfb_g[prob][seg] + (size_t)(n_tile * 2) * sp.katoms * 512;
-        const int so = seg == 0 ? 0 : (seg == 1 ? seg_off1 : seg_off2);
-        const int s_lo = max(pc.s0 - so, 0), s_hi = min(pc.s1 - so, sp.nstages);
+        const uint8_t* sfb_row = sp.sfb + (size_t)(n_tile * 2) * sp.katoms * 512;
 #pragma unroll 1
-        for (int s = s_lo; s < s_hi; ++s) {
-          wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, 1);
+        for (int s = 0; s < sp.nstages; ++s) {
+          wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, wait_limit, 1);
           const int atom0 = seg == 0 ? 2 * s : s;
           const int natoms = seg == 0 ? min(2, sp.katoms - atom0) : 1;
           const uint32_t sbase = ring + stage * C::STAGE_BYTES;
           const uint32_t fb = full_bar(stage);
-          if (leader && (p.dbg & 2)) {
-            ptx::mbar_arrive(fb);
-          } else if (leader) {
+          if (leader) {
             ptx::mbar_expect_tx(fb, tx_ab + (uint32_t)natoms * 512u * 3u);
             ptx::tma_load_2d(sbase, ta, s * 128, m_row0, fb);
             ptx::tma_load_2d(sbase + C::A_BYTES, tb, s * 128, n_row0, fb);
@@ -809,11 +785,13 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     // ------------------------------------------------------------ relay: stage landed -> leader's ready barrier
     int stage = 0;
     uint32_t phase = 0;
-    Piece pc;
-    for (int cur = cur0; next_piece(cur, pc);) {
+    for (int t = first_tile; t < total_tiles; t += tile_step) {
+      int prob, m_pt, n_tile;
+      locate(t, prob, m_pt, n_tile);
+      const int s_units = p.prob[prob].s_units;
 #pragma unroll 1
-      for (int s = pc.s0; s < pc.s1; ++s) {
-        wait_parity(full_bar(stage), phase, stop, p.status, 64);
+      for (int s = 0; s < s_units; ++s) {
+        wait_parity(full_bar(stage), phase, stop, p.status, wait_limit, 64);
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ready_bar(stage), 0));
         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -830,21 +808,21 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
       int stage = 0;
       uint32_t phase = 0, slot = 0;
       int it = 0;
-      Piece pc;
-      for (int cur = cur0; next_piece(cur, pc); ++it) {
-        wait_parity(tempty_bar, ((uint32_t)it & 1u) ^ 1u, stop, p.status, 4);
+      for (int t = first_tile; t < total_tiles; t += tile_step, ++it) {
+        int prob, m_pt, n_tile;
+        locate(t, prob, m_pt, n_tile);
+        const PairProb& pp = p.prob[prob];
+        wait_parity(tempty_bar, ((uint32_t)it & 1u) ^ 1u, stop, p.status, wait_limit, 4);
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base;
         uint32_t accumulate = 0;
 #pragma unroll 1
         for (int seg = 0; seg < 3; ++seg) {
-          const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
+          const SegParams sp = seg == 0 ? pp.seg[0] : (seg == 1 ? pp.seg[1] : pp.seg[2]);
           const uint32_t id0 = seg == 0 ? kIdesc[0] : (seg == 1 ? kIdesc[1] : kIdesc[2]);
-          const int so = seg == 0 ? 0 : (seg == 1 ? seg_off1 : seg_off2);
-          const int s_lo = max(pc.s0 - so, 0), s_hi = min(pc.s1 - so, sp.nstages);
 #pragma unroll 1
-          for (int s = s_lo; s < s_hi; ++s) {
-            wait_parity(ready_bar(stage), phase, stop, p.status, 2);
+          for (int s = 0; s < sp.nstages; ++s) {
+            wait_parity(ready_bar(stage), phase, stop, p.status, wait_limit, 2);
             ptx::tc_fence_after();
             const uint32_t sbase = ring + stage * C::STAGE_BYTES;
             const uint32_t sfa_lo = ptx::desc_lo(sbase + C::A_BYTES + C::B_BYTES);
@@ -852,10 +830,9 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
             const uint32_t sfa_t = tmem_base + C::SF_COL0 + slot * C::SF_SLOT_COLS;
             const uint32_t sfb_t = sfa_t + 8;
             const uint32_t a_lo = ptx::desc_lo(sbase), b_lo = ptx::desc_lo(sbase + C::A_BYTES);
+            // K elements left in this segment, in MMA steps (64 for FP4, 32 for FP6 / FP8)
             const int nm = seg == 0 ? min(4, (sp.kseg - s * 256) >> 6) : min(4, (sp.kseg - s * 128) >> 5);
-            if (leader && (p.dbg & 1)) {
-              ptx::tc_commit_pair(empty_bar(stage), 3);
-            } else if (leader) {
+            if (leader) {
               ptx::tc_cp_sf_pair(sfa_t, sfa_lo, ptx::kDescHiSf);
               ptx::tc_cp_sf_pair(sfb_t, sfb_lo, ptx::kDescHiSf);
               ptx::tc_cp_sf_pair(sfb_t + 4, sfb_lo + 64, ptx::kDescHiSf);
@@ -902,190 +879,54 @@ mixed_gemm_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap t
     const uint32_t tempty_leader = ptx::map_to_cta(tempty_bar, 0);
     const bool issuer = warp == 3 && lane == 0;
     int it = 0;
-    Piece pc;
-    unsigned long long* trace = nullptr;
-    if (issuer && p.sk_flags && (p.dbg & 8))
-      trace = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(p.sk_flags) + 20480) + (first_tile * 2 + (int)rank) * 8;
-    auto stamp = [&](int i) {
-      if (trace) {
-        unsigned long long ns;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
-        trace[i] = ns;
-      }
-    };
-    stamp(0);
-    for (int cur = cur0; next_piece(cur, pc); ++it) {
-      const int t = pc.tile;
+    for (int t = first_tile; t < total_tiles; t += tile_step, ++it) {
       int prob, m_pt, n_tile;
       locate(t, prob, m_pt, n_tile);
-      // what this piece is: a whole tile, the head of a tile other clusters complete (this CTA
-      // finishes it with their partials), or a later part of a tile (this CTA leaves a partial)
-      const bool contributor = pc.s0 > 0;
-      const bool head = pc.s0 == 0 && pc.s1 < S_units;
-      const int me = first_tile;  // cluster index
-      int n_contrib = 0;
-      if (head) {
-        // clusters me+1, me+2, ... own the rest of this tile's units
-        const long long tile_end_unit = (long long)(t + 1) * S_units;
-        while (me + 1 + n_contrib < tile_step && U_total * (me + 1 + n_contrib) / tile_step < tile_end_unit) ++n_contrib;
-      }
-      wait_parity(tfull_bar, (uint32_t)it & 1u, stop, p.status, 8);
+      wait_parity(tfull_bar, (uint32_t)it & 1u, stop, p.status, wait_limit, 8);
       __syncwarp();
       ptx::tc_fence_after();
-      if (it == 0) stamp(1);
-      if (head) stamp(3);
-      if (head) {
-        // The other parts were computed first thing by their clusters; wait (bounded) for them.  One
-        // thread polls, with back-off: many threads spinning on a flag starve the store that sets it.
-        if (issuer) {
-          for (int k = 0; k < n_contrib; ++k) {
-            const int* f = p.sk_flags + ((size_t)(me + 1 + k) * 2 + rank) * kSkFlagStride;
-            const long long t0 = clock64();
-            for (;;) {
-              int v;
-              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-              if (v != 0 || *stop) break;
-              __nanosleep(100);
-              if (clock64() - t0 > kWaitLimitCycles) { *stop = 1; atomicOr(p.status, 128); }
-            }
-          }
-        }
-        ptx::named_barrier_sync(1, 128);
-        __threadfence();
-        stamp(4);
-      }
-      if (!contributor && !head) {
-        // Whole tile.  Drain the accumulator in one go: every 32-column chunk is rounded to bf16 as it
-        // arrives, so the whole 256-column row fits in 128 registers and TMEM goes back to the MMA
-        // warp before the first byte is staged; the staging and the stores then overlap the next
-        // tile's MMAs instead of holding them up.
-        uint32_t pk[128];
+      // Drain the accumulator in one go: every 32-column chunk is rounded to bf16 as it arrives, so
+      // the whole 256-column row fits in 128 registers and TMEM goes back to the MMA warp before the
+      // first byte is staged; the staging and the stores then overlap the next tile's MMAs instead
+      // of holding them up.
+      uint32_t pk[128];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r0[32], r1[32];
-          ptx::tmem_ld_32x32(taddr + c * 64, r0);
-          ptx::tmem_ld_32x32(taddr + c * 64 + 32, r1);
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r0[k * 2]), __uint_as_float(r0[k * 2 + 1]));
-            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r1[k * 2]), __uint_as_float(r1[k * 2 + 1]));
-            pk[c * 32 + k] = *reinterpret_cast<uint32_t*>(&h0);
-            pk[c * 32 + 16 + k] = *reinterpret_cast<uint32_t*>(&h1);
-          }
-        }
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader);
-        const int m0 = m_pt * 256 + (int)rank * 128;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (issuer) ptx::bulk_wait_group_read<C::NSLOT - 1>();  // the slot's last store has read it
-          ptx::named_barrier_sync(1, 128);
-          const uint32_t slot_addr = base + (uint32_t)(j % C::NSLOT) * C::PANEL_BYTES;
-          const uint32_t prow = slot_addr + trow * 128;
-#pragma unroll
-          for (int c = 0; c < 8; ++c)
-            ptx::sts_v4(prow + ((uint32_t)(c ^ (trow & 7)) << 4), pk[j * 32 + c * 4], pk[j * 32 + c * 4 + 1],
-                        pk[j * 32 + c * 4 + 2], pk[j * 32 + c * 4 + 3]);
-          ptx::fence_proxy_async_smem();
-          ptx::named_barrier_sync(1, 128);
-          if (issuer) {
-            if (m0 < p.M && !*stop && !(p.dbg & 4)) ptx::tma_store_2d(&gm.d[prob], n_tile * 256 + j * 64, m0, slot_addr);
-            ptx::bulk_commit_group();  // one group per panel, also when nothing was stored
-          }
-        }
-        if (it == 0) stamp(7);
-        continue;
-      }
-      // Partials are private scratch, laid out [panel][4-column group][row] in 16-byte units so that a
-      // warp's store (and the finisher's load) covers 512 contiguous bytes; rows beyond M are skipped.
-      uint4* my_partial = reinterpret_cast<uint4*>(p.sk_partials + (size_t)(me * 2 + (int)rank) * 128 * 256) + trow;
-      const bool row_live = m_pt * 256 + (int)rank * 128 + trow < p.M;
-#pragma unroll 1
-      for (int j = 0; j < 4; ++j) {
-        // the store that last used this staging slot has finished reading it
-        if (issuer) ptx::bulk_wait_group_read<C::NSLOT - 1>();
-        ptx::named_barrier_sync(1, 128);
+      for (int c = 0; c < 4; ++c) {
         uint32_t r0[32], r1[32];
-        ptx::tmem_ld_32x32(taddr + j * 64, r0);
-        ptx::tmem_ld_32x32(taddr + j * 64 + 32, r1);
+        ptx::tmem_ld_32x32(taddr + c * 64, r0);
+        ptx::tmem_ld_32x32(taddr + c * 64 + 32, r1);
         ptx::tmem_ld_wait();
-        if (j == 3) {  // the accumulator is in registers: hand TMEM back to the MMA warp
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader);
-        }
-        if (contributor) {
-          // leave the fp32 partial of this row's 64 columns for the finishing cluster
-          if (row_live) {
-            uint4* dst = my_partial + (size_t)j * 16 * 128;
 #pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              __stcg(dst + v * 128, make_uint4(r0[v * 4], r0[v * 4 + 1], r0[v * 4 + 2], r0[v * 4 + 3]));
-              __stcg(dst + (8 + v) * 128, make_uint4(r1[v * 4], r1[v * 4 + 1], r1[v * 4 + 2], r1[v * 4 + 3]));
-            }
-          }
-          if (issuer) ptx::bulk_commit_group();  // keeps the one-group-per-panel count
-          continue;
+        for (int k = 0; k < 16; ++k) {
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r0[k * 2]), __uint_as_float(r0[k * 2 + 1]));
+          __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r1[k * 2]), __uint_as_float(r1[k * 2 + 1]));
+          pk[c * 32 + k] = *reinterpret_cast<uint32_t*>(&h0);
+          pk[c * 32 + 16 + k] = *reinterpret_cast<uint32_t*>(&h1);
         }
-        if (row_live) {
-          for (int k = 0; k < n_contrib; ++k) {
-            const uint4* src = reinterpret_cast<const uint4*>(p.sk_partials + (size_t)((me + 1 + k) * 2 + (int)rank) * 128 * 256) +
-                               (size_t)j * 16 * 128 + trow;
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader);
+      const int m0 = m_pt * 256 + (int)rank * 128;
 #pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              const uint4 a = __ldcg(src + v * 128), b = __ldcg(src + (8 + v) * 128);
-              r0[v * 4] = __float_as_uint(__uint_as_float(r0[v * 4]) + __uint_as_float(a.x));
-              r0[v * 4 + 1] = __float_as_uint(__uint_as_float(r0[v * 4 + 1]) + __uint_as_float(a.y));
-              r0[v * 4 + 2] = __float_as_uint(__uint_as_float(r0[v * 4 + 2]) + __uint_as_float(a.z));
-              r0[v * 4 + 3] = __float_as_uint(__uint_as_float(r0[v * 4 + 3]) + __uint_as_float(a.w));
-              r1[v * 4] = __float_as_uint(__uint_as_float(r1[v * 4]) + __uint_as_float(b.x));
-              r1[v * 4 + 1] = __float_as_uint(__uint_as_float(r1[v * 4 + 1]) + __uint_as_float(b.y));
-              r1[v * 4 + 2] = __float_as_uint(__uint_as_float(r1[v * 4 + 2]) + __uint_as_float(b.z));
-              r1[v * 4 + 3] = __float_as_uint(__uint_as_float(r1[v * 4 + 3]) + __uint_as_float(b.w));
-            }
-          }
-        }
+      for (int j = 0; j < 4; ++j) {
+        if (issuer) ptx::bulk_wait_group_read<C::NSLOT - 1>();  // the slot's last store has read it
+        ptx::named_barrier_sync(1, 128);
         const uint32_t slot_addr = base + (uint32_t)(j % C::NSLOT) * C::PANEL_BYTES;
         const uint32_t prow = slot_addr + trow * 128;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint32_t* r = c < 4 ? &r0[c * 8] : &r1[(c - 4) * 8];
-          uint32_t w[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[k * 2]), __uint_as_float(r[k * 2 + 1]));
-            w[k] = *reinterpret_cast<uint32_t*>(&h);
-          }
-          ptx::sts_v4(prow + ((uint32_t)(c ^ (trow & 7)) << 4), w[0], w[1], w[2], w[3]);
-        }
+        for (int c = 0; c < 8; ++c)
+          ptx::sts_v4(prow + ((uint32_t)(c ^ (trow & 7)) << 4), pk[j * 32 + c * 4], pk[j * 32 + c * 4 + 1],
+                      pk[j * 32 + c * 4 + 2], pk[j * 32 + c * 4 + 3]);
         ptx::fence_proxy_async_smem();
         ptx::named_barrier_sync(1, 128);
-        const int m0 = m_pt * 256 + (int)rank * 128;
         if (issuer) {
-          if (m0 < p.M && !*stop && !(p.dbg & 4)) ptx::tma_store_2d(&gm.d[prob], n_tile * 256 + j * 64, m0, slot_addr);
+          if (m0 < p.prob[prob].M && !*stop) ptx::tma_store_2d(&gm.d[prob], n_tile * 256 + j * 64, m0, slot_addr);
           ptx::bulk_commit_group();  // one group per panel, also when nothing was stored
         }
       }
-      if (it == 0) stamp(7);
-      if (contributor) {
-        __threadfence();  // every thread's partial is visible device-wide before the flag goes up
-        ptx::named_barrier_sync(1, 128);
-        if (issuer) {
-          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.sk_flags + ((size_t)me * 2 + rank) * kSkFlagStride), "r"(1)
-                       : "memory");
-          stamp(2);
-        }
-      } else if (head) {
-        stamp(5);
-        ptx::named_barrier_sync(1, 128);  // all 128 threads have read the partials
-        if (issuer)
-          for (int k = 0; k < n_contrib; ++k) p.sk_flags[((size_t)(me + 1 + k) * 2 + rank) * kSkFlagStride] = 0;  // for the next launch
-      }
     }
     if (issuer) ptx::bulk_wait_group0();
-    stamp(6);
   }
 
   // ------------------------------------------------------------ teardown
@@ -1208,11 +1049,8 @@ Plan make_plan(int M, int N, int KN, int KS, int KO, const size_t* pitches) {
   return pl;
 }
 
-int choose_bn(int M, int N, int sms) {
-  if (const char* e = std::getenv("MG_GEMM_BN")) {
-    int v = std::atoi(e);
-    if (v == 128 || (v == 256 && N % 256 == 0)) return v;
-  }
+int choose_bn(int M, int N, int sms, const mg::Options& opt) {
+  if (opt.gemm_bn == 128 || (opt.gemm_bn == 256 && N % 256 == 0)) return opt.gemm_bn;
   if (N % 256 != 0) return 128;
   const int tm = (M + BM - 1) / BM;
   auto eff = [&](int bn, double w) {
@@ -1292,31 +1130,26 @@ int cluster_split_capacity() {
 }
 
 // Cluster split-K is taken when the 128 x 128 tiles of the problem fit the clusters the device
-// holds at one time (at most a quarter of the SMs) and every quarter of K has at least two stages.  At these sizes a launch is bound by the fixed
-// cost of a K stage on the tensor pipe (about 255 ns, whatever the stage holds), so a quarter of
-// the stages per CTA is what shortens it; the accumulators meet in distributed shared memory, not
-// in L2.  MG_GEMM_CSPLIT=0 turns it off.
-bool csplit_wanted(int M, int N, int s_units, int sms) {
-  if (N % 128 != 0) return false;
-  if (const char* e = std::getenv("MG_GEMM_CSPLIT"))
-    if (e[0] == '0') return false;
+// holds at one time (at most a quarter of the SMs) and every quarter of K has at least two stages.
+// At these sizes a launch is bound by the fixed cost of a K stage on the tensor pipe (about 255 ns,
+// whatever the stage holds), so a quarter of the stages per CTA is what shortens it; the
+// accumulators meet in distributed shared memory, not in L2.  Option GEMM_CSPLIT = 0 turns it off.
+bool csplit_wanted(int M, int N, int s_units, int sms, const mg::Options& opt) {
+  if (N % 128 != 0 || opt.gemm_csplit == 0) return false;
   const int tiles = (M + BM - 1) / BM * (N / 128);
   return tiles <= sms / 4 && s_units >= 8 && tiles <= cluster_split_capacity();
 }
 
-// Scratch behind the padded copies: a 64 KB zone that must read zero between launches (stream-K
-// flags, one cache line each, from byte 0; debug time stamps from 20 KB; split-K tile counters from
-// 32 KB), then fp32 partials: one 128 x 256 block per CTA of up to 74 clusters for stream-K, or
-// [split][tile][column group][row] for split-K.  A launch uses one of the two, never both.
-constexpr int kSkMaxClusters = 74;
-constexpr size_t kSkFlagBytes = 64 * 1024;
-constexpr size_t kSpCounterOff = 32 * 1024;
-constexpr int kSpMaxTiles = (int)((kSkFlagBytes - kSpCounterOff) / sizeof(unsigned long long));
-constexpr size_t kSkBytes = kSkFlagBytes + (size_t)kSkMaxClusters * 2 * 128 * 256 * sizeof(float);
+// Scratch behind the padded copies, for split-K: 32 KB of tile counters (each carries a per-launch
+// token, so the bytes may hold anything when a call starts), then fp32 partials
+// [split][tile][column group][row].
+constexpr size_t kSpCounterBytes = 32 * 1024;
+constexpr int kSpMaxTiles = (int)(kSpCounterBytes / sizeof(unsigned long long));
 
 // Split-K plan of the single-CTA kernel: only when the tiles occupy at most half of the SMs, each
 // split keeps at least 16 K stages (below that the partial round trip through L2 costs more than
-// the shorter K loop saves: 12.6 against 8.9 us at 16 x 4096 x 4096), at most eight splits.  MG_GEMM_SPLITK=0 turns it off, =n forces n.
+// the shorter K loop saves: 12.6 against 8.9 us at 16 x 4096 x 4096), at most eight splits.
+// Option GEMM_SPLITK = 0 turns it off, n > 0 forces n splits.
 struct SplitPlan {
   int splits, rows;
   size_t bytes;  // fp32 partials
@@ -1325,20 +1158,19 @@ struct SplitPlan {
 // for M <= 32 when there are many weight tiles or a long K (16 x 14336 x 4096: 11.2 against 13.8 us,
 // 16 x 8192 x 28672: 28.1 against 37.5 us) and loses when M > 32, where its element-wise transposed
 // stores dominate (128 x 4096 x 4096: 16.3 against 9.8 us), or when the problem is a handful of
-// short tiles (16 x 4096 x 4096: 9.9 against 8.9 us).  MG_GEMM_SWAP=0 / 1 turns it off / on for every
-// M <= 128.
-bool swap_wanted(int M, int N, int s_units) {
+// short tiles (16 x 4096 x 4096: 9.9 against 8.9 us).  Option GEMM_SWAP = 0 / 1 turns it off / on
+// for every M <= 128.
+bool swap_wanted(int M, int N, int s_units, const mg::Options& opt) {
   if (M > 128 || N % 128 != 0) return false;
-  if (const char* e = std::getenv("MG_GEMM_SWAP")) return e[0] != '0';
+  if (opt.gemm_swap >= 0) return opt.gemm_swap != 0;
   return M <= 32 && (N / 128 >= 64 || s_units >= 32);
 }
 int swap_bn(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
 
-SplitPlan plan_splitk(int M, int N, int s_units, int bn, int sms, bool swap) {
+SplitPlan plan_splitk(int M, int N, int s_units, int bn, int sms, bool swap, const mg::Options& opt) {
   SplitPlan sp{1, 128, 0};
   const int tiles_m = (M + BM - 1) / BM, tiles = swap ? N / 128 : tiles_m * (N / bn);
-  int want = -1;
-  if (const char* e = std::getenv("MG_GEMM_SPLITK")) want = std::atoi(e);
+  const int want = opt.gemm_splitk;
   if (want == 0 || tiles > kSpMaxTiles) return sp;
   int splits = std::min(std::min(sms / tiles, s_units / 16), 8);  // the arrival count has 8 bits
   if (tiles * 2 > sms) splits = 1;
@@ -1350,49 +1182,85 @@ SplitPlan plan_splitk(int M, int N, int s_units, int bn, int sms, bool swap) {
   return sp;
 }
 
-// Off unless MG_GEMM_STREAMK=1.  Measured on B200, a cluster pays about 5 us for the partial it
-// leaves (its accumulator drains to global memory before the next MMAs may start) and 1.5 us per
-// partial it adds, which is more than the part of a wave stream-K saves on the shapes of a
-// Llama-3 layer (2 to 8 us per GEMM), so whole tiles stay the default.
-bool streamk_wanted() {
-  const char* e = std::getenv("MG_GEMM_STREAMK");
-  return e && e[0] == '1';
-}
+// One problem of a CTA-pair launch as the host sees it (device pointers).
+struct PairProblem {
+  const uint8_t* a[3];    // AN, AS, AO
+  const uint8_t* sfa[3];
+  size_t pitch_a[3];
+  const uint8_t* b[3];    // BN, BS, BO
+  const uint8_t* sfb[3];
+  size_t pitch_b[3];
+  int M, N, KN, KS, KO;
+  void* D;
+  int ldd;
+  const int* flag;
+  int flag_value;
+};
 
-// Stream-K flags must read 0 when a launch starts.  Kernels leave them 0, but the workspace is the
-// caller's and may have held anything since, so the bytes a launch will use are cleared on its
-// stream every time (a memset node of at most 19 KB).  Split-K counters need no clearing: they
-// carry a per-launch token.
-int launch_pair(GemmParams& p, const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& a2,
-                const GroupMaps& gm, int sms, void* sk_ws, size_t sk_bytes, cudaStream_t st) {
-  const int tiles = p.tile_end[p.nprob - 1];
-  const int max_clusters = sms / 2 < kSkMaxClusters ? sms / 2 : kSkMaxClusters;
-  int clusters = tiles < max_clusters ? tiles : max_clusters;
-  const long long units = (long long)tiles * (p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages);
-  p.streamk = 0;
-  if (sk_ws && sk_bytes >= kSkBytes) {
-    p.sk_flags = static_cast<int*>(sk_ws);  // also where the debug time stamps go
-    p.sk_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(sk_ws) + kSkFlagBytes);
-    if (streamk_wanted() && tiles % max_clusters != 0 && units >= max_clusters) {
-      // the tiles do not fill whole waves: deal out (tile, K-stage) units instead of tiles
-      p.streamk = 1;
-      clusters = max_clusters;
-      MG_CUDA_TRY(cudaMemsetAsync(sk_ws, 0, (size_t)clusters * 2 * kSkFlagStride * sizeof(int), st));
+// Validates the problems, builds their tensor maps and launches the CTA-pair kernel once.
+// Every code buffer must be readable in place (a pitch the unpacking tensor maps take).
+int launch_pair(int nprob, const PairProblem* pr, int sms, cudaStream_t st) {
+  if (nprob < 1 || nprob > kMaxProb) return MG_ERR_SHAPE;
+  PairParams p{};
+  PairMaps gm;
+  int rc;
+  int tiles = 0;
+  for (int j = 0; j < nprob; ++j) {
+    const PairProblem& q = pr[j];
+    if (q.M <= 0 || q.N <= 0 || q.N % 256 || q.KN < 0 || q.KS < 0 || q.KO < 0 || q.KN + q.KS + q.KO <= 0) return MG_ERR_SHAPE;
+    if (q.KN % 128 || q.KS % 64 || q.KO % 64 || q.ldd < q.N || q.ldd % 8) return MG_ERR_SHAPE;
+    if (!q.D) return MG_ERR_NULL;
+    if (!mg::aligned(q.D, 16)) return MG_ERR_ALIGN;
+    const size_t pitches[6] = {q.pitch_a[0], q.pitch_b[0], q.pitch_a[1], q.pitch_b[1], q.pitch_a[2], q.pitch_b[2]};
+    const Plan pl = make_plan(q.M, q.N, q.KN, q.KS, q.KO, pitches);
+    if (pl.status != MG_OK) return pl.status;
+    if (pl.total) return MG_ERR_ALIGN;  // a buffer would need the padded copy: not in this launch
+    const int kseg[3] = {q.KN, q.KS, q.KO};
+    const int first = q.KN ? 0 : (q.KS ? 1 : 2);
+    for (int seg = 0; seg < 3; ++seg) {
+      // a zero-sized segment still needs valid maps as kernel arguments: alias the first real one
+      const int sg = kseg[seg] ? seg : first;
+      if (!q.a[sg] || !q.sfa[sg] || !q.b[sg] || !q.sfb[sg]) return MG_ERR_NULL;
+      if (!mg::aligned(q.a[sg], 32) || !mg::aligned(q.b[sg], 32) || !mg::aligned(q.sfa[sg], 16) || !mg::aligned(q.sfb[sg], 16))
+        return MG_ERR_ALIGN;
+      const uint64_t kd = sg == 0 ? q.KN / 2 : (sg == 1 ? pl.ksp : pl.kop);
+      const CUtensorMapDataType da = sg == 1 ? CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+      const CUtensorMapDataType db = sg == 0 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B;
+      if ((rc = make_map(&gm.a[j][seg], da, q.a[sg], kd, q.M, pl.pitch[sg * 2], 128, BM))) return rc;
+      if ((rc = make_map(&gm.b[j][seg], db, q.b[sg], kd, q.N, pl.pitch[sg * 2 + 1], 128, 128))) return rc;
     }
+    if ((rc = make_map(&gm.d[j], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, q.D, q.N, q.M, (uint64_t)q.ldd * 2, 64, 128))) return rc;
+    PairProb& d = p.prob[j];
+    d.seg[0] = {q.KN, (q.KN + 255) / 256, (q.KN + 127) / 128, q.sfa[0], q.sfb[0]};
+    d.seg[1] = {q.KS, (q.KS + 127) / 128, (q.KS + 127) / 128, q.sfa[1], q.sfb[1]};
+    d.seg[2] = {q.KO, (q.KO + 127) / 128, (q.KO + 127) / 128, q.sfa[2], q.sfb[2]};
+    d.M = q.M;
+    d.tiles_m2 = (q.M + 255) / 256;
+    tiles += d.tiles_m2 * (q.N / 256);
+    d.tile_end = tiles;
+    d.s_units = d.seg[0].nstages + d.seg[1].nstages + d.seg[2].nstages;
+    d.flag = q.flag;
+    d.flag_value = q.flag_value;
   }
-  int variant = 1;
-  if (const char* e = std::getenv("MG_GEMM_PAIR_VARIANT")) variant = std::atoi(e);
-  if (variant == 0) {
-    using PC = PairCfgT<4, 4>;
-    MG_CUDA_TRY(cudaFuncSetAttribute(mixed_gemm_pair_kernel<PC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PC::SMEM));
-    MG_CUDA_TRY(mg::launch_kernel(mixed_gemm_pair_kernel<PC>, dim3(2 * clusters), dim3(PC::THREADS), PC::SMEM, st, p, a0,
-                                  a1, a2, gm));
-  } else {
-    using PC = PairCfgT<5, 2>;
-    MG_CUDA_TRY(cudaFuncSetAttribute(mixed_gemm_pair_kernel<PC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PC::SMEM));
-    MG_CUDA_TRY(mg::launch_kernel(mixed_gemm_pair_kernel<PC>, dim3(2 * clusters), dim3(PC::THREADS), PC::SMEM, st, p, a0,
-                                  a1, a2, gm));
+  for (int j = nprob; j < kMaxProb; ++j) {  // unused slots: valid maps, never dereferenced
+    for (int seg = 0; seg < 3; ++seg) {
+      gm.a[j][seg] = gm.a[0][seg];
+      gm.b[j][seg] = gm.b[0][seg];
+    }
+    gm.d[j] = gm.d[0];
   }
+  p.nprob = nprob;
+  // A tensor-map load signals the packed byte count of its box on the mbarrier.
+  p.tx_a[0] = BM * 128; p.tx_b[0] = 128 * 128;
+  p.tx_a[1] = BM * 96;  p.tx_b[1] = 128 * 64;
+  p.tx_a[2] = BM * 128; p.tx_b[2] = 128 * 64;
+  p.wait_cycles = mg::wait_limit_cycles();
+  rc = mg::device_status_word(&p.status);
+  if (rc != MG_OK) return rc;
+  const int max_clusters = sms / 2;
+  const int clusters = tiles < max_clusters ? tiles : max_clusters;
+  MG_CUDA_TRY(cudaFuncSetAttribute(mixed_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PairCfg::SMEM));
+  MG_CUDA_TRY(mg::launch_kernel(mixed_gemm_pair_kernel, dim3(2 * clusters), dim3(PairCfg::THREADS), PairCfg::SMEM, st, p, gm));
   return MG_OK;
 }
 
@@ -1403,7 +1271,9 @@ extern "C" size_t mg_matmul_workspace_bytes(int M, int N, int KN, int KS, int KO
   return make_plan(M, N, KN, KS, KO, nullptr).total;
 }
 
-static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
+// `allow_split`: whether split-K through the workspace may be chosen (mg_matmul_static_ws turns it
+// off so that its result does not depend on how large the built-in scratch happens to be).
+static int matmul_impl(bool f32_out, bool allow_split, const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
                        const uint8_t* AO, const uint8_t* BO, const size_t* pitches, int M, int N, int KN, int KS, int KO,
                        const void* C_bf16, void* D_bf16, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
                        const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
@@ -1426,6 +1296,7 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
   mg::DeviceInfo di;
   int rc = mg::device_info(&di);
   if (rc != MG_OK) return rc;
+  const mg::Options opt = mg::options();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   // Buffers whose pitch the unpacking tensor maps cannot take go through a padded copy.
@@ -1451,25 +1322,37 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
 
   // The CTA-pair kernel wants enough 256 x 256 tiles to occupy most SM pairs; smaller problems
   // spread better as 128-row tiles over single SMs.
-  // Stream-K scratch sits behind the padded copies, when the caller's workspace has room for it.
+  bool use_pair = !f32_out && C_bf16 == nullptr && N % 256 == 0 && M > 128;
+  const int pair_tiles = ((M + 255) / 256) * (N / 256);
+  if (opt.gemm_2cta >= 0) use_pair = use_pair && opt.gemm_2cta != 0;
+  else use_pair = use_pair && pair_tiles * 4 >= (di.sm_count / 2) * 3;
+  if (use_pair) {
+    PairProblem q{};
+    const uint8_t* a[3] = {AN, AS, AO};
+    const uint8_t* b[3] = {BN_, BS, BO};
+    const uint8_t* sa[3] = {SFAN, SFAS, SFAO};
+    const uint8_t* sb[3] = {SFBN, SFBS, SFBO};
+    for (int i = 0; i < 3; ++i) {
+      q.a[i] = a[i]; q.b[i] = b[i]; q.sfa[i] = sa[i]; q.sfb[i] = sb[i];
+      q.pitch_a[i] = pl.pitch[2 * i]; q.pitch_b[i] = pl.pitch[2 * i + 1];
+    }
+    q.M = M; q.N = N; q.KN = KN; q.KS = KS; q.KO = KO; q.D = D_bf16; q.ldd = ldd;
+    return launch_pair(1, &q, di.sm_count, st);
+  }
+
+  // Split-K scratch sits behind the padded copies, when the caller's workspace has room for it.
   const size_t sk_off = align_up(pl.total, 1024);
-  void* sk_ws = nullptr;
+  uint8_t* sk_ws = nullptr;
   size_t sk_bytes = 0;
-  if (workspace && mg::aligned(workspace, 1024) && workspace_bytes >= sk_off + kSkFlagBytes) {
+  if (allow_split && workspace && mg::aligned(workspace, 1024) && workspace_bytes >= sk_off + kSpCounterBytes) {
     sk_ws = static_cast<uint8_t*>(workspace) + sk_off;
     sk_bytes = workspace_bytes - sk_off;
   }
-  // stream-K: then small problems also fill every SM pair
-  const bool sk = allow_streamk && sk_ws != nullptr && sk_bytes >= kSkBytes && streamk_wanted();
-  bool use_pair = !f32_out && C_bf16 == nullptr && N % 256 == 0 && (M > 128 || sk);
-  const int pair_tiles = ((M + 255) / 256) * (N / 256);
-  if (const char* e = std::getenv("MG_GEMM_2CTA")) use_pair = use_pair && std::atoi(e) != 0;
-  else use_pair = use_pair && (sk || pair_tiles * 4 >= (di.sm_count / 2) * 3);
   const int s_units = (KN + 255) / 256 + (KS + 127) / 128 + (KO + 127) / 128;
-  const bool csplit = !use_pair && csplit_wanted(M, N, s_units, di.sm_count);
-  const bool swap = !use_pair && !csplit && swap_wanted(M, N, s_units);
+  const bool csplit = csplit_wanted(M, N, s_units, di.sm_count, opt);
+  const bool swap = !csplit && swap_wanted(M, N, s_units, opt);
   // rows of one load of the MMA's column operand: weights, or (decode form) activations
-  const int bn = (use_pair || csplit) ? 128 : (swap ? swap_bn(M) : choose_bn(M, N, di.sm_count));
+  const int bn = csplit ? 128 : (swap ? swap_bn(M) : choose_bn(M, N, di.sm_count, opt));
 
   GemmParams p{};
   p.M = M;
@@ -1483,6 +1366,8 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
   p.C = static_cast<const __nv_bfloat16*>(C_bf16);
   p.D = f32_out ? nullptr : static_cast<__nv_bfloat16*>(D_bf16);
   p.Df32 = f32_out ? static_cast<float*>(D_bf16) : nullptr;
+  p.wait_cycles = mg::wait_limit_cycles();
+  p.skip_load = opt.fault_skip_load > 0 ? opt.fault_skip_load : 0;
   rc = mg::device_status_word(&p.status);
   if (rc != MG_OK) return rc;
   // A tensor-map load signals the packed byte count of its box on the mbarrier.
@@ -1493,8 +1378,6 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
     p.tx_a[1] = BM * 64;      p.tx_b[1] = (uint32_t)bn * 96;
     p.tx_a[2] = BM * 64;      p.tx_b[2] = (uint32_t)bn * 128;
   }
-
-  if (const char* e = std::getenv("MG_GEMM_DEBUG")) p.dbg = std::atoi(e);
 
   CUtensorMap maps[6];
   // a zero-sized segment still needs valid maps as kernel arguments: alias the first real one
@@ -1516,30 +1399,18 @@ static int matmul_impl(bool f32_out, bool allow_streamk, const uint8_t* AN, cons
       if ((rc = make_map(mb, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, BO, pl.kop, N, pl.pitch[5], 128, box_b))) return rc;
     }
   }
-  if (use_pair) {
-    GroupMaps gm;
-    if ((rc = make_map(&gm.d[0], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D_bf16, N, M, (uint64_t)ldd * 2, 64, 128))) return rc;
-    for (int seg = 0; seg < 3; ++seg) {
-      gm.b[0][seg] = maps[seg * 2 + 1];
-      p.sfb_g[0][seg] = p.seg[seg].sfb;
-    }
-    p.nprob = 1;
-    p.tile_end[0] = pair_tiles;
-    return launch_pair(p, maps[0], maps[2], maps[4], gm, di.sm_count, allow_streamk ? sk_ws : nullptr, sk_bytes, st);
-  }
   p.splits = 1;
-  p.sk_flags = static_cast<int*>(sk_ws);  // the debug time stamps go behind them
   if (csplit) {
     p.splits = 4;
     return launch_gemm_cs(p, maps, di.sm_count, st);
   }
   if (sk_ws) {
-    const SplitPlan sp = plan_splitk(M, N, p.seg[0].nstages + p.seg[1].nstages + p.seg[2].nstages, bn, di.sm_count, swap);
-    if (sp.splits > 1 && sk_bytes >= kSkFlagBytes + sp.bytes) {
+    const SplitPlan sp = plan_splitk(M, N, s_units, bn, di.sm_count, swap, opt);
+    if (sp.splits > 1 && sk_bytes >= kSpCounterBytes + sp.bytes) {
       p.splits = sp.splits;
       p.sp_rows = sp.rows;
-      p.sp_counters = reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(sk_ws) + kSpCounterOff);
-      p.sp_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(sk_ws) + kSkFlagBytes);
+      p.sp_counters = reinterpret_cast<unsigned long long*>(sk_ws);
+      p.sp_partials = reinterpret_cast<float*>(sk_ws + kSpCounterBytes);
       static std::atomic<unsigned long long> token{std::random_device{}() | 1ull};
       p.sp_token = (token.fetch_add(0x9E3779B97F4A7C15ull) >> 8) | 1ull;  // 56 bits, never 0
     }
@@ -1576,16 +1447,18 @@ extern "C" int mg_matmul_pitched(const uint8_t* AN, const uint8_t* BN_, const ui
 extern "C" size_t mg_matmul_pitched_workspace_bytes(int M, int N, int KN, int KS, int KO, const size_t* pitches) {
   if (M <= 0 || N <= 0 || KN < 0 || KS < 0 || KO < 0) return 0;
   const size_t need = make_plan(M, N, KN, KS, KO, pitches).total;
-  // On top: what stream-K (CTA-pair kernel) or split-K (single-CTA kernel, few tiles) would use.
-  // A smaller workspace still works, without them.
+  // On top: what split-K of the single-CTA kernel (few tiles, long K) would use, if it may be chosen
+  // for this problem.  A smaller workspace still works, without it.
   mg::DeviceInfo di;
   const int sms = mg::device_info(&di) == MG_OK ? di.sm_count : 148;
+  const mg::Options opt = mg::options();
   const int s_units = (KN + 255) / 256 + (KS + 127) / 128 + (KO + 127) / 128;
-  size_t extra = N % 256 == 0 ? kSkBytes - kSkFlagBytes : 0;
+  size_t extra = 0;
   for (int bn : {128, 256})
-    if (N % bn == 0) extra = std::max(extra, plan_splitk(M, N, s_units, bn, sms, false).bytes);
-  if (M <= 128 && N % 128 == 0) extra = std::max(extra, plan_splitk(M, N, s_units, swap_bn(M), sms, true).bytes);
-  return align_up(need, 1024) + kSkFlagBytes + extra;
+    if (N % bn == 0) extra = std::max(extra, plan_splitk(M, N, s_units, bn, sms, false, opt).bytes);
+  if (M <= 128 && N % 128 == 0) extra = std::max(extra, plan_splitk(M, N, s_units, swap_bn(M), sms, true, opt).bytes);
+  if (extra == 0) return need;
+  return align_up(need, 1024) + kSpCounterBytes + extra;
 }
 
 extern "C" int mg_matmul_f32(const uint8_t* AN, const uint8_t* BN_, const uint8_t* AS, const uint8_t* BS,
@@ -1593,7 +1466,7 @@ extern "C" int mg_matmul_f32(const uint8_t* AN, const uint8_t* BN_, const uint8_
                              const void* C_bf16, float* D_f32, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
                              const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
                              void* workspace, size_t workspace_bytes, void* stream) {
-  return matmul_impl(true, false, AN, BN_, AS, BS, AO, BO, nullptr, M, N, KN, KS, KO, C_bf16, D_f32, ldd, SFAN, SFBN, SFAS,
+  return matmul_impl(true, true, AN, BN_, AS, BS, AO, BO, nullptr, M, N, KN, KS, KO, C_bf16, D_f32, ldd, SFAN, SFBN, SFAS,
                      SFBS, SFAO, SFBO, workspace, workspace_bytes, stream);
 }
 
@@ -1623,66 +1496,55 @@ extern "C" int mg_matmul_group_pitched(int nprob, const uint8_t* AN, const uint8
                                        const uint8_t* SFAS, const uint8_t* SFAO, const uint8_t* const* SFBN,
                                        const uint8_t* const* SFBS, const uint8_t* const* SFBO, void* workspace,
                                        size_t workspace_bytes, void* stream) {
-  if (nprob < 1 || nprob > kMaxGroup || M <= 128 || KN < 0 || KS < 0 || KO < 0 || KN + KS + KO <= 0) return MG_ERR_SHAPE;
-  if (KN % 128 || KS % 64 || KO % 64) return MG_ERR_SHAPE;
+  (void)workspace;
+  (void)workspace_bytes;
+  if (nprob < 1 || nprob > kMaxProb || M <= 128) return MG_ERR_SHAPE;
   if (!pitches_a || !pitches_b || !N || !D_bf16 || !ldd) return MG_ERR_NULL;
-  if ((KN && (!AN || !SFAN)) || (KS && (!AS || !SFAS)) || (KO && (!AO || !SFAO))) return MG_ERR_NULL;
   mg::DeviceInfo di;
   int rc = mg::device_info(&di);
   if (rc != MG_OK) return rc;
-
-  GemmParams p{};
-  GroupMaps gm;
-  CUtensorMap ma[3];
-  const int ksp = round_up(KS, 128), kop = round_up(KO, 128);
-  const int tiles_m2 = (M + 255) / 256;
-  int tiles = 0;
+  PairProblem pr[kMaxProb] = {};
   for (int j = 0; j < nprob; ++j) {
-    if (N[j] <= 0 || N[j] % 256 || ldd[j] < N[j] || ldd[j] % 8 || !D_bf16[j] || !mg::aligned(D_bf16[j], 16)) return MG_ERR_SHAPE;
-    const size_t pitches[6] = {pitches_a[0], pitches_b[j * 3 + 0], pitches_a[1], pitches_b[j * 3 + 1], pitches_a[2],
-                               pitches_b[j * 3 + 2]};
-    const Plan pl = make_plan(M, N[j], KN, KS, KO, pitches);
-    if (pl.status != MG_OK) return pl.status;
-    if (pl.total) return MG_ERR_ALIGN;  // grouped calls read every buffer in place: pitched buffers only
-    const uint8_t* b[3] = {BN_ ? BN_[j] : nullptr, BS ? BS[j] : nullptr, BO ? BO[j] : nullptr};
-    const uint8_t* sfb[3] = {SFBN ? SFBN[j] : nullptr, SFBS ? SFBS[j] : nullptr, SFBO ? SFBO[j] : nullptr};
-    const int kseg[3] = {KN, KS, KO};
-    const int first = KN ? 0 : (KS ? 1 : 2);
-    for (int seg = 0; seg < 3; ++seg) {
-      const int sg = kseg[seg] ? seg : first;
-      if (!b[sg] || !sfb[sg]) return MG_ERR_NULL;
-      if (!mg::aligned(b[sg], 32) || !mg::aligned(sfb[sg], 16)) return MG_ERR_ALIGN;
-      const CUtensorMapDataType dt = sg == 0 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B;
-      const uint64_t kd = sg == 0 ? KN / 2 : (sg == 1 ? ksp : kop);
-      if ((rc = make_map(&gm.b[j][seg], dt, b[sg], kd, N[j], pl.pitch[sg * 2 + 1], 128, 128))) return rc;
-      p.sfb_g[j][seg] = sfb[sg];
-      if (j == 0) {
-        const uint8_t* a = sg == 0 ? AN : (sg == 1 ? AS : AO);
-        if (!mg::aligned(a, 32)) return MG_ERR_ALIGN;
-        const CUtensorMapDataType da = sg == 1 ? CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-        const uint64_t ka = sg == 0 ? KN / 2 : (sg == 1 ? ksp : kop);
-        if ((rc = make_map(&ma[seg], da, a, ka, M, pl.pitch[sg * 2], 128, BM))) return rc;
-      }
+    PairProblem& q = pr[j];
+    q.a[0] = AN; q.a[1] = AS; q.a[2] = AO;
+    q.sfa[0] = SFAN; q.sfa[1] = SFAS; q.sfa[2] = SFAO;
+    q.b[0] = BN_ ? BN_[j] : nullptr; q.b[1] = BS ? BS[j] : nullptr; q.b[2] = BO ? BO[j] : nullptr;
+    q.sfb[0] = SFBN ? SFBN[j] : nullptr; q.sfb[1] = SFBS ? SFBS[j] : nullptr; q.sfb[2] = SFBO ? SFBO[j] : nullptr;
+    for (int i = 0; i < 3; ++i) {
+      q.pitch_a[i] = pitches_a[i];
+      q.pitch_b[i] = pitches_b[j * 3 + i];
     }
-    if ((rc = make_map(&gm.d[j], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D_bf16[j], N[j], M, (uint64_t)ldd[j] * 2, 64, 128)))
-      return rc;
-    tiles += tiles_m2 * (N[j] / 256);
-    p.tile_end[j] = tiles;
+    q.M = M; q.N = N[j]; q.KN = KN; q.KS = KS; q.KO = KO;
+    q.D = D_bf16[j]; q.ldd = ldd[j];
   }
-  p.nprob = nprob;
-  p.M = M;
-  p.N = N[0];
-  p.ldd = ldd[0];
-  p.seg[0] = {KN, (KN + 255) / 256, (KN + 127) / 128, SFAN, nullptr};
-  p.seg[1] = {KS, (KS + 127) / 128, (KS + 127) / 128, SFAS, nullptr};
-  p.seg[2] = {KO, (KO + 127) / 128, (KO + 127) / 128, SFAO, nullptr};
-  rc = mg::device_status_word(&p.status);
+  return launch_pair(nprob, pr, di.sm_count, static_cast<cudaStream_t>(stream));
+}
+
+// ---------------------------------------------------------------- a list of independent problems
+extern "C" int mg_matmul_multi(int nprob, const mg_problem_t* probs, void* stream) {
+  if (!probs) return MG_ERR_NULL;
+  if (nprob < 1 || nprob > kMaxProb) return MG_ERR_SHAPE;
+  mg::DeviceInfo di;
+  int rc = mg::device_info(&di);
   if (rc != MG_OK) return rc;
-  p.tx_a[0] = BM * 128; p.tx_b[0] = 128 * 128;
-  p.tx_a[1] = BM * 96;  p.tx_b[1] = 128 * 64;
-  p.tx_a[2] = BM * 128; p.tx_b[2] = 128 * 64;
-  void* sk_ws = (workspace && mg::aligned(workspace, 1024) && workspace_bytes >= kSkBytes) ? workspace : nullptr;
-  return launch_pair(p, ma[0], ma[1], ma[2], gm, di.sm_count, sk_ws, workspace_bytes, static_cast<cudaStream_t>(stream));
+  PairProblem pr[kMaxProb] = {};
+  for (int j = 0; j < nprob; ++j) {
+    const mg_problem_t& s = probs[j];
+    PairProblem& q = pr[j];
+    if (s.M <= 128) return MG_ERR_SHAPE;
+    q.a[0] = s.AN; q.a[1] = s.AS; q.a[2] = s.AO;
+    q.sfa[0] = s.SFAN; q.sfa[1] = s.SFAS; q.sfa[2] = s.SFAO;
+    q.b[0] = s.BN; q.b[1] = s.BS; q.b[2] = s.BO;
+    q.sfb[0] = s.SFBN; q.sfb[1] = s.SFBS; q.sfb[2] = s.SFBO;
+    for (int i = 0; i < 3; ++i) {
+      q.pitch_a[i] = s.pitch_a[i];
+      q.pitch_b[i] = s.pitch_b[i];
+    }
+    q.M = s.M; q.N = s.N; q.KN = s.KN; q.KS = s.KS; q.KO = s.KO;
+    q.D = s.D_bf16; q.ldd = s.ldd;
+    q.flag = s.ready_flag; q.flag_value = s.ready_value;
+  }
+  return launch_pair(nprob, pr, di.sm_count, static_cast<cudaStream_t>(stream));
 }
 
 // ---------------------------------------------------------------- entry point that allocates nothing
@@ -1723,6 +1585,9 @@ extern "C" int mg_matmul_static_ws(const uint8_t* AN, const uint8_t* BN_, const 
     }
     ws = g_static_ws_ptr[dev];
   }
+  // Only the padded copies live in the array: split-K through scratch is not taken, so the kernel
+  // chosen (and with it the result) is that of mg_matmul given a workspace of exactly
+  // mg_matmul_workspace_bytes() bytes.
   return matmul_impl(false, false, AN, BN_, AS, BS, AO, BO, nullptr, M, N, KN, KS, KO, C_bf16, D_bf16, ldd, SFAN, SFBN,
                      SFAS, SFBS, SFAO, SFBO, ws, (size_t)MG_STATIC_WS_BYTES, stream);
 }

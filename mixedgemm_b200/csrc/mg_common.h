@@ -30,10 +30,31 @@ int device_info(DeviceInfo* out);
 // waits expire).  Resolved with cudaGetSymbolAddress in capi.cu.
 int device_status_word(int** dev_ptr);
 
-// True unless MG_PDL=0: kernels are launched with programmatic stream serialisation, so that a
-// kernel's prologue (barrier set-up, TMEM allocation, descriptor prefetch) overlaps the tail of
-// the kernel before it; every kernel waits (griddepcontrol.wait) before it touches global memory.
+// Switches that choose between kernels or turn a mode off (mg_set_option / mg_get_option).  Each is
+// read from the environment (MG_<NAME>) once, when the library is first used, and can be changed at
+// run time through the C ABI; -1 stands for "let the library decide".
+struct Options {
+  int gemm_bn;        // GEMM_BN: 128 / 256 forces the tile width of the single-CTA kernel
+  int gemm_2cta;      // GEMM_2CTA: 0 / 1 forces the CTA-pair kernel off / on where it applies
+  int gemm_csplit;    // GEMM_CSPLIT: 0 turns the cluster split-K form off
+  int gemm_splitk;    // GEMM_SPLITK: 0 turns split-K through the workspace off, n > 0 forces n splits
+  int gemm_swap;      // GEMM_SWAP: 0 / 1 forces the decode form (weights as the 128-row operand) off / on
+  int pdl;            // PDL: 0 launches without programmatic dependent launch
+  int reorder_ctas;   // REORDER_CTAS: n > 0 caps the quantiser's grid (to share the GPU with another kernel)
+  int fault_skip_load;  // FAULT_SKIP_LOAD: n > 0 makes the GEMM's first CTA withhold its n-th stage load
+                        // (host-side fault injection for the bounded-wait test; the kernel then gives up
+                        // after the wait limit and returns normally)
+};
+Options options();
+
+// True unless the PDL option is 0: kernels are launched with programmatic stream serialisation, so
+// that a kernel's prologue (barrier set-up, TMEM allocation, descriptor prefetch) overlaps the tail
+// of the kernel before it; every kernel waits (griddepcontrol.wait) before it touches global memory.
 bool pdl_enabled();
+
+// Limit of every bounded wait inside the kernels, in SM clock cycles (about one second unless
+// mg_set_wait_limit_us changed it).
+long long wait_limit_cycles();
 
 // <<<grid, block, smem, stream>>> with the programmatic-dependent-launch attribute when enabled.
 template <typename... KArgs, typename... Args>

@@ -70,17 +70,9 @@ def _check(A, B, M, N, split, rows=None, C=None):
     mx = np.abs(y32s - Yo).max() / rms
     assert fro <= REL_FRO_TOL, "fp32 accumulator: rel-Frobenius %.3e" % fro
     assert mx <= MAX_ABS_TOL, "fp32 accumulator: max-abs %.3e RMS" % mx
-    # the bf16 output is the accumulator rounded once, to nearest even.  The fp32 entry point adds the
-    # K stages of a tile in order; with stream-K the bf16 entry point may add two or more partial sums
-    # of the same products instead, so a few results may land on the neighbouring bf16 value.
+    # the bf16 output is the accumulator rounded once, to nearest even
     rne = orc.bf16_round(Y32.cpu().numpy())
-    if not np.array_equal(y16, rne):
-        import os
-        assert os.environ.get("MG_GEMM_STREAMK", "0") == "1", "bf16 output is not RNE(fp32 accumulator)"
-        bad = y16 != rne
-        assert bad.mean() < 2e-3, "too many results off the rounded accumulator: %.2e" % bad.mean()
-        ulp = np.abs(rne[bad]).astype(np.float64) * 2.0 ** -7 + 1e-30
-        assert np.all(np.abs(y16[bad].astype(np.float64) - rne[bad]) <= ulp), "off by more than one bf16 step"
+    assert np.array_equal(y16, rne), "bf16 output is not RNE(fp32 accumulator)"
     # against the bf16-rounded float64 product: Frobenius bound, and max-abs up to one-ulp flips
     yo16 = orc.bf16_round(Yo).astype(np.float64)
     fro16 = np.linalg.norm(y16s - yo16) / np.linalg.norm(yo16)
@@ -102,11 +94,11 @@ def test_small_shapes(M, N, split):
 
 
 @pytest.mark.parametrize("bn", ["128", "256"])
-def test_both_tile_widths(bn, monkeypatch):
-    monkeypatch.setenv("MG_GEMM_CSPLIT", "0")
+def test_both_tile_widths(bn, mgopt):
+    mgopt.setenv("MG_GEMM_CSPLIT", "0")
     """The single-CTA kernel with 128- and 256-column tiles."""
-    monkeypatch.setenv("MG_GEMM_2CTA", "0")
-    monkeypatch.setenv("MG_GEMM_BN", bn)
+    mgopt.setenv("MG_GEMM_2CTA", "0")
+    mgopt.setenv("MG_GEMM_BN", bn)
     M, N, split = 384, 1024, (1280, 768, 128)
     A, B = _quantise(M, N, sum(split), split, seed=9)
     _check(A, B, M, N, split)
@@ -115,22 +107,21 @@ def test_both_tile_widths(bn, monkeypatch):
 @pytest.mark.parametrize("M,N,split", [(256, 256, (256, 128, 128)), (300, 512, (640, 384, 128)),
                                        (129, 256, (128, 0, 0)), (1000, 768, (2560, 1408, 128)),
                                        (640, 256, (384, 192, 64)), (2048, 1024, (2560, 1408, 128))])
-def test_cta_pair_kernel_equals_single_cta_kernel(M, N, split, monkeypatch):
+def test_cta_pair_kernel_equals_single_cta_kernel(M, N, split, mgopt):
     """The CTA-pair kernel (256 x 256 tiles over two SMs, TMA-store epilogue) and the single-CTA
     kernel accumulate the same products in the same order: same bytes, and both pass the oracle."""
     import mixedgemm_b200 as mg
-    monkeypatch.setenv("MG_GEMM_STREAMK", "0")  # same summation order in both kernels
-    monkeypatch.setenv("MG_GEMM_CSPLIT", "0")
+    mgopt.setenv("MG_GEMM_CSPLIT", "0")
     A, B = _quantise(M, N, sum(split), split, seed=M)
     args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
-    monkeypatch.setenv("MG_GEMM_2CTA", "1")
+    mgopt.setenv("MG_GEMM_2CTA", "1")
     Yp = mg.matmul(*args)
-    monkeypatch.setenv("MG_GEMM_2CTA", "0")
+    mgopt.setenv("MG_GEMM_2CTA", "0")
     Ys = mg.matmul(*args)
     torch.cuda.synchronize()
     assert mg.device_status() == 0
     assert torch.equal(Yp.view(torch.int16), Ys.view(torch.int16))
-    monkeypatch.setenv("MG_GEMM_2CTA", "1")
+    mgopt.setenv("MG_GEMM_2CTA", "1")
     _check(A, B, M, N, split)
 
 
@@ -404,12 +395,11 @@ def test_rejects_operands_that_disagree_with_the_inferred_sizes():
 
 @pytest.mark.parametrize("M,Ns,split", [(512, (512, 256, 256), (1280, 640, 128)), (2048, (4096, 1024, 1024), (2560, 1408, 128)),
                                         (300, (256, 768), (8960, 4928, 448)), (100, (256, 256), (256, 128, 128))])
-def test_grouped_weights_equal_separate_calls(M, Ns, split, monkeypatch):
+def test_grouped_weights_equal_separate_calls(M, Ns, split, mgopt):
     """q/k/v- or gate/up-style groups in one launch give the bytes of one launch per weight
     (the last case is too small for the grouped kernel and takes the fallback)."""
     import mixedgemm_b200 as mg
-    monkeypatch.setenv("MG_GEMM_STREAMK", "0")  # tile-per-cluster order in both, so the bytes agree
-    monkeypatch.setenv("MG_GEMM_CSPLIT", "0")
+    mgopt.setenv("MG_GEMM_CSPLIT", "0")
     KN, KS, KO = split
     K = sum(split)
     X = H.make_x(M, K, seed=31)
@@ -426,47 +416,20 @@ def test_grouped_weights_equal_separate_calls(M, Ns, split, monkeypatch):
     _check(A, Bs[-1], M, Ns[-1], split)
 
 
-@pytest.mark.parametrize("M,N,split", [(2048, 4096, (2560, 1408, 128)), (2048, 1024, (2560, 1408, 128)),
-                                       (1000, 768, (8960, 4928, 448)), (16, 4096, (2560, 1408, 128)),
-                                       (1, 1024, (256, 128, 128)), (128, 14336, (2560, 1408, 128)),
-                                       (300, 256, (128, 0, 0))])
-def test_stream_k(M, N, split, monkeypatch):
-    """Stream-K on the CTA-pair kernel (tiles cut along K between clusters, fp32 partials through the
-    workspace), including decode shapes: within the oracle's tolerance, within one bf16 step of the
-    tile-per-cluster result, and repeatable (the flags are left clear)."""
-    import mixedgemm_b200 as mg
-    A, B = _quantise(M, N, sum(split), split, seed=M + N)
-    args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
-    monkeypatch.setenv("MG_GEMM_STREAMK", "1")
-    y1 = mg.matmul(*args)
-    y2 = mg.matmul(*args)
-    torch.cuda.synchronize()
-    assert mg.device_status() == 0
-    assert torch.equal(y1.view(torch.int16), y2.view(torch.int16))
-    monkeypatch.setenv("MG_GEMM_STREAMK", "0")
-    y0 = mg.matmul(*args)
-    d = (y1.float() - y0.float()).abs()
-    assert torch.all(d <= y0.float().abs() * 2.0 ** -7 + 1e-30)
-    assert (d > 0).float().mean().item() < 2e-3
-    monkeypatch.setenv("MG_GEMM_STREAMK", "1")
-    rows = None if M * N <= 1 << 20 else np.unique(np.concatenate([[0, M - 1], np.random.default_rng(0).integers(0, M, 30)]))
-    _check(A, B, M, N, split, rows=rows)
-
-
 @pytest.mark.parametrize("M,N,split,force", [
     (16, 4096, (8960, 4928, 448), None), (384, 512, (8960, 4928, 448), None), (16, 4096, (2560, 1408, 128), "4"),
     (128, 1024, (2560, 1408, 128), "6"), (100, 768, (2560, 1408, 128), "7"), (300, 256, (2560, 1408, 128), "5"),
     (1, 128, (256, 128, 128), "3"), (97, 512, (1280, 704, 64), "5"), (16, 14336, (2560, 1408, 128), "2")])
-def test_split_k(M, N, split, force, monkeypatch):
+def test_split_k(M, N, split, force, mgopt):
     """Problems with few tiles (decode shapes, narrow weight shards) run several CTAs per tile of the
     single-CTA kernel, each over a range of K stages; the CTA that arrives last adds the fp32
     partials in split order.  Same bounds against the oracle, bf16 == RNE(fp32 result) exactly,
     the same bytes on every call (the counters are left clear, the sum order is fixed), within one
     bf16 step of the unsplit kernel, with and without the C addend."""
     import mixedgemm_b200 as mg
-    monkeypatch.setenv("MG_GEMM_CSPLIT", "0")  # otherwise the cluster form takes these shapes
+    mgopt.setenv("MG_GEMM_CSPLIT", "0")  # otherwise the cluster form takes these shapes
     if force is not None:
-        monkeypatch.setenv("MG_GEMM_SPLITK", force)
+        mgopt.setenv("MG_GEMM_SPLITK", force)
     A, B = _quantise(M, N, sum(split), split, seed=3 * M + N)
     args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
     _check(A, B, M, N, split)
@@ -476,10 +439,10 @@ def test_split_k(M, N, split, force, monkeypatch):
     y2 = mg.matmul(*args)
     # the scratch is the caller's: whatever it holds when a launch starts must not matter
     from mixedgemm_b200 import api
-    for buf in api._workspaces.values():
+    for buf in list(api._workspaces.values()) + api._retired:
         buf.fill_(0xAB)
     y3 = mg.matmul(*args)
-    monkeypatch.setenv("MG_GEMM_SPLITK", "0")
+    mgopt.setenv("MG_GEMM_SPLITK", "0")
     y0 = mg.matmul(*args)
     torch.cuda.synchronize()
     assert mg.device_status() == 0
@@ -493,15 +456,15 @@ def test_split_k(M, N, split, force, monkeypatch):
                                        (17, 256, (128, 64, 64)), (32, 1024, (8960, 4928, 448)), (33, 384, (1280, 704, 64)),
                                        (64, 4096, (2560, 1408, 128)), (100, 768, (2560, 1408, 128)),
                                        (128, 14336, (2560, 1408, 128))])
-def test_decode_form(M, N, split, monkeypatch):
+def test_decode_form(M, N, split, mgopt):
     """M <= 128 runs the single-CTA kernel with the operand roles swapped (weights as the 128-row
     operand, activations as a 16/32/64/128-column operand, tile stored transposed).  Same bounds
     against the oracle, with and without the C addend, and the same bytes as the 128-row form:
     every output element is the same K-ordered sum either way."""
     import mixedgemm_b200 as mg
-    monkeypatch.setenv("MG_GEMM_SPLITK", "0")
-    monkeypatch.setenv("MG_GEMM_CSPLIT", "0")
-    monkeypatch.setenv("MG_GEMM_SWAP", "1")
+    mgopt.setenv("MG_GEMM_SPLITK", "0")
+    mgopt.setenv("MG_GEMM_CSPLIT", "0")
+    mgopt.setenv("MG_GEMM_SWAP", "1")
     A, B = _quantise(M, N, sum(split), split, seed=7 * M + N)
     args = (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
     rows = None if M * N <= 1 << 20 else np.unique(np.concatenate([[0, M - 1], np.random.default_rng(0).integers(0, M, 30)]))
@@ -510,7 +473,7 @@ def test_decode_form(M, N, split, monkeypatch):
     _check(A, B, M, N, split, rows=rows, C=C)
     y1 = mg.matmul(*args)
     f1 = mg.matmul(*args, out_dtype=torch.float32)
-    monkeypatch.setenv("MG_GEMM_SWAP", "0")
+    mgopt.setenv("MG_GEMM_SWAP", "0")
     y0 = mg.matmul(*args)
     f0 = mg.matmul(*args, out_dtype=torch.float32)
     torch.cuda.synchronize()
@@ -523,7 +486,7 @@ def test_decode_form(M, N, split, monkeypatch):
                                        (64, 4096, (8960, 4928, 448)), (300, 256, (2560, 1408, 128)),
                                        (100, 768, (2560, 1408, 128)), (4096, 128, (5120, 2816, 256)),
                                        (1, 128, (1280, 704, 64)), (129, 2304, (640, 256, 128))])
-def test_cluster_split_k(M, N, split, monkeypatch):
+def test_cluster_split_k(M, N, split, mgopt):
     """Problems whose 128 x 128 tiles occupy at most a quarter of the SMs run as clusters of four
     CTAs, each over a quarter of the K stages; the accumulators are exchanged through distributed
     shared memory and added in CTA order.  Same bounds against the oracle, bf16 == RNE(fp32 result)
@@ -538,9 +501,9 @@ def test_cluster_split_k(M, N, split, monkeypatch):
     _check(A, B, M, N, split, rows=rows, C=C)
     y1 = mg.matmul(*args)
     y2 = mg.matmul(*args)
-    monkeypatch.setenv("MG_GEMM_CSPLIT", "0")
-    monkeypatch.setenv("MG_GEMM_SPLITK", "0")
-    monkeypatch.setenv("MG_GEMM_SWAP", "0")
+    mgopt.setenv("MG_GEMM_CSPLIT", "0")
+    mgopt.setenv("MG_GEMM_SPLITK", "0")
+    mgopt.setenv("MG_GEMM_SWAP", "0")
     y0 = mg.matmul(*args)
     torch.cuda.synchronize()
     assert mg.device_status() == 0
@@ -548,3 +511,113 @@ def test_cluster_split_k(M, N, split, monkeypatch):
     d = (y1.float() - y0.float()).abs()
     assert torch.all(d <= y0.float().abs() * 2.0 ** -7 + 1e-30)
     assert not torch.equal(y1, torch.zeros_like(y1))
+
+
+def _abargs(A, B):
+    return (A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+
+
+def test_multi_problem_launch_equals_separate_calls(mgopt):
+    """Independent problems (own activation, own K split) in one launch of the CTA-pair kernel give
+    the bytes of one launch each; a list the kernel does not take falls back to separate launches."""
+    import mixedgemm_b200 as mg
+    mgopt.setenv("MG_GEMM_CSPLIT", "0")
+    mgopt.setenv("MG_GEMM_SPLITK", "0")
+    shapes = [(512, 512, (1280, 640, 128)), (300, 256, (8960, 4928, 448)), (2048, 1024, (2560, 1408, 128)),
+              (129, 768, (128, 0, 0))]
+    probs = []
+    for j, (M, N, split) in enumerate(shapes):
+        A, B = _quantise(M, N, sum(split), split, seed=50 + j)
+        probs.append((A, B, None))
+    outs = mg.matmul_multi(probs)
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    for (A, B, _), y, (M, N, split) in zip(probs, outs, shapes):
+        ref = mg.matmul(*_abargs(A, B))
+        assert y.shape == (M, N)
+        assert torch.equal(y.view(torch.int16), ref.view(torch.int16))
+    _check(probs[1][0], probs[1][1], *shapes[1][:2], shapes[1][2])
+    # M <= 128 is not for the pair kernel: the list is then served by separate launches
+    A, B = _quantise(64, 256, 512, (256, 128, 128), seed=60)
+    outs = mg.matmul_multi([probs[0], (A, B, None)])
+    assert torch.equal(outs[1].view(torch.int16), mg.matmul(*_abargs(A, B)).view(torch.int16))
+
+
+def test_ready_flag_holds_a_problem_back_until_its_activation_is_there(mgopt):
+    """A problem with a ready flag is not read before the flag reaches its value: the activation is
+    filled, and the flag raised, by copy-engine copies on another stream AFTER the launch."""
+    import mixedgemm_b200 as mg
+    mg.set_wait_limit_us(2_000_000)
+    M, N, split = 512, 512, (1280, 640, 128)
+    A0, B0 = _quantise(M, N, sum(split), split, seed=70)
+    A1, B1 = _quantise(M, N, sum(split), split, seed=72)
+    want0, want1 = mg.matmul(*_abargs(A0, B0)), mg.matmul(*_abargs(A1, B1))
+    late = [torch.full_like(t, 0x5A) for t in A1]     # what the kernel must NOT multiply
+    for t in late[3:]:
+        t.fill_(127)                                   # scale bytes of 1.0, so a premature read is finite but wrong
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    one = torch.ones(1, dtype=torch.int32).pin_memory()
+    good = [t.contiguous().cpu().pin_memory() if t.is_contiguous() else None for t in A1]
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    outs = mg.matmul_multi([(A0, B0, None), (tuple(late), B1, None)], flags=[None, (flag, 1)])
+    with torch.cuda.stream(side):
+        for dst, src, host in zip(late, A1, good):
+            if host is not None:
+                dst.copy_(host, non_blocking=True)     # host -> device: a copy engine, no SM needed
+            else:
+                dst.copy_(src, non_blocking=True)
+        flag.copy_(one, non_blocking=True)
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    assert torch.equal(outs[0].view(torch.int16), want0.view(torch.int16))
+    assert torch.equal(outs[1].view(torch.int16), want1.view(torch.int16))
+
+
+def test_bounded_waits_run_out_and_the_context_survives(mgopt):
+    """Host-side fault injection: (1) the first CTA of the single-CTA kernel never loads its second
+    K stage, (2) a problem's ready flag is never raised.  With the wait limit at 1 ms the kernels
+    give up, store nothing, return normally; mg_device_status reports the code (and
+    MG_ERR_TIMEOUT), and the next call on the same context is correct."""
+    import ctypes
+    import mixedgemm_b200 as mg
+    from mixedgemm_b200 import _capi
+    lib = _capi.load()
+    M, N, split = 128, 128, (512, 256, 128)
+    A, B = _quantise(M, N, sum(split), split, seed=80)
+    mgopt.setenv("MG_GEMM_CSPLIT", "0")
+    mgopt.setenv("MG_GEMM_SPLITK", "0")
+    mgopt.setenv("MG_GEMM_2CTA", "0")
+    want = mg.matmul(*_abargs(A, B))
+    torch.cuda.synchronize()
+    mg.set_wait_limit_us(1000)
+    mgopt.setenv("MG_FAULT_SKIP_LOAD", "2")
+    out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    mg.matmul(*_abargs(A, B), out=out)
+    torch.cuda.synchronize()
+    v = ctypes.c_int(0)
+    st = lib.mg_device_status(ctypes.byref(v), None)
+    assert st == 7 and b"bounded wait" in lib.mg_strerror(st)
+    assert v.value & (2 | 8), v.value                   # the MMA warp's or the epilogue's wait ran out
+    assert torch.all(out == 7.0)                        # nothing was stored
+    mgopt.setenv("MG_FAULT_SKIP_LOAD", "0")
+    assert lib.mg_device_status(ctypes.byref(v), None) == 0 and v.value == 0   # the word was cleared
+    again = mg.matmul(*_abargs(A, B))
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    assert torch.equal(again.view(torch.int16), want.view(torch.int16))
+    # (2) a flag that nothing raises
+    M2, N2, split2 = 256, 256, (256, 128, 128)
+    A2, B2 = _quantise(M2, N2, sum(split2), split2, seed=81)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out2 = torch.full((M2, N2), 7.0, dtype=torch.bfloat16, device="cuda")
+    mg.matmul_multi([(A2, B2, out2)], flags=[(flag, 1)])
+    torch.cuda.synchronize()
+    assert mg.device_status() & 1024
+    assert torch.all(out2 == 7.0)
+    mg.set_wait_limit_us(0)
+    flag.fill_(1)
+    mg.matmul_multi([(A2, B2, out2)], flags=[(flag, 1)])
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    assert torch.equal(out2.view(torch.int16), mg.matmul(*_abargs(A2, B2)).view(torch.int16))
