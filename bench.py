@@ -2,22 +2,23 @@
 """Benchmark of the hot path: activation reorder-and-quantise + mixed MXFP4/6/8 GEMM.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                  [--workload NAME] [--exchange replicated|bcast|allgather] [--no-graph]
-  python bench.py --kernel gemm|reorder --shape M,N,K     one kernel, one shape (what profiles/ is made with)
+                  [--workload NAME] [--exchange push|allgather|bcast|replicated] [--no-graph] [--no-fuse]
+  python bench.py --kernel gemm|reorder --shape M,N,K     one kernel, one shape
   python bench.py --sweep decode|square|all               the other benchmark configurations, a line per shape
 
 One "step" is one pass over a projection set of a Llama-shaped layer stack: every distinct
 activation is reorder-quantised once and multiplied with each weight that consumes it
-(q/k/v share one activation, gate/up another).  Weights are quantised once, outside the
-timed region, as in deployment.
+(q/k/v share one activation, gate/up another); all products of the step go out as one GEMM
+launch.  Weights are quantised once, outside the timed region, as in deployment.
 
-  N = 1 (default)   workload llama3-8b-m2048   (BASELINE configs[1])
-  N > 1             workload llama3-70b-m4096  (BASELINE configs[3]): weights sharded along N
-                    over the ranks.  --exchange replicated (default: the fastest measured): every
-                    rank quantises the activations itself; bcast: rank 0 quantises and broadcasts
-                    them with NCCL; allgather: every rank quantises M/P rows and NCCL all-gathers
-                    complete the buffers; rows: not N-sharding at all - the ranks split the M tokens
-                    and every rank holds all weights (no exchange, the quantiser is sharded too)
+  N = 1 (default)   workload llama3-8b-m2048 (M = 2048 tokens on the Llama-3-8B projections)
+  N > 1             workload llama3-70b-m4096: weights sharded along N over the ranks.  --exchange
+                    push (default): every rank quantises M / P rows and pushes them into every
+                    peer's buffer with copy-engine copies over NVLink while the GEMM, already
+                    launched, waits row shard by row shard for the flags that follow the data;
+                    allgather: the same rows, completed by NCCL all-gathers before the GEMM;
+                    bcast: rank 0 quantises, NCCL broadcast; replicated: every rank quantises
+                    everything, nothing is exchanged
 
 Prints ONE JSON line (rank 0).  `value` is the whole-job GEMM throughput with inputs resident
 in HBM; `e2e` is the same metric with the activations starting in pinned host memory and the
@@ -50,7 +51,7 @@ WORKLOADS = {
         (8192, [("o", 8192)]),
         (8192, [("gate", 28672), ("up", 28672)]),
         (28672, [("down", 8192)])]),
-    # BASELINE configs[0]: the CPU-runnable single layer
+    # the CPU-runnable single layer
     "single-layer-m16": dict(M=16, dist="normal", outlier=20.0, wstd=0.02, groups=[(4096, [("proj", 4096)])]),
 }
 
@@ -136,6 +137,7 @@ def cpu_arm(wl_name, rows, steps, warmup):
     import numpy as np
     from oracle import mx_oracle as orc
     wl = WORKLOADS[wl_name]
+    rows = min(rows, wl["M"])
     cores = len(os.sched_getaffinity(0))
     torch.set_num_threads(cores)
     g = torch.Generator().manual_seed(0)
@@ -191,26 +193,23 @@ def cpu_arm(wl_name, rows, steps, warmup):
 # ----------------------------------------------------------------------------- GPU arm
 class Job:
     """Device-resident state of one rank: activations, reorder indices, quantised weight shards,
-    output buffers."""
+    output buffers, and - on several GPUs - the exchange that brings every rank the whole
+    quantised activation."""
 
-    def __init__(self, wl_name, rank, world, device, exchange):
+    def __init__(self, wl_name, rank, world, device, exchange, fused=True):
         import mixedgemm_b200 as mg
         self.mg = mg
         wl = WORKLOADS[wl_name]
-        M = wl["M"]
-        self.rank, self.world, self.exchange = rank, world, exchange
-        # "rows": the ranks split the tokens instead of the weights (every rank holds all weights)
-        self.by_rows = world > 1 and exchange == "rows"
-        assert not self.by_rows or M % (128 * world) == 0
-        self.M_total = M
-        self.M = Ml = M // world if self.by_rows else M
+        self.M = M = wl["M"]
+        self.rank, self.world, self.device = rank, world, device
+        self.exchange = exchange if world > 1 else "none"
+        self.fused = fused
+        self.sharded_q = self.exchange in ("push", "allgather")  # every rank quantises M / P rows
         g = torch.Generator(device=device).manual_seed(1234)  # same activations on every rank
         self.groups = []
         self.flops_local = 0
         self.flops_total = 0
-        self.reorder_bytes = 0
         self.gemm_shapes = []
-        self.n_kernels = 0
         for gi, (K, layers) in enumerate(wl["groups"]):
             KN, KS, KO = split_k(K)
             X = torch.randn(M, K, generator=g, device=device)
@@ -225,70 +224,119 @@ class Job:
             Xb = X.to(torch.bfloat16)
             del X
             idx = torch.sort(Xb.float().abs().amax(0), stable=True).indices.to(torch.int16)
-            if self.by_rows:
-                from mixedgemm_b200 import dist as mgd
-                m0, _ = mgd.shard_range(M, world, rank)
-                Xb = Xb[m0:m0 + Ml].contiguous()
-            A = mg.alloc_quantized_x(Ml, KN, KS, KO, device, one_buffer=world > 1)
+            if self.sharded_q:
+                mp = M // world
+                Xb = Xb[rank * mp:(rank + 1) * mp].contiguous()  # this rank's rows are all it ever reads
             Ls = []
             for li, (name, N) in enumerate(layers):
                 assert N % (128 * world) == 0, "every shard must be a multiple of 128 columns"
-                Nl = N if self.by_rows else N // world
+                Nl = N // world
                 gw = torch.Generator(device=device).manual_seed(977 * gi + 31 * li + 7)
                 W = (torch.randn(N, K, generator=gw, device=device) * wl["wstd"]).to(torch.bfloat16)
-                Wl = W if self.by_rows else W[rank * Nl:(rank + 1) * Nl].contiguous()
+                Wl = W[rank * Nl:(rank + 1) * Nl].contiguous()
                 del W
-                B = mg.reorder_quantize_w(Wl, idx, KN, KS, KO, Ml, Nl)
+                B = mg.reorder_quantize_w(Wl, idx, KN, KS, KO, M, Nl)
                 del Wl
-                Y = torch.empty((Ml, Nl), dtype=torch.bfloat16, device=device)
+                Y = torch.empty((M, Nl), dtype=torch.bfloat16, device=device)
                 Ls.append((name, Nl, B, Y))
-                self.flops_local += 2 * Ml * Nl * K
+                self.flops_local += 2 * M * Nl * K
                 self.flops_total += 2 * M * N * K
-                self.gemm_shapes.append((Ml, Nl, K))
-            grouped = Ml > 128 and len(layers) <= 4 and all(Nl % 256 == 0 for (_, Nl, _, _) in Ls)
-            self.n_kernels += 1 + (1 if grouped else len(layers))  # the quantiser + one or several GEMM launches
-            self.reorder_bytes += reorder_bytes(Ml, K)
-            self.groups.append(dict(K=K, split=(KN, KS, KO), X=Xb, idx=idx, A=A, layers=Ls))
+                self.gemm_shapes.append((M, Nl, K))
+            self.groups.append(dict(K=K, split=(KN, KS, KO), X=Xb, idx=idx, layers=Ls))
+        # the fused launch and the exchange take the activations with the most work first
+        self.order = sorted(range(len(self.groups)), key=lambda i: -sum(2 * M * Nl * self.groups[i]["K"]
+                                                                         for (_, Nl, _, _) in self.groups[i]["layers"]))
+        self.nsets = 1
+        self.ex = self.comm = None
+        if self.exchange == "push":
+            from mixedgemm_b200 import dist as mgd
+            # two buffer sets used in turn: a rank may push the next step while a peer still multiplies this one
+            self.nsets = 2
+            self.ex = mgd.PushExchange([(M, gr["split"]) for gr in self.groups], world, rank, device, n_sets=2)
+            for gi, gr in enumerate(self.groups):
+                gr["A"] = [self.ex.buffers(s, gi) for s in range(2)]
+        else:
+            if self.exchange in ("bcast", "allgather"):
+                from mixedgemm_b200 import dist as mgd
+                self.comm = mgd.Communicator(world, rank)
+            for gr in self.groups:
+                gr["A"] = [mg.alloc_quantized_x(M, *gr["split"], device)]
+        nq = len(self.groups)
+        can_fuse = M > 128 and all(Nl % 256 == 0 for gr in self.groups for (_, Nl, _, _) in gr["layers"]) and \
+            sum(len(gr["layers"]) for gr in self.groups) <= 8
+        self.fused = self.fused and can_fuse
+        grouped = [M > 128 and len(gr["layers"]) <= 8 and all(Nl % 256 == 0 for (_, Nl, _, _) in gr["layers"])
+                   for gr in self.groups]
+        # kernels of this library per step: the quantisers + the GEMM launches (+ the epoch bump)
+        self.n_kernels = nq + (1 if self.fused else sum(1 if g_ else len(gr["layers"]) for g_, gr in zip(grouped, self.groups)))
+        self.n_kernels += 1 if self.ex is not None else 0
+        self.reorder_bytes = sum(reorder_bytes(gr["X"].size(0), gr["K"]) for gr in self.groups)
         torch.cuda.synchronize()
 
-    def quantize(self, gr):
+    # -- pieces of a step
+    def quantize(self, gi, s=0):
+        """This rank's part of the quantisation of activation gi into buffer set s."""
+        gr = self.groups[gi]
         KN, KS, KO = gr["split"]
-        self.mg.reorder_quantize_x(gr["X"], gr["idx"], KN, KS, KO, self.M, 0, out=gr["A"])
-
-    def exchange_a(self, gr):
-        from mixedgemm_b200 import dist as mgd
-        mgd.broadcast_activations(gr["A"], src=0)
-
-    def gemms(self, gr):
-        # weights that consume the same activation go out as one grouped launch where the kernel takes them
-        self.mg.matmul_group(gr["A"], [B for (_, _, B, _) in gr["layers"]], outs=[Y for (_, _, _, Y) in gr["layers"]])
-
-    def quantize_and_exchange(self, gr):
-        """bcast: rank 0 quantises, one NCCL broadcast; allgather: every rank quantises M/P rows in
-        place, NCCL all-gathers complete the buffers; replicated: every rank quantises everything."""
-        if self.world == 1 or self.exchange in ("replicated", "rows"):
-            self.quantize(gr)
-        elif self.exchange == "allgather":
+        A = gr["A"][s]
+        if self.sharded_q:
             from mixedgemm_b200 import dist as mgd
-            KN, KS, KO = gr["split"]
-            mp = self.M // self.world
-            sh = mgd.activation_shard(gr["A"], self.M, gr["split"], self.world, self.rank)
-            self.mg.reorder_quantize_x(gr["X"][self.rank * mp:(self.rank + 1) * mp], gr["idx"], KN, KS, KO, mp, 0, out=sh)
-            mgd.all_gather_activations(gr["A"], self.M, gr["split"], self.world, self.rank)
+            out = self.ex.shard(s, gi) if self.ex is not None else mgd.activation_shard(A, self.M, gr["split"], self.world, self.rank)
+            self.mg.reorder_quantize_x(gr["X"], gr["idx"], KN, KS, KO, gr["X"].size(0), 0, out=out)
+        elif self.exchange == "bcast" and self.rank != 0:
+            pass
         else:
-            if self.rank == 0:
-                self.quantize(gr)
-            self.exchange_a(gr)
+            self.mg.reorder_quantize_x(gr["X"], gr["idx"], KN, KS, KO, self.M, 0, out=A)
 
-    def step(self):
-        for gr in self.groups:
-            self.quantize_and_exchange(gr)
-            self.gemms(gr)
+    def exchange_a(self, gi, s=0):
+        gr = self.groups[gi]
+        if self.exchange == "push":
+            self.ex.push(s, gi)
+        elif self.exchange == "bcast":
+            self.comm.broadcast_activations(gr["A"][s], src=0)
+        elif self.exchange == "allgather":
+            self.comm.all_gather_activations(gr["A"][s], self.M, gr["split"])
+
+    def gemm_group(self, gi, s=0):
+        gr = self.groups[gi]
+        self.mg.matmul_group(gr["A"][s], [B for (_, _, B, _) in gr["layers"]], outs=[Y for (_, _, _, Y) in gr["layers"]])
+
+    def gemm_fused(self, s=0):
+        probs, flags = [], []
+        for gi in self.order:
+            gr = self.groups[gi]
+            for (_, _, B, Y) in gr["layers"]:
+                probs.append((gr["A"][s], B, Y))
+                flags.append(self.ex.ready(s, gi) if self.ex is not None else None)
+        self.mg.matmul_multi(probs, flags=flags if self.ex is not None else None)
+
+    def step(self, s=0):
+        """One pass: quantise (this rank's part of) every activation, exchange, multiply."""
+        if self.ex is not None:
+            self.ex.begin_step()
+        if self.fused:
+            for gi in self.order:
+                self.quantize(gi, s)
+                self.exchange_a(gi, s)
+            self.gemm_fused(s)
+        else:
+            for gi in range(len(self.groups)):
+                self.quantize(gi, s)
+                self.exchange_a(gi, s)
+                self.gemm_group(gi, s)
+        if self.ex is not None:
+            self.ex.join()
+
+    def close(self):
+        if self.ex is not None:
+            self.ex.close()
+        if self.comm is not None:
+            self.comm.close()
 
 
 def timed(fn, steps, sync, finish=None):
-    """ms per step by CUDA events on the current stream; `finish` (optional) makes that stream wait
-    for work the step put on other streams before the closing event is recorded."""
+    """ms per call of fn by CUDA events on the current stream; `finish` (optional) makes that stream
+    wait for work the calls put on other streams before the closing event is recorded."""
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync()
     e0.record()
@@ -298,46 +346,14 @@ def timed(fn, steps, sync, finish=None):
         finish()
     e1.record()
     sync()
-    return e0.elapsed_time(e1) / steps  # ms per step
+    return e0.elapsed_time(e1) / steps
 
 
-def single_kernel(a):
-    """One kernel, one shape, rotating operand sets larger than L2: the command the ncu summaries
-    under profiles/ are made with."""
-    import mixedgemm_b200 as mg
-    M, N, K = [int(v) for v in a.shape.split(",")]
-    KN, KS, KO = split_k(K)
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
-    g = torch.Generator(device=dev).manual_seed(5)
-    pk = peaks()
-    X = torch.randn(M, K, generator=g, device=dev)
-    X[:, torch.randperm(K, generator=g, device=dev)[:K // 32]] *= 20
-    X = X.to(torch.bfloat16)
-    idx = torch.sort(X.float().abs().amax(0), stable=True).indices.to(torch.int16)
-    L2 = 130 << 20
-    if a.kernel == "reorder":
-        per = reorder_bytes(M, K)
-        nb = a.buffers or max(2, L2 // (M * K * 2) + 1)
-        Xs = [X.clone() for _ in range(nb)]
-        outs = [mg.alloc_quantized_x(M, KN, KS, KO, dev) for _ in range(nb)]
-        fns = [lambda i=i: mg.reorder_quantize_x(Xs[i], idx, KN, KS, KO, M, 0, out=outs[i]) for i in range(nb)]
-        work, unit, peak, bound = per / 1e9, "GB/s", pk["hbm"], "hbm"
-    else:
-        W = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
-        wbytes = N * K // 2 + N * K // 32
-        nb = a.buffers or max(2, L2 // wbytes + 1)
-        A = mg.reorder_quantize_x(X, idx, KN, KS, KO, M, N)
-        Bs = [mg.reorder_quantize_w(W, idx, KN, KS, KO, M, N) for _ in range(nb)]
-        Ys = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _ in range(nb)]
-        fns = [lambda i=i: mg.matmul(A[0], Bs[i][0], A[1], Bs[i][1], A[2], Bs[i][2], A[3], Bs[i][3], A[4], Bs[i][4],
-                                     A[5], Bs[i][5], out=Ys[i]) for i in range(nb)]
-        work, unit, bound = 2.0 * M * N * K / 1e12, "TFLOP/s", "tensor"
-        peak = blended_peak(pk["bf16"], K)
-        if M <= 128:  # decode shapes are bound by reading the weights once
-            work = (wbytes + M * (KN // 2 + KS // 4 * 3 + KO + K // 32) + 2 * M * N) / 1e9
-            unit, bound, peak = "GB/s", "hbm", pk["hbm"]
-    for i in range(max(a.warmup, 1)):
+def graph_time(fns, launches, warmup=3):
+    """us per launch of fns[i % len(fns)] replayed as one CUDA graph of `launches` launches
+    (rotating operand sets larger than L2 is the caller's business)."""
+    nb = len(fns)
+    for i in range(max(warmup, 1)):
         fns[i % nb]()
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
@@ -346,7 +362,7 @@ def single_kernel(a):
         fns[0]()
         torch.cuda.synchronize()
         with torch.cuda.graph(graph, stream=st):
-            for i in range(a.steps):
+            for i in range(launches):
                 fns[i % nb]()
         graph.replay()
         torch.cuda.synchronize()
@@ -355,12 +371,57 @@ def single_kernel(a):
         graph.replay()
         e1.record()
         torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / a.steps
+    return e0.elapsed_time(e1) * 1e3 / launches
+
+
+def kernel_case(kernel, M, N, K, launches, buffers=0, warmup=3):
+    """One kernel, one shape, rotating operand sets larger than L2 -> dict with us per launch and
+    the roofline figures (what `--kernel` prints and what the `extra` entries of the default line hold)."""
+    import mixedgemm_b200 as mg
+    KN, KS, KO = split_k(K)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(5)
+    pk = peaks()
+    X = torch.randn(M, K, generator=g, device=dev)
+    X[:, torch.randperm(K, generator=g, device=dev)[:K // 32]] *= 20
+    X = X.to(torch.bfloat16)
+    idx = torch.sort(X.float().abs().amax(0), stable=True).indices.to(torch.int16)
+    L2 = 130 << 20
+    if kernel == "reorder":
+        per = reorder_bytes(M, K)
+        nb = buffers or max(2, min(64, L2 // (M * K * 2) + 1))
+        Xs = [X.clone() for _ in range(nb)]
+        outs = [mg.alloc_quantized_x(M, KN, KS, KO, dev) for _ in range(nb)]
+        fns = [lambda i=i: mg.reorder_quantize_x(Xs[i], idx, KN, KS, KO, M, 0, out=outs[i]) for i in range(nb)]
+        work, unit, peak, bound = per / 1e9, "GB/s", pk["hbm"], "hbm"
+    else:
+        W = (torch.randn(N, K, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        wbytes = N * K // 2 + N * K // 32
+        nb = buffers or max(2, min(64, L2 // wbytes + 1))
+        A = mg.reorder_quantize_x(X, idx, KN, KS, KO, M, N)
+        Bs = [mg.reorder_quantize_w(W, idx, KN, KS, KO, M, N) for _ in range(nb)]
+        del W
+        Ys = [torch.empty((M, N), dtype=torch.bfloat16, device=dev) for _ in range(nb)]
+        fns = [lambda i=i: mg.matmul(A[0], Bs[i][0], A[1], Bs[i][1], A[2], Bs[i][2], A[3], Bs[i][3], A[4], Bs[i][4],
+                                     A[5], Bs[i][5], out=Ys[i]) for i in range(nb)]
+        work, unit, bound = 2.0 * M * N * K / 1e12, "TFLOP/s", "tensor"
+        peak = blended_peak(pk["bf16"], K)
+        if M <= 128:  # decode shapes are bound by reading the weights once
+            work = (wbytes + M * (KN // 2 + KS // 4 * 3 + KO + K // 32) + 2 * M * N) / 1e9
+            unit, bound, peak = "GB/s", "hbm", pk["hbm"]
+    us = graph_time(fns, launches, warmup)
     assert mg.device_status() == 0
-    print(json.dumps({"kernel": a.kernel, "M": M, "N": N, "K": K, "launches": a.steps, "operand_sets": nb,
-                      "us_per_launch": us, "achieved": work / (us * 1e-6), "unit": unit, "bound": bound,
-                      "peak": peak, "frac": work / (us * 1e-6) / peak,
-                      "peak_note": "%s burst figures (kernel timed alone)" % pk["source"]}))
+    return {"kernel": kernel, "M": M, "N": N, "K": K, "launches": launches, "operand_sets": nb,
+            "us_per_launch": us, "achieved": work / (us * 1e-6), "unit": unit, "bound": bound,
+            "peak": peak, "frac": work / (us * 1e-6) / peak,
+            "peak_note": "%s burst figures (kernel timed alone)" % pk["source"]}
+
+
+def single_kernel(a):
+    """`--kernel`: one kernel, one shape; prints a short JSON line."""
+    M, N, K = [int(v) for v in a.shape.split(",")]
+    torch.cuda.set_device(0)
+    print(json.dumps(kernel_case(a.kernel, M, N, K, a.steps, a.buffers, a.warmup)))
 
 
 def main():
@@ -370,8 +431,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=list(WORKLOADS))
-    ap.add_argument("--exchange", default="replicated", choices=["bcast", "replicated", "allgather", "rows"])
+    ap.add_argument("--exchange", default="push", choices=["push", "allgather", "bcast", "replicated"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-fuse", action="store_true", help="one GEMM launch per activation instead of one over all layers")
+    ap.add_argument("--no-extra", action="store_true", help="skip the `extra` kernels of the default line")
     ap.add_argument("--cpu-rows", type=int, default=128)
     ap.add_argument("--kernel", default=None, choices=["gemm", "reorder"],
                     help="run only this kernel on --shape (for profiling); prints a short JSON line")
@@ -441,22 +504,30 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    job = Job(wl_name, rank, world, device, a.exchange)
+    job = Job(wl_name, rank, world, device, a.exchange, fused=not a.no_fuse)
     pk = peaks()
+    nsets = job.nsets
 
-    # ---- whole-step timing, inputs resident in HBM
+    # ---- whole-step timing, inputs resident in HBM.  One "run" is `nsets` steps (the overlapped
+    # exchange alternates between two buffer sets, so its replay unit is two steps).
+    def run_eager():
+        for s_ in range(nsets):
+            job.step(s_)
+
     use_graph = not a.no_graph
     stream = torch.cuda.Stream()
+    runs = (a.steps + nsets - 1) // nsets
+    steps = runs * nsets
     with torch.cuda.stream(stream):
-        for _ in range(a.warmup):
-            job.step()
+        for _ in range((a.warmup + nsets - 1) // nsets):
+            run_eager()
         torch.cuda.synchronize()
-        run = job.step
+        run = run_eager
         if use_graph:
             try:
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=stream):
-                    job.step()
+                    run_eager()
                 graph.replay()
                 torch.cuda.synchronize()
                 run = graph.replay
@@ -471,23 +542,23 @@ def main():
             sampler.start()
             time.sleep(0.25)
         t0 = time.time()
-        ms = timed(run, a.steps, sync)
+        ms = timed(run, runs, sync) / nsets
         t1 = time.time()
         # nvidia-smi samples every 100 ms: when the K timed steps are shorter than that, the clocks are
         # read over an identical window of back-to-back steps that follows them immediately
         clock_window = "the timed steps"
-        # every rank must run the same number of steps (they contain collectives): decide on rank 0's clock
+        # every rank must run the same number of steps (they may contain collectives): decide on rank 0's clock
         plan = torch.tensor([t1 - t0, ms], device=device, dtype=torch.float64)
         if world > 1:
             import torch.distributed as dist
             dist.broadcast(plan, src=0)
         span, ms_ref = plan.tolist()
         if span < 0.6:
-            n_extra = int(0.6 / max(ms_ref / 1e3, 1e-6)) + 1
+            n_extra = int(0.6 / max(ms_ref * nsets / 1e3, 1e-6)) + 1
             t0 = time.time()
             timed(run, n_extra, sync)
             t1 = time.time()
-            clock_window = "%d further identical steps right after the timed ones" % n_extra
+            clock_window = "%d further identical steps right after the timed ones" % (n_extra * nsets)
         clocks = sampler.stop(t0, t1) if rank == 0 else None
         if clocks is not None:
             clocks["window"] = clock_window
@@ -495,25 +566,33 @@ def main():
         # ---- per-kernel durations: an instrumented pass of whole steps in launch order, so every kernel
         # sees the cache state it has inside a step.  A spin kernel keeps the GPU busy while the CPU
         # enqueues, so the event pairs bracket pure GPU execution rather than Python launch overhead.
+        # The GEMMs are timed both ways: one launch per activation (so that every layer group has its
+        # own figure) and the single launch over all layers that the step uses.
         ev = lambda: torch.cuda.Event(enable_timing=True)
-        q_ms, g_ms, q_each, g_each = 0.0, 0.0, [], []
+        q_ms, g_ms, q_each, g_each, fused_ms = 0.0, 0.0, [], [], None
         if world == 1:
             reps = max(3, min(a.steps, 10))
             marks = []
             torch.cuda.synchronize()
             torch.cuda._sleep(int(1.0e7) * reps)
             for _ in range(reps):
-                for gi, gr in enumerate(job.groups):
+                for gi in range(len(job.groups)):
                     e0, e1 = ev(), ev()
                     e0.record()
-                    job.quantize(gr)
+                    job.quantize(gi)
                     e1.record()
                     marks.append((("q", gi), e0, e1))
                     e0, e1 = ev(), ev()
                     e0.record()
-                    job.gemms(gr)
+                    job.gemm_group(gi)
                     e1.record()
                     marks.append((("g", gi), e0, e1))
+                if job.fused:
+                    e0, e1 = ev(), ev()
+                    e0.record()
+                    job.gemm_fused()
+                    e1.record()
+                    marks.append((("f", 0), e0, e1))
             torch.cuda.synchronize()
             acc = {}
             for key, e0, e1 in marks:
@@ -525,16 +604,19 @@ def main():
                 Nsum = sum(Nl for (_, Nl, _, _) in gr["layers"])
                 g_each.append((names, job.M, Nsum, gr["K"], acc[("g", gi)]))
                 g_ms += acc[("g", gi)]
+            fused_ms = acc.get(("f", 0))
 
-        # ---- end to end: activations from pinned host memory, results back to pinned host memory
+        # ---- end to end: activations from pinned host memory, results back to pinned host memory.
+        # Every rank uploads the rows it quantises (all of them on one GPU; M / P with a sharded
+        # quantiser) and downloads its output shards.
         hX = [gr["X"].cpu().pin_memory() for gr in job.groups]
         hY = [[torch.empty(Y.shape, dtype=Y.dtype).pin_memory() for (_, _, _, Y) in gr["layers"]] for gr in job.groups]
         h2d = sum(t.numel() * 2 for t in hX)
         d2h = sum(t.numel() * 2 for ys in hY for t in ys)
 
         # Three streams, as a caller with host buffers would run it: uploads, compute and downloads
-        # overlap (PCIe is full duplex), ordered per buffer by events.  Every step uploads all its
-        # activations and downloads all its outputs; the closing event waits for the last download.
+        # overlap (PCIe is full duplex), ordered by events.  Every step uploads all its activations
+        # and downloads all its outputs; the closing event waits for the last download.
         main_s = torch.cuda.current_stream()
         in_s, out_s = torch.cuda.Stream(), torch.cuda.Stream()
         ng = len(job.groups)
@@ -545,22 +627,43 @@ def main():
         for g in range(ng):
             ev_xfree[g].record(main_s)
             ev_yfree[g].record(main_s)
+        e2e_count = [0]
+        # On one GPU the GEMMs go out per activation here, so that a group's outputs travel to the
+        # host while the next group multiplies (the link, not the GPU, bounds this leg); with the
+        # overlapped exchange the single launch stays, because it is what waits for the flags.
+        e2e_fused = job.fused and job.ex is not None
 
         def e2e_step():
-            for g, (gr, hx, hys) in enumerate(zip(job.groups, hX, hY)):
+            s_ = e2e_count[0] % nsets
+            e2e_count[0] += 1
+            order = job.order if e2e_fused else list(range(ng))
+            for g in order:
                 in_s.wait_event(ev_xfree[g])
                 with torch.cuda.stream(in_s):
-                    gr["X"].copy_(hx, non_blocking=True)
+                    job.groups[g]["X"].copy_(hX[g], non_blocking=True)
                     ev_in[g].record(in_s)
+            if job.ex is not None:
+                job.ex.begin_step()
+            for g in order:
                 main_s.wait_event(ev_in[g])
-                job.quantize_and_exchange(gr)
+                job.quantize(g, s_)
                 ev_xfree[g].record(main_s)
-                main_s.wait_event(ev_yfree[g])
-                job.gemms(gr)
-                ev_done[g].record(main_s)
+                job.exchange_a(g, s_)
+                if not e2e_fused:
+                    main_s.wait_event(ev_yfree[g])
+                    job.gemm_group(g, s_)
+                    ev_done[g].record(main_s)
+            if e2e_fused:
+                for g in order:
+                    main_s.wait_event(ev_yfree[g])
+                job.gemm_fused(s_)
+                job.ex.join()
+                for g in order:
+                    ev_done[g].record(main_s)
+            for g in order:
                 out_s.wait_event(ev_done[g])
                 with torch.cuda.stream(out_s):
-                    for (_, _, _, Y), hy in zip(gr["layers"], hys):
+                    for (_, _, _, Y), hy in zip(job.groups[g]["layers"], hY[g]):
                         hy.copy_(Y, non_blocking=True)
                     ev_yfree[g].record(out_s)
 
@@ -568,9 +671,9 @@ def main():
             main_s.wait_stream(in_s)
             main_s.wait_stream(out_s)
 
-        for _ in range(2):
+        for _ in range(2 * nsets):
             e2e_step()
-        e2e_ms = timed(e2e_step, max(3, min(a.steps, 10)), sync, finish=e2e_finish)
+        e2e_ms = timed(e2e_step, max(4, min(a.steps, 10)) // nsets * nsets, sync, finish=e2e_finish)
 
     # max over ranks
     solo = None
@@ -583,7 +686,7 @@ def main():
         # not have to be taken against the (smaller) default workload of `--gpus 1`: rank 0 alone,
         # all weights, same graph-replay timing, while the other ranks wait.
         if rank == 0:
-            job1 = Job(wl_name, 0, 1, device, "replicated")
+            job1 = Job(wl_name, 0, 1, device, "none", fused=not a.no_fuse)
             with torch.cuda.stream(stream):
                 for _ in range(a.warmup):
                     job1.step()
@@ -603,63 +706,95 @@ def main():
     if rank != 0:
         if world > 1:
             import torch.distributed as dist
+            dist.barrier()
+            job.close()
             dist.destroy_process_group()
         return
 
     value = job.flops_total / (ms * 1e-3) / 1e12
     out = {
-        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": a.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
         "vs_baseline": None, "dtype": "mxfp4/mxfp6/mxfp8 x mxfp4, f32 accumulate, bf16 out", "data": "synthetic",
-        "config": {"workload": wl_name, "M": job.M_total,
-                   "layers": [[gr["K"], [[n, N if job.by_rows else N * world] for (n, N, _, _) in gr["layers"]]]
-                              for gr in job.groups],
-                   "k_split": "62.5% fp4 / 34.375% fp6 / 3.125% fp8", "parallelism": ("m-shard x%d" if job.by_rows else "n-shard x%d") % world,
-                   "exchange": a.exchange if world > 1 else "none", "cuda_graph": use_graph,
+        "config": {"workload": wl_name, "M": job.M,
+                   "layers": [[gr["K"], [[n, N * world] for (n, N, _, _) in gr["layers"]]] for gr in job.groups],
+                   "k_split": "62.5% fp4 / 34.375% fp6 / 3.125% fp8", "parallelism": "n-shard x%d" % world,
+                   "exchange": job.exchange, "cuda_graph": use_graph,
+                   "gemm_launch": "one launch over all layers" if job.fused else "one launch per activation",
                    "l2": "inputs larger than L2: one step touches ~%d MB of weights, activations and outputs" % (
                        (sum(t.numel() * t.element_size() for gr in job.groups for (_, _, B, Y) in gr["layers"]
                             for t in list(B) + [Y]) + h2d) >> 20)},
         "clocks": clocks,
-        "gpu_launches": job.n_kernels * a.steps,
+        "gpu_launches": job.n_kernels * steps,
         "e2e": {"value": job.flops_total / (e2e_ms * 1e-3) / 1e12, "unit": unit, "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world},
     }
     if solo is not None:
         out["same_workload_1gpu"] = solo
     if world == 1:
-        Kdom = max(job.groups, key=lambda gr: gr["K"])["K"]
         gemm_flops = job.flops_local
-        peak_t = blended_peak(pk["bf16_sustained"], 4096)  # same split for every K
-        achieved_t, unit_t, bound_t, kern_t = gemm_flops / (g_ms * 1e-3) / 1e12, "TFLOP/s", "tensor", "mixed_gemm_pair_kernel"
+        peak_s = blended_peak(pk["bf16_sustained"], 4096)  # same split for every K
+        peak_b = blended_peak(pk["bf16"], 4096)
+        g_best = fused_ms if (fused_ms is not None and job.fused) else g_ms
+        achieved_t, unit_t, bound_t, kern_t = gemm_flops / (g_best * 1e-3) / 1e12, "TFLOP/s", "tensor", "mixed_gemm_pair_kernel"
         if job.M <= 128:  # decode shapes are bound by reading the weights once
             gbytes = sum(N * K // 2 + N * K // 32 + reorder_bytes(M, K) - 2 * M * K + 2 * M * N for (M, N, K) in job.gemm_shapes)
-            achieved_t, unit_t, bound_t, kern_t, peak_t = gbytes / (g_ms * 1e-3) / 1e9, "GB/s", "hbm", "mixed_gemm_kernel", pk["hbm"]
+            achieved_t, unit_t, bound_t, kern_t = gbytes / (g_best * 1e-3) / 1e9, "GB/s", "hbm", "mixed_gemm_kernel"
+            peak_s = peak_b = pk["hbm"]
         out["roofline"] = {
             "kernel": kern_t, "bound": bound_t, "achieved": achieved_t,
-            "peak": peak_t, "unit": unit_t, "frac": achieved_t / peak_t,
-            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the largest GEMM of the step
-            # (gate/up, 2048 x 14336 x 4096), from the ncu capture summarised under profiles/
+            "peak": peak_s, "unit": unit_t, "frac": achieved_t / peak_s,
+            "frac_sustained": achieved_t / peak_s, "peak_burst": peak_b, "frac_burst": achieved_t / peak_b,
+            "what": ("the step's single GEMM launch over all layers, %.1f us" % (g_best * 1e3)) if job.fused and fused_ms
+            else "the step's GEMM launches, %.1f us together" % (g_best * 1e3),
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the largest GEMM of the set
+            # (gate/up, 2048 x 14336 x 4096) under ncu
             "traffic": 50.6e6 if wl_name == "llama3-8b-m2048" else None,
+            "traffic_source": "ncu capture of the 2048 x 14336 x 4096 launch, summarised in profiles/mixed_gemm_pair_kernel_2048x14336x4096.md",
             "peak_note": ("%s copy bandwidth" % pk["source"]) if job.M <= 128 else
-            "K-blended tensor peak: fp4 segment at 4x and fp6/fp8 at 2x the %s sustained bf16 rate (%.1f TF/s)" % (
-                pk["source"], pk["bf16_sustained"]),
-            "launches": [{"layer": n, "M": M, "N": N, "K": K, "us": t * 1e3, "tflops": 2 * M * N * K / (t * 1e-3) / 1e12}
-                         for (n, M, N, K, t) in g_each]}
+            "K-blended tensor peak: fp4 segment at 4x and fp6/fp8 at 2x the %s bf16 rate (sustained %.1f, burst %.1f TF/s)" % (
+                pk["source"], pk["bf16_sustained"], pk["bf16"]),
+            "launches_per_activation": [{"layer": n, "M": M, "N": N, "K": K, "us": t * 1e3,
+                                         "tflops": 2 * M * N * K / (t * 1e-3) / 1e12} for (n, M, N, K, t) in g_each],
+            "launches_per_activation_us": g_ms * 1e3,
+            "launch_all_layers_us": fused_ms * 1e3 if fused_ms is not None else None}
+        rbytes = sum(reorder_bytes(job.M, K) for (K, _) in q_each)
         out["roofline_reorder"] = {
-            "kernel": "reorder_quantize_kernel", "bound": "hbm", "achieved": job.reorder_bytes / (q_ms * 1e-3) / 1e9,
-            "peak": pk["hbm"], "unit": "GB/s", "frac": job.reorder_bytes / (q_ms * 1e-3) / 1e9 / pk["hbm"],
+            "kernel": "reorder_quantize_kernel", "bound": "hbm", "achieved": rbytes / (q_ms * 1e-3) / 1e9,
+            "peak": pk["hbm"], "unit": "GB/s", "frac": rbytes / (q_ms * 1e-3) / 1e9 / pk["hbm"],
             # one K=4096 launch under ncu: 16.8 MB read, the 5.3 MB written are still in L2 at kernel end
             "traffic": 16.8e6 if wl_name == "llama3-8b-m2048" else None,
+            "traffic_source": "ncu capture at 8192 x 16384 scaled by rows x K, summarised in profiles/reorder_quantize_kernel_8192x16384.md",
             "peak_note": "%s copy bandwidth" % pk["source"],
             "launches": [{"M": job.M, "K": K, "us": t * 1e3, "gbs": reorder_bytes(job.M, K) / (t * 1e-3) / 1e9}
                          for (K, t) in q_each]}
         out["reorder_quant_gbs"] = out["roofline_reorder"]["achieved"]
+        if not a.no_extra:
+            # the other benchmark configurations, each kernel alone over operand sets larger than L2:
+            # the standalone quantiser, the 8192-cube GEMM and two points of the decode sweep
+            job.close()
+            del job
+            torch.cuda.empty_cache()
+            extra = {"standalone_reorder_8192x16384": kernel_case("reorder", 8192, 0, 16384, 10),
+                     "gemm_8192_cube": kernel_case("gemm", 8192, 8192, 8192, 6)}
+            torch.cuda.empty_cache()
+            for M_ in (16, 128):
+                cases = [kernel_case("gemm", M_, N_, K_, 20) for (N_, K_) in ((4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336))]
+                cases.append(kernel_case("reorder", M_, 0, 4096, 20))
+                cases.append(kernel_case("reorder", M_, 0, 14336, 20))
+                extra["decode_m%d" % M_] = [{k: c[k] for k in ("kernel", "M", "N", "K", "us_per_launch", "achieved", "unit", "frac")}
+                                           for c in cases]
+                torch.cuda.empty_cache()
+            out["extra"] = extra
+            job = None
         r = cpu_arm(wl_name, a.cpu_rows, 2, 1)
         out["cpu_baseline"] = {"value": r["tflops"], "unit": unit, "cores": r["cores"], "kind": "port",
                                "sample": r["sample"], "reorder_quant_gbs": r["reorder_gbs"]}
     print(json.dumps(out))
     if world > 1:
         import torch.distributed as dist
+        dist.barrier()
+        job.close()
         dist.destroy_process_group()
 
 

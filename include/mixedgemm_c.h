@@ -9,7 +9,8 @@
  *   - `stream` is a cudaStream_t passed as void* (NULL = default stream); calls are
  *     asynchronous, never synchronise the device and never print;
  *   - the return value is an MG_* status; nothing throws or exits;
- *   - output buffers are caller-owned; the library allocates no device memory.
+ *   - output buffers are caller-owned; the library allocates no device memory (the one
+ *     exception, mg_xbuf_alloc, says so).
  *
  * Paths below (src/..., include/...) are relative to the MixedGemm project and name
  * the reference interface each entry point replaces.
@@ -37,7 +38,8 @@ enum {
   MG_ERR_WORKSPACE = 4,  /* workspace missing or too small */
   MG_ERR_CUDA = 5,       /* a CUDA runtime / driver call failed (see mg_last_cuda_error) */
   MG_ERR_DEVICE = 6,     /* the device is not an sm_100 part */
-  MG_ERR_TIMEOUT = 7     /* a kernel gave up on a bounded wait (see mg_device_status) */
+  MG_ERR_TIMEOUT = 7,    /* a kernel gave up on a bounded wait (see mg_device_status) */
+  MG_ERR_NCCL = 8        /* NCCL is not available in this process, or one of its calls failed */
 };
 
 /* Human-readable text of a status. */
@@ -209,10 +211,17 @@ int mg_matmul_group_pitched(int nprob, const uint8_t* AN, const uint8_t* AS, con
  * so that it is read in place (mg_code_pitch); nprob <= 8.  Otherwise MG_ERR_SHAPE / MG_ERR_ALIGN is
  * returned, nothing is launched, and the caller issues mg_matmul per problem instead.
  *
- * ready_flag (optional): device address of an int.  The kernel does not read the problem's
- * activation before *ready_flag - ready_value >= 0 (an acquire load at system scope, bounded
- * wait, status code 1024 on expiry).  It lets an exchange that is still filling the activation
- * buffer - a copy engine, another GPU writing over NVLink - overlap the problems listed before it.
+ * ready_flags (optional): device address of ready_count ints (0 counts as 1).  The kernel does not
+ * read the problem's activation before every one of them has reached the target value
+ * (flag - target >= 0; acquire loads at system scope, bounded wait, status code 1024 on expiry).
+ * The target is *ready_epoch when that device pointer is set - a word the host bumps once per step
+ * (mg_epoch_bump), so that a captured launch can be replayed - and ready_value otherwise.  It lets
+ * an exchange that is still filling the activation buffer - copy engines, other GPUs writing over
+ * NVLink (mg_push_shard) - overlap the problems listed before it.
+ * ready_rows > 0 (a multiple of 256) makes flag i stand for rows [i ready_rows, (i+1) ready_rows)
+ * only: a tile then waits for the flag of its own rows, not for all of them.  first_row (a
+ * multiple of 256) is the row the problem's tile order starts with, wrapping around - the rows
+ * that are there first, e.g. the ones this GPU quantised itself.
  */
 typedef struct mg_problem {
   const uint8_t *AN, *AS, *AO, *SFAN, *SFAS, *SFAO; /* activation, as written by mg_reorder_quantize_pitched */
@@ -222,8 +231,12 @@ typedef struct mg_problem {
   int M, N, KN, KS, KO;
   void* D_bf16; /* [M,N] bf16, row pitch ldd elements */
   int ldd;
-  const int* ready_flag;
+  const int* ready_flags;
+  int ready_count;
+  const int* ready_epoch;
   int ready_value;
+  int ready_rows;
+  int first_row;
 } mg_problem_t;
 int mg_matmul_multi(int nprob, const mg_problem_t* probs, void* stream);
 
@@ -238,6 +251,57 @@ int mg_matmul_f32(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, const
                   const void* C_bf16, float* D_f32, int ldd, const uint8_t* SFAN, const uint8_t* SFBN,
                   const uint8_t* SFAS, const uint8_t* SFBS, const uint8_t* SFAO, const uint8_t* SFBO,
                   void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Multi-GPU use, one process per GPU.  The GEMM shards along N (rank r owns rows
+ * [r N/P, (r+1) N/P) of the quantised weight, whole 128-row scale blocks); K is never split, so
+ * every output element is the same K-ordered sum as on one GPU.  The reference has no multi-GPU
+ * mode; these entry points have no counterpart there.
+ *
+ * Plain collectives (NCCL, taken from the process or loaded by name; MG_ERR_NCCL when absent):
+ *   mg_dist_unique_id    rank 0 makes the 128-byte id, the host hands it to the other ranks
+ *   mg_dist_init         communicator of `world` ranks for the current device
+ *   mg_bcast_activations one grouped broadcast of up to six buffers from `root` into every rank's
+ *                        own memory ("quantise once, broadcast")
+ *   mg_allgather_inplace every rank has written its shard (bytes [rank * shard, (rank+1) * shard)
+ *                        of each buffer); the others' shards are gathered in place
+ *   mg_allgather_output  [M, N/P] shards -> P consecutive [M, N/P] blocks, for callers that need
+ *                        the whole output
+ */
+int mg_dist_unique_id(void* id128);
+int mg_dist_init(void** comm, const void* id128, int world, int rank);
+int mg_dist_destroy(void* comm);
+int mg_bcast_activations(void* comm, int root, void* const* bufs, const size_t* bytes, int nbuf, void* stream);
+int mg_allgather_inplace(void* comm, void* const* bufs, const size_t* shard_bytes, int nbuf, void* stream);
+int mg_allgather_output(void* comm, const void* Y_local, void* Y_shards, size_t bytes_per_rank, void* stream);
+
+/*
+ * The overlapped exchange: every rank quantises M / P rows of an activation in place in its own
+ * full-size buffer and pushes them into every peer's buffer with copy-engine copies over NVLink,
+ * followed by a 4-byte flag; the GEMM that consumes the activation is launched at once and waits,
+ * problem by problem, for the flags (mg_problem_t.ready_flags).  No SM takes part in the transfer.
+ *   mg_xbuf_alloc / mg_xbuf_free   an exchange buffer (plain device allocation, zero-filled): the
+ *                        one place where this library allocates, because the buffer must be
+ *                        exportable as a whole
+ *   mg_ipc_export / mg_ipc_import / mg_ipc_close   64-byte handle of such a buffer for the other
+ *                        processes of the node; importing enables peer access
+ *   mg_epoch_bump        *epoch_word += 1 on `stream` (one thread); call once per step before the
+ *                        quantisers
+ *   mg_push_shard        bases[r] = rank r's buffer as seen from this process (bases[rank] the own
+ *                        one); byte ranges seg_off / seg_bytes (the same in every buffer) go to
+ *                        each peer on streams[0 .. world-2], then the int at flag_off + rank * 4
+ *                        receives *epoch_word.  The streams must already wait for the quantiser.
+ * Buffers are used in turn by consecutive steps; keep two sets and alternate, because a rank may
+ * start pushing the next step while a slower peer still multiplies the current one.
+ */
+int mg_xbuf_alloc(void** ptr, size_t bytes);
+int mg_xbuf_free(void* ptr);
+int mg_ipc_export(const void* ptr, void* handle64);
+int mg_ipc_import(const void* handle64, void** ptr);
+int mg_ipc_close(void* ptr);
+int mg_epoch_bump(int* epoch_word, void* stream);
+int mg_push_shard(int world, int rank, void* const* bases, const size_t* seg_off, const size_t* seg_bytes, int nseg,
+                  size_t flag_off, const int* epoch_word, void* const* streams);
 
 /*
  * mg_matmul for callers that cannot allocate.  No counterpart in the reference (its binding

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_PKG, "libmixedgemm_b200.so")
 
 MG_OK = 0
 STATUS_NAMES = {0: "MG_OK", 1: "MG_ERR_SHAPE", 2: "MG_ERR_NULL", 3: "MG_ERR_ALIGN", 4: "MG_ERR_WORKSPACE",
-                5: "MG_ERR_CUDA", 6: "MG_ERR_DEVICE", 7: "MG_ERR_TIMEOUT"}
+                5: "MG_ERR_CUDA", 6: "MG_ERR_DEVICE", 7: "MG_ERR_TIMEOUT", 8: "MG_ERR_NCCL"}
 
 # every symbol include/*.h declares, with its prototype
 _vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
@@ -25,6 +25,19 @@ PROTOTYPES = {
     "mg_get_option": (_i, [ctypes.c_char_p, ctypes.POINTER(_i)]),
     "mg_reset_options": (None, []),
     "mg_matmul_multi": (_i, [_i, _vp, _vp]),
+    "mg_dist_unique_id": (_i, [_vp]),
+    "mg_dist_init": (_i, [ctypes.POINTER(_vp), _vp, _i, _i]),
+    "mg_dist_destroy": (_i, [_vp]),
+    "mg_bcast_activations": (_i, [_vp, _i, _vp, _vp, _i, _vp]),
+    "mg_allgather_inplace": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "mg_allgather_output": (_i, [_vp, _vp, _vp, _sz, _vp]),
+    "mg_xbuf_alloc": (_i, [ctypes.POINTER(_vp), _sz]),
+    "mg_xbuf_free": (_i, [_vp]),
+    "mg_ipc_export": (_i, [_vp, _vp]),
+    "mg_ipc_import": (_i, [_vp, ctypes.POINTER(_vp)]),
+    "mg_ipc_close": (_i, [_vp]),
+    "mg_epoch_bump": (_i, [_vp, _vp]),
+    "mg_push_shard": (_i, [_i, _i, _vp, _vp, _vp, _i, _sz, _vp, _vp]),
     "mg_sf_bytes": (_sz, [_i, _i]),
     "mg_reorder_quantize_x": (_i, [_vp, _i, _i, _vp, _i, _i, _i] + [_vp] * 6 + [_vp]),
     "mg_reorder_quantize_w": (_i, [_vp, _i, _i, _vp, _i, _i, _i] + [_vp] * 6 + [_vp]),
@@ -51,7 +64,9 @@ class Problem(ctypes.Structure):
     _fields_ = ([(n, _vp) for n in ("AN", "AS", "AO", "SFAN", "SFAS", "SFAO")] + [("pitch_a", _sz * 3)] +
                 [(n, _vp) for n in ("BN", "BS", "BO", "SFBN", "SFBS", "SFBO")] + [("pitch_b", _sz * 3)] +
                 [(n, _i) for n in ("M", "N", "KN", "KS", "KO")] + [("D_bf16", _vp), ("ldd", _i),
-                                                                  ("ready_flag", _vp), ("ready_value", _i)])
+                                                                  ("ready_flags", _vp), ("ready_count", _i),
+                                                                  ("ready_epoch", _vp), ("ready_value", _i),
+                                                                  ("ready_rows", _i), ("first_row", _i)])
 
 
 _lib = None

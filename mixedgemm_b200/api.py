@@ -259,8 +259,9 @@ def matmul_multi(problems, flags=None):
     """One launch for a list of independent products (up to 8): problems = [(A, B, out), ...] with
     A = (AN, AS, AO, SFAN, SFAS, SFAO), B likewise for the weights, out a [M, N] bf16 tensor or None.
     Each problem has its own activation and K split, unlike matmul_group.  `flags` (optional) gives
-    per problem None or (int32 CUDA tensor of one element, value): the kernel reads that problem's
-    activation only once the flag has reached the value (mg_problem_t.ready_flag).  Problems the
+    per problem None or (int32 CUDA tensor, value or int32 CUDA tensor holding the value[, rows per flag, first row]): the kernel
+    reads that problem's activation only once every flag has reached the value
+    (mg_problem_t.ready_flags).  Problems the
     CTA-pair kernel does not take (M <= 128, N not a multiple of 256, buffers that need the padded
     copy) fall back to one matmul per problem; flags are then refused.  Returns the outputs."""
     import ctypes
@@ -288,10 +289,16 @@ def matmul_multi(problems, flags=None):
         q.D_bf16, q.ldd = _ptr(out), out.stride(0)
         f = flags[j] if flags is not None else None
         if f is not None:
-            ft, fv = f
+            ft, fv = f[0], f[1]
+            q.ready_rows = int(f[2]) if len(f) > 2 else 0
+            q.first_row = int(f[3]) if len(f) > 3 else 0
             if not ft.is_cuda or ft.dtype != torch.int32 or ft.numel() < 1 or ft.device != dev:
-                raise RuntimeError("matmul_multi: a ready flag must be an int32 CUDA tensor on the operands' device")
-            q.ready_flag, q.ready_value = ft.data_ptr(), int(fv)
+                raise RuntimeError("matmul_multi: ready flags must be an int32 CUDA tensor on the operands' device")
+            q.ready_flags, q.ready_count = ft.data_ptr(), ft.numel()
+            if torch.is_tensor(fv):  # a device word that holds the target (bumped once per step)
+                q.ready_epoch, q.ready_value = fv.data_ptr(), 0
+            else:
+                q.ready_epoch, q.ready_value = None, int(fv)
     st = 1
     if 1 <= n <= 8:
         with torch.cuda.device(dev):

@@ -50,7 +50,7 @@ def build_lib(force=False, verbose=False):
     for p, cmd in procs:
         if p.wait() != 0:
             raise RuntimeError("nvcc failed: " + " ".join(cmd))
-    cmd = ["nvcc", "-shared", "-o", LIB] + objs + ["-lcudart"]
+    cmd = ["nvcc", "-shared", "-o", LIB] + objs + ["-lcudart", "-ldl"]
     if verbose:
         print(" ".join(cmd))
     subprocess.check_call(cmd)

@@ -110,6 +110,7 @@ extern "C" const char* mg_strerror(int status) {
     case MG_ERR_CUDA: return "CUDA call failed";
     case MG_ERR_DEVICE: return "device is not sm_100";
     case MG_ERR_TIMEOUT: return "kernel gave up on a bounded wait";
+    case MG_ERR_NCCL: return "NCCL unavailable or an NCCL call failed";
     default: return "unknown status";
   }
 }

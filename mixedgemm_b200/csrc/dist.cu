@@ -1,0 +1,226 @@
+// Multi-GPU exchange behind the C ABI (one process per GPU).
+//
+// The GEMM shards along N, so every rank needs the whole quantised activation.  Two ways to get
+// it there:
+//   * plain NCCL collectives on the caller's stream (mg_bcast_activations, mg_allgather_inplace,
+//     mg_allgather_output).  NCCL is taken from the process (the libnccl that the host framework
+//     already loaded) or loaded by name; nothing links against it, so the library loads without it.
+//   * the overlapped exchange: every rank quantises its M / P rows and PUSHES them into every
+//     peer's buffer with copy-engine copies over NVLink (cudaMemcpyAsync on per-peer streams, no SM
+//     involved, so the copies run under the GEMMs), followed by a 4-byte flag copy.  The GEMM that
+//     consumes the activation is already running: its producer waits for the flags
+//     (mg_problem_t.ready_flags).  Peer buffers are opened through CUDA IPC.
+// No kernel of this library ever has another GPU's memory as an operand; the only things that
+// cross NVLink are NCCL's transfers and those copies.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <mutex>
+
+#include "mg_common.h"
+
+namespace {
+
+struct NcclApi {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*Broadcast)(const void*, void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
+  bool ok = false;
+};
+
+NcclApi g_nccl;
+std::once_flag g_nccl_once;
+
+const NcclApi& nccl() {
+  std::call_once(g_nccl_once, [] {
+    // the copy the process already holds (one NCCL per process), else by name
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return;
+    g_nccl.handle = h;
+#define MG_SYM(field, name) g_nccl.field = reinterpret_cast<decltype(g_nccl.field)>(dlsym(h, name))
+    MG_SYM(GetUniqueId, "ncclGetUniqueId");
+    MG_SYM(CommInitRank, "ncclCommInitRank");
+    MG_SYM(CommDestroy, "ncclCommDestroy");
+    MG_SYM(Broadcast, "ncclBroadcast");
+    MG_SYM(AllGather, "ncclAllGather");
+    MG_SYM(GroupStart, "ncclGroupStart");
+    MG_SYM(GroupEnd, "ncclGroupEnd");
+#undef MG_SYM
+    g_nccl.ok = g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.CommDestroy && g_nccl.Broadcast &&
+                g_nccl.AllGather && g_nccl.GroupStart && g_nccl.GroupEnd;
+  });
+  return g_nccl;
+}
+
+struct Comm {
+  ncclComm_t nccl;
+  int world, rank;
+};
+
+#define MG_NCCL_TRY(expr)                      \
+  do {                                         \
+    if ((expr) != ncclSuccess) return MG_ERR_NCCL; \
+  } while (0)
+
+__global__ void epoch_bump_kernel(int* word) { *word += 1; }
+
+}  // namespace
+
+extern "C" int mg_dist_unique_id(void* id128) {
+  if (!id128) return MG_ERR_NULL;
+  const NcclApi& n = nccl();
+  if (!n.ok) return MG_ERR_NCCL;
+  static_assert(sizeof(ncclUniqueId) == 128, "the C ABI hands the id around as 128 bytes");
+  MG_NCCL_TRY(n.GetUniqueId(static_cast<ncclUniqueId*>(id128)));
+  return MG_OK;
+}
+
+extern "C" int mg_dist_init(void** comm, const void* id128, int world, int rank) {
+  if (!comm || !id128) return MG_ERR_NULL;
+  if (world < 1 || rank < 0 || rank >= world) return MG_ERR_SHAPE;
+  const NcclApi& n = nccl();
+  if (!n.ok) return MG_ERR_NCCL;
+  ncclUniqueId id;
+  memcpy(&id, id128, sizeof(id));
+  Comm* c = new Comm{nullptr, world, rank};
+  if (n.CommInitRank(&c->nccl, world, id, rank) != ncclSuccess) {
+    delete c;
+    return MG_ERR_NCCL;
+  }
+  *comm = c;
+  return MG_OK;
+}
+
+extern "C" int mg_dist_destroy(void* comm) {
+  if (!comm) return MG_OK;
+  Comm* c = static_cast<Comm*>(comm);
+  const NcclApi& n = nccl();
+  const bool ok = n.ok && n.CommDestroy(c->nccl) == ncclSuccess;
+  delete c;
+  return ok ? MG_OK : MG_ERR_NCCL;
+}
+
+extern "C" int mg_bcast_activations(void* comm, int root, void* const* bufs, const size_t* bytes, int nbuf,
+                                    void* stream) {
+  if (!comm || !bufs || !bytes) return MG_ERR_NULL;
+  Comm* c = static_cast<Comm*>(comm);
+  if (root < 0 || root >= c->world || nbuf < 0) return MG_ERR_SHAPE;
+  const NcclApi& n = nccl();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MG_NCCL_TRY(n.GroupStart());
+  for (int i = 0; i < nbuf; ++i) {
+    if (bytes[i] == 0) continue;
+    if (!bufs[i]) {
+      n.GroupEnd();
+      return MG_ERR_NULL;
+    }
+    if (n.Broadcast(bufs[i], bufs[i], bytes[i], ncclUint8, root, c->nccl, st) != ncclSuccess) {
+      n.GroupEnd();
+      return MG_ERR_NCCL;
+    }
+  }
+  MG_NCCL_TRY(n.GroupEnd());
+  return MG_OK;
+}
+
+extern "C" int mg_allgather_inplace(void* comm, void* const* bufs, const size_t* shard_bytes, int nbuf, void* stream) {
+  if (!comm || !bufs || !shard_bytes) return MG_ERR_NULL;
+  Comm* c = static_cast<Comm*>(comm);
+  const NcclApi& n = nccl();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MG_NCCL_TRY(n.GroupStart());
+  for (int i = 0; i < nbuf; ++i) {
+    if (shard_bytes[i] == 0) continue;
+    if (!bufs[i]) {
+      n.GroupEnd();
+      return MG_ERR_NULL;
+    }
+    uint8_t* base = static_cast<uint8_t*>(bufs[i]);
+    if (n.AllGather(base + (size_t)c->rank * shard_bytes[i], base, shard_bytes[i], ncclUint8, c->nccl, st) != ncclSuccess) {
+      n.GroupEnd();
+      return MG_ERR_NCCL;
+    }
+  }
+  MG_NCCL_TRY(n.GroupEnd());
+  return MG_OK;
+}
+
+extern "C" int mg_allgather_output(void* comm, const void* Y_local, void* Y_shards, size_t bytes_per_rank,
+                                   void* stream) {
+  if (!comm || !Y_local || !Y_shards) return MG_ERR_NULL;
+  Comm* c = static_cast<Comm*>(comm);
+  const NcclApi& n = nccl();
+  MG_NCCL_TRY(n.AllGather(Y_local, Y_shards, bytes_per_rank, ncclUint8, c->nccl, static_cast<cudaStream_t>(stream)));
+  return MG_OK;
+}
+
+// ---------------------------------------------------------------- peer buffers
+extern "C" int mg_xbuf_alloc(void** ptr, size_t bytes) {
+  if (!ptr) return MG_ERR_NULL;
+  if (bytes == 0) return MG_ERR_SHAPE;
+  MG_CUDA_TRY(cudaMalloc(ptr, bytes));
+  MG_CUDA_TRY(cudaMemset(*ptr, 0, bytes));
+  return MG_OK;
+}
+
+extern "C" int mg_xbuf_free(void* ptr) {
+  if (ptr) MG_CUDA_TRY(cudaFree(ptr));
+  return MG_OK;
+}
+
+extern "C" int mg_ipc_export(const void* ptr, void* handle64) {
+  if (!ptr || !handle64) return MG_ERR_NULL;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the C ABI hands the handle around as 64 bytes");
+  MG_CUDA_TRY(cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), const_cast<void*>(ptr)));
+  return MG_OK;
+}
+
+extern "C" int mg_ipc_import(const void* handle64, void** ptr) {
+  if (!ptr || !handle64) return MG_ERR_NULL;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  MG_CUDA_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return MG_OK;
+}
+
+extern "C" int mg_ipc_close(void* ptr) {
+  if (ptr) MG_CUDA_TRY(cudaIpcCloseMemHandle(ptr));
+  return MG_OK;
+}
+
+extern "C" int mg_epoch_bump(int* epoch_word, void* stream) {
+  if (!epoch_word) return MG_ERR_NULL;
+  epoch_bump_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(epoch_word);
+  MG_CUDA_TRY(cudaGetLastError());
+  return MG_OK;
+}
+
+extern "C" int mg_push_shard(int world, int rank, void* const* bases, const size_t* seg_off, const size_t* seg_bytes,
+                             int nseg, size_t flag_off, const int* epoch_word, void* const* streams) {
+  if (!bases || !seg_off || !seg_bytes || !epoch_word || !streams) return MG_ERR_NULL;
+  if (world < 1 || rank < 0 || rank >= world || nseg < 0) return MG_ERR_SHAPE;
+  const uint8_t* mine = static_cast<const uint8_t*>(bases[rank]);
+  if (!mine) return MG_ERR_NULL;
+  for (int step = 0; step < world; ++step) {
+    // peers in ring order downwards from this rank, so that at any moment the ranks write to
+    // different targets and rank r hears from r + 1 first, then r + 2, ...; step 0 is this rank
+    // itself: its rows are already in place, only its own flag goes up
+    const int peer = (rank - step + world) % world;
+    uint8_t* dst = static_cast<uint8_t*>(bases[peer]);
+    if (!dst) return MG_ERR_NULL;
+    cudaStream_t st = static_cast<cudaStream_t>(streams[step == 0 ? 0 : step - 1]);
+    for (int i = 0; i < nseg && step > 0; ++i)
+      if (seg_bytes[i])
+        MG_CUDA_TRY(cudaMemcpyAsync(dst + seg_off[i], mine + seg_off[i], seg_bytes[i], cudaMemcpyDefault, st));
+    // stream order: the flag leaves after the data has arrived
+    MG_CUDA_TRY(cudaMemcpyAsync(dst + flag_off + (size_t)rank * sizeof(int), epoch_word, sizeof(int), cudaMemcpyDefault, st));
+  }
+  return MG_OK;
+}

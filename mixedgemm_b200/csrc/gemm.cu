@@ -621,8 +621,15 @@ struct PairProb {
   int tiles_m2;   // 256-row blocks
   int tile_end;   // tiles of problems 0..this one
   int s_units;    // K stages per tile
-  const int* flag;  // optional: activation is complete when *flag >= flag_value
+  // optional: the activation is complete when flag[0 .. flag_count) have all reached the target
+  // value, which is *flag_epoch when that pointer is set (a device word the host bumps once per
+  // step, so that a captured launch can be replayed) and flag_value otherwise
+  const int* flag;
+  int flag_count;
+  const int* flag_epoch;
   int flag_value;
+  int flag_rows;  // > 0: flag i covers rows [i * flag_rows, (i + 1) * flag_rows) and a tile waits only for its own rows' flag
+  int m_rot;      // 256-row block the problem's tile order starts with (the blocks whose rows are there first)
 };
 
 struct PairParams {
@@ -718,6 +725,8 @@ mixed_gemm_pair_kernel(const __grid_constant__ PairParams p, const __grid_consta
     while (prob + 1 < p.nprob && t >= p.prob[prob].tile_end) start = p.prob[prob++].tile_end;
     const int tm2 = p.prob[prob].tiles_m2;
     raster(t - start, tm2, (p.prob[prob].tile_end - start) / tm2, m_pt, n_tile);
+    m_pt += p.prob[prob].m_rot;
+    if (m_pt >= tm2) m_pt -= tm2;
   };
 
   if (warp == 0) {
@@ -725,27 +734,40 @@ mixed_gemm_pair_kernel(const __grid_constant__ PairParams p, const __grid_consta
     const bool leader = ptx::elect_one();
     int stage = 0;
     uint32_t phase = 0;
-    int flag_seen = -1;  // last problem whose ready flag has been seen up
+    int flag_prob = -1;      // problem the mask below belongs to
+    uint32_t flag_mask = 0;  // its flags that have been seen up
     for (int t = first_tile; t < total_tiles; t += tile_step) {
       int prob, m_pt, n_tile;
       locate(t, prob, m_pt, n_tile);
       const PairProb& pp = p.prob[prob];
-      if (pp.flag != nullptr && flag_seen != prob) {
-        // the activation of this problem is being filled by somebody else (a copy engine, another
-        // GPU): wait until its flag says it is complete, then order the tensor-map reads after it
-        const long long t0 = clock64();
-        for (;;) {
-          int v;
-          asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(pp.flag) : "memory");
-          if (v - pp.flag_value >= 0 || *stop) break;
-          __nanosleep(200);
-          if (clock64() - t0 > wait_limit) {
-            *stop = 1;
-            atomicOr(p.status, 1024);
+      if (pp.flag != nullptr) {
+        // The activation of this problem is being filled by somebody else (copy engines, other
+        // GPUs over NVLink): wait until the flag of this tile's rows - or, without per-row flags,
+        // every flag - has reached the target, then order the tensor-map reads after it.
+        if (flag_prob != prob) { flag_prob = prob; flag_mask = 0; }
+        const int f0 = pp.flag_rows > 0 ? min((m_pt * 256) / pp.flag_rows, pp.flag_count - 1) : 0;
+        const int f1 = pp.flag_rows > 0 ? f0 + 1 : pp.flag_count;
+        bool waited = false;
+        for (int f = f0; f < f1; ++f) {
+          if (flag_mask & (1u << (f & 31))) continue;
+          const long long t0 = clock64();
+          int target = pp.flag_value;
+          if (pp.flag_epoch != nullptr)
+            asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(target) : "l"(pp.flag_epoch) : "memory");
+          for (;;) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(pp.flag + f) : "memory");
+            if (v - target >= 0 || *stop) break;
+            __nanosleep(200);
+            if (clock64() - t0 > wait_limit) {
+              *stop = 1;
+              atomicOr(p.status, 1024);
+            }
           }
+          flag_mask |= 1u << (f & 31);
+          waited = true;
         }
-        asm volatile("fence.proxy.async.global;" ::: "memory");
-        flag_seen = prob;
+        if (waited) asm volatile("fence.proxy.async.global;" ::: "memory");
       }
       const int m_row0 = m_pt * 256 + (int)rank * 128, n_row0 = n_tile * 256 + (int)rank * 128;
 #pragma unroll 1
@@ -1194,7 +1216,11 @@ struct PairProblem {
   void* D;
   int ldd;
   const int* flag;
+  int flag_count;
+  const int* flag_epoch;
   int flag_value;
+  int flag_rows;
+  int first_row;
 };
 
 // Validates the problems, builds their tensor maps and launches the CTA-pair kernel once.
@@ -1240,7 +1266,13 @@ int launch_pair(int nprob, const PairProblem* pr, int sms, cudaStream_t st) {
     d.tile_end = tiles;
     d.s_units = d.seg[0].nstages + d.seg[1].nstages + d.seg[2].nstages;
     d.flag = q.flag;
+    d.flag_count = q.flag ? (q.flag_count > 0 ? q.flag_count : 1) : 0;
+    d.flag_epoch = q.flag_epoch;
     d.flag_value = q.flag_value;
+    if (q.flag && q.flag_count > 32) return MG_ERR_SHAPE;
+    if (q.flag_rows < 0 || q.flag_rows % 256 || q.first_row < 0 || q.first_row % 256) return MG_ERR_SHAPE;
+    d.flag_rows = q.flag ? q.flag_rows : 0;
+    d.m_rot = (q.first_row / 256) % d.tiles_m2;
   }
   for (int j = nprob; j < kMaxProb; ++j) {  // unused slots: valid maps, never dereferenced
     for (int seg = 0; seg < 3; ++seg) {
@@ -1542,7 +1574,8 @@ extern "C" int mg_matmul_multi(int nprob, const mg_problem_t* probs, void* strea
     }
     q.M = s.M; q.N = s.N; q.KN = s.KN; q.KS = s.KS; q.KO = s.KO;
     q.D = s.D_bf16; q.ldd = s.ldd;
-    q.flag = s.ready_flag; q.flag_value = s.ready_value;
+    q.flag = s.ready_flags; q.flag_count = s.ready_count; q.flag_epoch = s.ready_epoch; q.flag_value = s.ready_value;
+    q.flag_rows = s.ready_rows; q.first_row = s.first_row;
   }
   return launch_pair(nprob, pr, di.sm_count, static_cast<cudaStream_t>(stream));
 }

@@ -1,17 +1,31 @@
-"""N-sharded multi-GPU use of the path (one process per GPU, torch.distributed for the plumbing).
+"""N-sharded multi-GPU use of the path (one process per GPU).
 
 The GEMM shards along N: rank r owns output columns [r*N/P, (r+1)*N/P), i.e. rows of the
 quantised weight.  K is never split, so every output element is computed exactly as on one
-GPU.  The one exchange step is the broadcast of the quantised activations (six buffers) from
-the rank that quantised them; outputs stay sharded unless the caller gathers them.
+GPU.  What has to travel is the quantised activation; outputs stay sharded unless the caller
+gathers them.  The transfers are made by the C ABI (include/mixedgemm_c.h, csrc/dist.cu):
 
-The reference has no multi-GPU mode; these helpers are tensor-library agnostic on purpose
-(they work on CPU tensors over gloo as well), the kernels never see another GPU's memory.
+  Communicator   NCCL collectives through mg_dist_* / mg_bcast_activations / mg_allgather_*:
+                 "quantise once, broadcast", or "quantise M/P rows each, all-gather"
+  PushExchange   the overlapped exchange: every rank quantises M/P rows in place in its own
+                 full-size buffer and pushes them into every peer's buffer with copy-engine
+                 copies over NVLink (mg_push_shard); the GEMM is launched at once and waits,
+                 row shard by row shard, for the flags that follow the data
+
+The only thing the host framework (torch.distributed) is used for is handing small byte strings
+from rank to rank at set-up time: the NCCL id and the IPC handles of the exchange buffers.
+The shard bookkeeping (shard_range, sf_shard, shard_weights, activation_shard) is plain tensor
+slicing and works on CPU tensors too.  The reference has no multi-GPU mode; the kernels never
+have another GPU's memory as an operand.
 """
+import ctypes
+
 import torch
-import torch.distributed as dist
+
+from . import _capi
 
 
+# ----------------------------------------------------------------------------- shard bookkeeping
 def shard_range(N, world, rank):
     """(first row, row count) of `rank`'s weight shard.  Shards are whole 128-row scale blocks."""
     if N % (128 * world) != 0:
@@ -36,27 +50,6 @@ def shard_weights(B, N, KN, KS, KO, world, rank):
             sf_shard(B[3], N, KN, world, rank), sf_shard(B[4], N, KS, world, rank), sf_shard(B[5], N, KO, world, rank))
 
 
-def broadcast_activations(A, src=0, group=None):
-    """Broadcast the six quantised-activation buffers from `src` into every rank's own memory.
-    Buffers carved from one allocation (alloc_quantized_x(one_buffer=True)) go as a single
-    transfer; otherwise each buffer is sent on its own, row-pitched views with their padding."""
-    live = [t for t in A if t.numel()]
-    if not live:
-        return
-    storages = {t.untyped_storage().data_ptr() for t in live}
-    if len(storages) == 1 and len(live) > 1:
-        st = live[0].untyped_storage()
-        flat = torch.empty(0, dtype=torch.uint8, device=live[0].device).set_(st, 0, (st.nbytes(),))
-        dist.broadcast(flat, src=src, group=group)
-        return
-    for t in live:
-        base = t
-        if not t.is_contiguous():
-            # a pitched view [rows, logical] of a [rows, pitch] buffer: send the whole buffer
-            base = t.as_strided((t.size(0), t.stride(0)), (t.stride(0), 1), t.storage_offset())
-        dist.broadcast(base, src=src, group=group)
-
-
 def _pitched_base(t):
     """[rows, pitch] buffer under a [rows, logical] row-pitched view (or the tensor itself)."""
     if t.is_contiguous():
@@ -79,36 +72,218 @@ def activation_shard(A, M, split, world, rank):
     return tuple(out)
 
 
-def all_gather_activations(A, M, split, world, rank, group=None):
-    """Every rank has quantised its own M/P rows in place (activation_shard); gather the other
-    ranks' rows so that each GPU holds the whole quantised activation in its own memory."""
+def shard_byte_ranges(A, M, split, world, rank):
+    """[(tensor, first byte, byte count), ...]: where rank's M/P rows live inside each of the six
+    buffers of a quantised activation (codes: rows x pitch; scales: whole 128-row blocks)."""
     mp = M // world
+    out = []
     for i in range(3):
-        if A[i].numel() == 0:
-            continue
         base = _pitched_base(A[i])
-        dist.all_gather_into_tensor(base.view(-1), base[rank * mp:(rank + 1) * mp].reshape(-1), group=group)
+        pitch = base.stride(0) if base.numel() else 0
+        out.append((base, rank * mp * pitch, mp * pitch))
     for i, k in enumerate(split):
-        if k == 0:
-            continue
         per_block = ((k + 127) // 128) * 512
-        n = (M // 128) * per_block
-        full = A[3 + i][:n]
-        dist.all_gather_into_tensor(full, full[(rank * mp // 128) * per_block:((rank + 1) * mp // 128) * per_block],
-                                    group=group)
+        out.append((A[3 + i], (rank * mp // 128) * per_block, (mp // 128) * per_block))
+    return out
 
 
-def all_gather_output(Y_local, world, group=None):
-    """[M, N/P] shards -> [M, N] (only for callers that need the full tensor)."""
-    parts = [torch.empty_like(Y_local) for _ in range(world)]
-    dist.all_gather(parts, Y_local.contiguous(), group=group)
-    return torch.cat(parts, dim=1)
+def _vp_array(values):
+    return (ctypes.c_void_p * len(values))(*values)
 
 
-def all_gather_rows(Y_local, world, group=None):
-    """Token-sharded use (every rank multiplies its own M/P rows with all weights; nothing is
-    exchanged on the way in): [M/P, N] shards -> [M, N], for callers that need the full tensor."""
-    full = torch.empty((Y_local.size(0) * world,) + tuple(Y_local.shape[1:]), dtype=Y_local.dtype,
-                       device=Y_local.device)
-    dist.all_gather_into_tensor(full, Y_local.contiguous(), group=group)
-    return full
+def _sz_array(values):
+    return (ctypes.c_size_t * len(values))(*values)
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _exchange_bytes(payload, group=None):
+    """Every rank contributes a byte string; returns the list of all of them (set-up time only)."""
+    import torch.distributed as dist
+    out = [None] * dist.get_world_size(group)
+    dist.all_gather_object(out, payload, group=group)
+    return out
+
+
+# ----------------------------------------------------------------------------- NCCL through the C ABI
+class Communicator:
+    """An NCCL communicator owned by the library (mg_dist_init).  The 128-byte id is made on rank 0
+    and handed to the others through `group` (a torch.distributed group over any backend)."""
+
+    def __init__(self, world, rank, group=None):
+        import torch.distributed as dist
+        self.lib = _capi.load()
+        self.world, self.rank = world, rank
+        ident = ctypes.create_string_buffer(128)
+        if rank == 0:
+            _capi.check(self.lib.mg_dist_unique_id(ident), "mg_dist_unique_id")
+        box = [ident.raw]
+        dist.broadcast_object_list(box, src=0, group=group)
+        self.handle = ctypes.c_void_p()
+        _capi.check(self.lib.mg_dist_init(ctypes.byref(self.handle), box[0], world, rank), "mg_dist_init")
+
+    def close(self):
+        if self.handle:
+            self.lib.mg_dist_destroy(self.handle)
+            self.handle = ctypes.c_void_p()
+
+    def broadcast_activations(self, A, src=0):
+        """The six quantised-activation buffers go from `src` into every rank's own memory in one
+        grouped broadcast (row-pitched views are sent with their padding)."""
+        bufs = [_pitched_base(t) for t in A if t.numel()]
+        _capi.check(self.lib.mg_bcast_activations(
+            self.handle, src, _vp_array([t.data_ptr() for t in bufs]),
+            _sz_array([t.numel() * t.element_size() for t in bufs]), len(bufs), _stream()), "mg_bcast_activations")
+
+    def all_gather_activations(self, A, M, split):
+        """Every rank has quantised its own M/P rows in place (activation_shard); gather the others'."""
+        ptrs, shard = [], []
+        for t, first, count in shard_byte_ranges(A, M, split, self.world, 0):
+            if count:
+                ptrs.append(t.data_ptr())
+                shard.append(count)
+        _capi.check(self.lib.mg_allgather_inplace(self.handle, _vp_array(ptrs), _sz_array(shard), len(ptrs), _stream()),
+                    "mg_allgather_inplace")
+
+    def all_gather_output(self, Y_local):
+        """[M, N/P] shards -> [M, N] (only for callers that need the whole output)."""
+        Yl = Y_local.contiguous()
+        parts = torch.empty((self.world,) + tuple(Yl.shape), dtype=Yl.dtype, device=Yl.device)
+        _capi.check(self.lib.mg_allgather_output(self.handle, Yl.data_ptr(), parts.data_ptr(),
+                                                 Yl.numel() * Yl.element_size(), _stream()), "mg_allgather_output")
+        return torch.cat(list(parts), dim=1)
+
+
+# ----------------------------------------------------------------------------- the overlapped exchange
+class _Raw:
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+def _align(n, a=1024):
+    return (n + a - 1) // a * a
+
+
+class PushExchange:
+    """Exchange buffers for `n_sets` x len(shapes) quantised activations (shapes = [(M, (KN, KS, KO)), ...];
+    n_sets = 2 lets consecutive steps alternate, which they must: a rank may start pushing the next
+    step while a slower peer still multiplies the current one).  Every buffer is one device
+    allocation that holds the six row-pitched tensors of alloc_quantized_x plus `world` flag words,
+    laid out identically on every rank and opened on every other rank through CUDA IPC."""
+
+    def __init__(self, shapes, world, rank, device, n_sets=2, group=None):
+        self.lib = lib = _capi.load()
+        self.world, self.rank, self.device = world, rank, device
+        self.shapes = list(shapes)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.streams = [torch.cuda.Stream(device=device) for _ in range(max(world - 1, 1))]
+        self.sets = []
+        handles = []
+        with torch.cuda.device(device):
+            for s in range(n_sets):
+                bufs = []
+                for (M, split) in self.shapes:
+                    if M % (256 * world) != 0:
+                        raise ValueError("M = %d must split into %d shards of whole 256-row blocks" % (M, world))
+                    logical = (split[0] // 2, split[1] // 4 * 3, split[2])
+                    pitch = [lib.mg_code_pitch(0, i, k) for i, k in enumerate(split)]
+                    sizes = [M * p for p in pitch] + [lib.mg_sf_bytes(M, k) for k in split]
+                    offs, off = [], 0
+                    for n in sizes:
+                        offs.append(off)
+                        off += _align(max(n, 1))
+                    flag_off = off
+                    total = off + _align(4 * world)
+                    ptr = ctypes.c_void_p()
+                    _capi.check(lib.mg_xbuf_alloc(ctypes.byref(ptr), total), "mg_xbuf_alloc")
+                    h = ctypes.create_string_buffer(64)
+                    _capi.check(lib.mg_ipc_export(ptr, h), "mg_ipc_export")
+                    handles.append(h.raw)
+                    flat = torch.as_tensor(_Raw(ptr.value, total), device=device)
+                    A = []
+                    for i in range(3):
+                        v = flat[offs[i]:offs[i] + sizes[i]].view(M, pitch[i])
+                        A.append(v[:, :logical[i]] if pitch[i] != logical[i] else v)
+                    for i in range(3):
+                        A.append(flat[offs[3 + i]:offs[3 + i] + sizes[3 + i]])
+                    flags = flat[flag_off:flag_off + 4 * world].view(torch.int32)
+                    mp = M // world
+                    segs = [(offs[i] + rank * mp * pitch[i], mp * pitch[i]) for i in range(3)]
+                    for i, k in enumerate(split):
+                        per_block = ((k + 127) // 128) * 512
+                        segs.append((offs[3 + i] + (rank * mp // 128) * per_block, (mp // 128) * per_block))
+                    bufs.append(dict(ptr=ptr, A=tuple(A), flags=flags, flag_off=flag_off, segs=segs, M=M, split=split,
+                                     bases=None, flat=flat))
+                self.sets.append(bufs)
+        # every rank opens every other rank's buffers
+        self._imported = []
+        all_handles = _exchange_bytes(handles, group) if world > 1 else [handles]
+        k = 0
+        for bufs in self.sets:
+            for b in bufs:
+                bases = []
+                for r in range(world):
+                    if r == rank:
+                        bases.append(b["ptr"].value)
+                    else:
+                        p = ctypes.c_void_p()
+                        with torch.cuda.device(device):
+                            _capi.check(lib.mg_ipc_import(all_handles[r][k], ctypes.byref(p)), "mg_ipc_import")
+                        self._imported.append(p)
+                        bases.append(p.value)
+                b["bases"] = bases
+                k += 1
+
+    def buffers(self, set_index, i):
+        """The six tensors (alloc_quantized_x layout) of activation i in set `set_index`."""
+        return self.sets[set_index][i]["A"]
+
+    def shard(self, set_index, i):
+        """Views of this rank's M/P rows of activation i: what its quantiser writes."""
+        b = self.sets[set_index][i]
+        return activation_shard(b["A"], b["M"], b["split"], self.world, self.rank)
+
+    def begin_step(self):
+        """Once per step, before the quantisers: the value the flags of this step will carry."""
+        _capi.check(self.lib.mg_epoch_bump(self.epoch.data_ptr(), _stream()), "mg_epoch_bump")
+
+    def push(self, set_index, i):
+        """After this rank's rows of activation i have been quantised on the current stream: copy
+        them into every peer's buffer and raise this rank's flag there.  The copies run on the
+        exchange's own streams, ordered after the current stream's work so far."""
+        b = self.sets[set_index][i]
+        done = torch.cuda.Event()
+        done.record()
+        for st in self.streams:
+            st.wait_event(done)
+        _capi.check(self.lib.mg_push_shard(
+            self.world, self.rank, _vp_array(b["bases"]), _sz_array([o for o, _ in b["segs"]]),
+            _sz_array([n for _, n in b["segs"]]), len(b["segs"]), b["flag_off"], self.epoch.data_ptr(),
+            _vp_array([st.cuda_stream for st in self.streams])), "mg_push_shard")
+
+    def ready(self, set_index, i):
+        """The `flags` entry of api.matmul_multi for a problem that reads activation i: one flag per
+        row shard, target = this step's epoch, tiles start with this rank's own rows."""
+        b = self.sets[set_index][i]
+        mp = b["M"] // self.world
+        return (b["flags"], self.epoch, mp, self.rank * mp)
+
+    def join(self):
+        """Make the current stream wait for the copies this rank has issued (end of a step: the
+        buffers it pushed FROM may be overwritten afterwards)."""
+        for st in self.streams:
+            torch.cuda.current_stream().wait_stream(st)
+
+    def close(self):
+        torch.cuda.synchronize(self.device)
+        for p in self._imported:
+            self.lib.mg_ipc_close(p)
+        self._imported = []
+        for bufs in self.sets:
+            for b in bufs:
+                b["A"] = b["flags"] = b["flat"] = None
+                self.lib.mg_xbuf_free(b["ptr"])
+        self.sets = []

@@ -1,7 +1,8 @@
 """world_size-2 CPU (gloo) test of the N-sharded path's host logic: shard ranges, slicing of the
-swizzled scale buffers, broadcast of quantised activations, gather of output shards.  The compute
-on each rank is the CPU oracle, so the check is on the bookkeeping: shards recombine to exactly
-the unsharded result."""
+swizzled scale buffers, the byte ranges the exchange moves (what mg_allgather_inplace and
+mg_push_shard are told to copy), gather of output shards.  The compute on each rank is the CPU
+oracle and the transfers are made by the test over gloo, so the check is on the bookkeeping:
+shards recombine to exactly the unsharded result."""
 import os
 import socket
 
@@ -39,27 +40,9 @@ def _worker(rank, world, port, ret):
         # every rank holds the full quantised weight here only to cut its shard out of it
         Bfull = [torch.from_numpy(np.ascontiguousarray(a)) for a in H.oracle_outputs(H.bits(W), idx, KN, KS, KO, True)]
         Bl = mgd.shard_weights(Bfull, N, KN, KS, KO, world, rank)
-        # rank 0 quantises, the others receive
-        if rank == 0:
-            A = [torch.from_numpy(np.ascontiguousarray(a)) for a in H.oracle_outputs(H.bits(X), idx, KN, KS, KO)]
-        else:
-            A = [torch.zeros((M, KN // 2), dtype=torch.uint8), torch.zeros((M, KS // 4 * 3), dtype=torch.uint8),
-                 torch.zeros((M, KO), dtype=torch.uint8)] + [torch.zeros(orc.sf_bytes(M, k), dtype=torch.uint8)
-                                                              for k in SPLIT]
-        mgd.broadcast_activations(A, src=0)
-        # the same six buffers carved from one allocation travel as one transfer
-        sizes = [t.numel() for t in A]
-        flat = torch.zeros(sum(sizes), dtype=torch.uint8)
-        views, o = [], 0
-        for t_, n_ in zip(A, sizes):
-            views.append(flat[o:o + n_].view(t_.shape))
-            o += n_
-        if rank == 0:
-            for v, t_ in zip(views, A):
-                v.copy_(t_)
-        mgd.broadcast_activations(views, src=0)
-        ret["one_buffer_%d" % rank] = all(bool(torch.equal(v, t_)) for v, t_ in zip(views, A))
-        # quantisation sharded along M: each rank fills its rows, an all-gather completes the buffers
+        A = [torch.from_numpy(np.ascontiguousarray(a)) for a in H.oracle_outputs(H.bits(X), idx, KN, KS, KO)]
+        # quantisation sharded along M: each rank fills its rows of full-size buffers; the byte ranges
+        # shard_byte_ranges names are what the exchange copies, here with gloo
         M2 = 256
         X2 = H.make_x(M2, K, seed=9)
         full = [np.ascontiguousarray(a) for a in H.oracle_outputs(H.bits(X2), idx, KN, KS, KO)]
@@ -69,17 +52,25 @@ def _worker(rank, world, port, ret):
         part = H.oracle_outputs(H.bits(X2[rank * mp_:(rank + 1) * mp_]), idx, KN, KS, KO)
         for dst, src in zip(sh, part):
             dst.copy_(torch.from_numpy(np.ascontiguousarray(src))[:dst.numel()].view(dst.shape))
-        mgd.all_gather_activations(mine, M2, SPLIT, world, rank)
+        covered = True
+        for i in range(6):
+            ranges = [mgd.shard_byte_ranges(mine, M2, SPLIT, world, r)[i] for r in range(world)]
+            # the ranks' ranges tile the buffer: consecutive, equal, no gap
+            covered &= all(ranges[r][1] == r * ranges[0][2] and ranges[r][2] == ranges[0][2] for r in range(world))
+            t, first, count = ranges[rank]
+            flat = t.view(-1)
+            parts = [torch.empty(count, dtype=torch.uint8) for _ in range(world)]
+            dist.all_gather(parts, flat[first:first + count].clone())
+            for r in range(world):
+                flat[ranges[r][1]:ranges[r][1] + count].copy_(parts[r])
+        ret["covered_%d" % rank] = bool(covered)
         ret["allgather_%d" % rank] = all(np.array_equal(m.numpy(), f) for m, f in zip(mine, full))
-        # token-sharded use: each rank quantises and multiplies its own rows with the whole weight
-        m0, mrows = mgd.shard_range(M2, world, rank)
-        Yrows = orc.gemm_f64([np.ascontiguousarray(a) for a in part], [t.numpy() for t in Bfull], mrows, N, KN, KS, KO)
-        Yall = mgd.all_gather_rows(torch.from_numpy(Yrows), world)
-        Yfull = orc.gemm_f64(full, [t.numpy() for t in Bfull], M2, N, KN, KS, KO)
-        ret["rows_%d" % rank] = bool(np.array_equal(Yall.numpy(), Yfull))
+        # N-sharded product: every rank multiplies the whole activation with its weight rows
         r0, n = mgd.shard_range(N, world, rank)
-        Yl = orc.gemm_f64([t.numpy() for t in A], [t.numpy() for t in Bl], M, n, KN, KS, KO)
-        Y = mgd.all_gather_output(torch.from_numpy(Yl), world)
+        Yl = torch.from_numpy(orc.gemm_f64([t.numpy() for t in A], [t.numpy() for t in Bl], M, n, KN, KS, KO))
+        parts = [torch.empty_like(Yl) for _ in range(world)]
+        dist.all_gather(parts, Yl)
+        Y = torch.cat(parts, dim=1)
         if rank == 0:
             Yref = orc.gemm_f64([t.numpy() for t in A], [t.numpy() for t in Bfull], M, N, KN, KS, KO)
             ret["equal"] = bool(np.array_equal(Y.numpy(), Yref))
@@ -94,9 +85,8 @@ def test_two_rank_sharding_recombines_exactly():
     mp.spawn(_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
     assert ret["shape"] == (M, N)
     assert ret["equal"]
-    assert ret["one_buffer_0"] and ret["one_buffer_1"]
+    assert ret["covered_0"] and ret["covered_1"]
     assert ret["allgather_0"] and ret["allgather_1"]
-    assert ret["rows_0"] and ret["rows_1"]
 
 
 def test_shard_helpers():
