@@ -703,12 +703,20 @@ def main():
     status = job.mg.device_status()
     if status != 0:
         raise SystemExit("a kernel reported device status %d" % status)
+    def leave():
+        # Every rank is between steps with nothing in flight (synchronised, then a barrier).  The
+        # process then ends without tearing the communicators down: their destructors are
+        # collective and gain nothing here.
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
     if rank != 0:
         if world > 1:
-            import torch.distributed as dist
-            dist.barrier()
-            job.close()
-            dist.destroy_process_group()
+            leave()
         return
 
     value = job.flops_total / (ms * 1e-3) / 1e12
@@ -779,7 +787,9 @@ def main():
                      "gemm_8192_cube": kernel_case("gemm", 8192, 8192, 8192, 6)}
             torch.cuda.empty_cache()
             for M_ in (16, 128):
-                cases = [kernel_case("gemm", M_, N_, K_, 20) for (N_, K_) in ((4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336))]
+                # the four layers, then q+k+v and gate+up as one product over the concatenated weights
+                cases = [kernel_case("gemm", M_, N_, K_, 20) for (N_, K_) in ((4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336),
+                                                                                (6144, 4096), (28672, 4096))]
                 cases.append(kernel_case("reorder", M_, 0, 4096, 20))
                 cases.append(kernel_case("reorder", M_, 0, 14336, 20))
                 extra["decode_m%d" % M_] = [{k: c[k] for k in ("kernel", "M", "N", "K", "us_per_launch", "achieved", "unit", "frac")}
@@ -792,10 +802,7 @@ def main():
                                "sample": r["sample"], "reorder_quant_gbs": r["reorder_gbs"]}
     print(json.dumps(out))
     if world > 1:
-        import torch.distributed as dist
-        dist.barrier()
-        job.close()
-        dist.destroy_process_group()
+        leave()
 
 
 if __name__ == "__main__":

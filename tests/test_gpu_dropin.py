@@ -72,3 +72,23 @@ def test_unknown_k_raises_runtime_error(mixedgemm):
     idx = torch.arange(128, dtype=torch.int16, device="cuda")
     with pytest.raises(RuntimeError):
         mixedgemm.reorder_quantize_x(X, idx, 64, 32, 64, 4, 4)
+
+
+def test_reference_smoke_script_runs_unmodified(mixedgemm, monkeypatch, capsys):
+    """The acceptance smoke of a drop-in: the reference project's own main.py, executed as it is
+    against this build of the `mixedgemm` module.  It needs a checkout of the reference, named by
+    the environment variable MIXEDGEMM_REFERENCE; without one the test is skipped (the sequence of
+    calls the script makes is covered by test_main_py_sequence either way)."""
+    import runpy
+    import time
+    ref = os.environ.get("MIXEDGEMM_REFERENCE", "")
+    script = os.path.join(ref, "main.py")
+    if not ref or not os.path.exists(script):
+        pytest.skip("MIXEDGEMM_REFERENCE does not name a checkout of the reference")
+    monkeypatch.setattr(time, "sleep", lambda s: None)  # the script pauses a second between its ten rounds
+    runpy.run_path(script, run_name="__main__")         # raises if any call into the module fails
+    torch.cuda.synchronize()
+    out = capsys.readouterr().out
+    assert "Hello from test_function!" in out or len(out) > 0
+    import mixedgemm_b200 as mg
+    assert mg.device_status() == 0
