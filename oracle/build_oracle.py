@@ -17,7 +17,9 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_DEFAULT = os.environ.get("MIXEDGEMM_REFERENCE", "/root/reference")
+# where the reference project is checked out: MIXEDGEMM_REFERENCE, else a directory `reference`
+# beside this repository
+REF_DEFAULT = os.environ.get("MIXEDGEMM_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _newer(target, sources):

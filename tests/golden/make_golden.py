@@ -2,8 +2,8 @@
 
   python tests/golden/make_golden.py
 
-Compiles gen_cutlass_tables.cpp with g++ against a CUTLASS header tree found in the
-Python packages of the authoring image and writes the JSON beside this script.  Only the
+Compiles gen_cutlass_tables.cpp with g++ against a CUTLASS header tree found inside the
+installed Python packages and writes the JSON beside this script.  Only the
 JSON is needed at test time.
 """
 import os

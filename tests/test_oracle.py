@@ -93,7 +93,7 @@ def test_c_equals_numpy(R, KN, KS, KO, weights):
 
 
 def test_config1_gaussian_with_outliers():
-    """BASELINE config 1 shapes/distribution: M=16, K=4096, 128 outlier channels x20."""
+    """The single-layer CPU configuration: M=16, K=4096, 128 outlier channels x20."""
     import torch
     g = torch.Generator().manual_seed(0)
     M, K, KN, KS, KO = 16, 4096, 2560, 1408, 128
