@@ -299,6 +299,10 @@ class Job:
 
     def gemm_group(self, gi, s=0):
         gr = self.groups[gi]
+        if self.ex is not None:  # the exchange's row-sharded buffers and its ready flags
+            self.mg.matmul_multi([(gr["A"][s], B, Y) for (_, _, B, Y) in gr["layers"]],
+                                 flags=[self.ex.ready(s, gi)] * len(gr["layers"]))
+            return
         self.mg.matmul_group(gr["A"][s], [B for (_, _, B, _) in gr["layers"]], outs=[Y for (_, _, _, Y) in gr["layers"]])
 
     def gemm_fused(self, s=0):

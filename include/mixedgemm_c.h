@@ -222,6 +222,12 @@ int mg_matmul_group_pitched(int nprob, const uint8_t* AN, const uint8_t* AS, con
  * only: a tile then waits for the flag of its own rows, not for all of them.  first_row (a
  * multiple of 256) is the row the problem's tile order starts with, wrapping around - the rows
  * that are there first, e.g. the ones this GPU quantised itself.
+ *
+ * a_shard_rows > 0 (a multiple of 128): the activation is stored in row shards - rows
+ * [i a_shard_rows, (i+1) a_shard_rows) of AN / AS / AO are contiguous at the row pitch, shard i + 1
+ * starts a_shard_stride[seg] bytes after shard i, and likewise the scale blocks with
+ * sfa_shard_stride[seg].  It is the layout in which a rank's rows of all six buffers can be one
+ * contiguous block, so that an exchange moves them with one copy per peer.
  */
 typedef struct mg_problem {
   const uint8_t *AN, *AS, *AO, *SFAN, *SFAS, *SFAO; /* activation, as written by mg_reorder_quantize_pitched */
@@ -237,6 +243,9 @@ typedef struct mg_problem {
   int ready_value;
   int ready_rows;
   int first_row;
+  int a_shard_rows;
+  size_t a_shard_stride[3];
+  size_t sfa_shard_stride[3];
 } mg_problem_t;
 int mg_matmul_multi(int nprob, const mg_problem_t* probs, void* stream);
 

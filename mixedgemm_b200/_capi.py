@@ -66,7 +66,9 @@ class Problem(ctypes.Structure):
                 [(n, _i) for n in ("M", "N", "KN", "KS", "KO")] + [("D_bf16", _vp), ("ldd", _i),
                                                                   ("ready_flags", _vp), ("ready_count", _i),
                                                                   ("ready_epoch", _vp), ("ready_value", _i),
-                                                                  ("ready_rows", _i), ("first_row", _i)])
+                                                                  ("ready_rows", _i), ("first_row", _i),
+                                                                  ("a_shard_rows", _i), ("a_shard_stride", _sz * 3),
+                                                                  ("sfa_shard_stride", _sz * 3)])
 
 
 _lib = None

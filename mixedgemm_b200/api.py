@@ -255,10 +255,38 @@ def matmul_group(A, Bs, outs=None):
     return outs
 
 
+class ShardedActivation:
+    """A quantised activation stored in row shards: `shards` = one (AN, AS, AO, SFAN, SFAS, SFAO) per
+    shard, every shard with the same (multiple of 128) row count and the same shapes, and every one of
+    the six tensors a constant number of bytes after its counterpart in the shard before
+    (mg_problem_t.a_shard_rows).  It is how a multi-GPU exchange lays the activation out, so that a
+    rank's rows of all six tensors are one contiguous block; matmul_multi takes it in place of A."""
+
+    def __init__(self, shards):
+        shards = [tuple(s) for s in shards]
+        if not shards or any(len(s) != 6 for s in shards):
+            raise RuntimeError("ShardedActivation: one six-tuple per shard")
+        first = shards[0]
+        rows = first[0].size(0)
+        if len(shards) > 1 and rows % 128 != 0:
+            raise RuntimeError("ShardedActivation: shards must be whole 128-row scale blocks")
+        self.stride = [0] * 6
+        for i in range(6):
+            step = shards[1][i].data_ptr() - first[i].data_ptr() if len(shards) > 1 else 0
+            for j, s in enumerate(shards):
+                if (s[i].shape != first[i].shape or s[i].stride() != first[i].stride() or s[i].dtype != first[i].dtype
+                        or s[i].device != first[i].device or s[i].data_ptr() != first[i].data_ptr() + j * step):
+                    raise RuntimeError("ShardedActivation: shards must be equal and equally spaced in memory")
+            self.stride[i] = step
+        if len(shards) > 1 and any(self.stride[i] <= 0 for i in range(6) if first[i].numel()):
+            raise RuntimeError("ShardedActivation: shards must follow one another in memory")
+        self.shards, self.shard_rows, self.rows = shards, rows, rows * len(shards)
+
+
 def matmul_multi(problems, flags=None):
     """One launch for a list of independent products (up to 8): problems = [(A, B, out), ...] with
-    A = (AN, AS, AO, SFAN, SFAS, SFAO), B likewise for the weights, out a [M, N] bf16 tensor or None.
-    Each problem has its own activation and K split, unlike matmul_group.  `flags` (optional) gives
+    A = (AN, AS, AO, SFAN, SFAS, SFAO) or a ShardedActivation, B likewise for the weights, out a
+    [M, N] bf16 tensor or None.  Each problem has its own activation and K split, unlike matmul_group.  `flags` (optional) gives
     per problem None or (int32 CUDA tensor, value or int32 CUDA tensor holding the value[, rows per flag, first row]): the kernel
     reads that problem's activation only once every flag has reached the value
     (mg_problem_t.ready_flags).  Problems the
@@ -269,9 +297,13 @@ def matmul_multi(problems, flags=None):
     n = len(problems)
     outs = []
     arr = (_capi.Problem * max(n, 1))()
+    sharded = [A if isinstance(A, ShardedActivation) else None for A, _, _ in problems]
+    problems = [(A.shards[0] if isinstance(A, ShardedActivation) else A, B, out) for A, B, out in problems]
     dev = problems[0][0][0].device
     for j, (A, B, out) in enumerate(problems):
         M, N, KN, KS, KO = _check_operands(A, B, "matmul_multi")
+        if sharded[j] is not None and len(sharded[j].shards) > 1:
+            M = sharded[j].rows
         if out is None:
             out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
         if out.dtype != torch.bfloat16 or tuple(out.shape) != (M, N) or out.stride(1) != 1 or out.device != dev:
@@ -287,6 +319,11 @@ def matmul_multi(problems, flags=None):
             q.pitch_b[i] = B[i].stride(0) if B[i].size(1) else 0
         q.M, q.N, q.KN, q.KS, q.KO = M, N, KN, KS, KO
         q.D_bf16, q.ldd = _ptr(out), out.stride(0)
+        if sharded[j] is not None and len(sharded[j].shards) > 1:
+            q.a_shard_rows = sharded[j].shard_rows
+            for i in range(3):
+                q.a_shard_stride[i] = sharded[j].stride[i]
+                q.sfa_shard_stride[i] = sharded[j].stride[3 + i]
         f = flags[j] if flags is not None else None
         if f is not None:
             ft, fv = f[0], f[1]
@@ -304,8 +341,8 @@ def matmul_multi(problems, flags=None):
         with torch.cuda.device(dev):
             st = lib.mg_matmul_multi(n, ctypes.cast(arr, ctypes.c_void_p), _stream())
     if st in (1, 3):  # a shape or pitch the grouped kernel does not take
-        if flags is not None and any(f is not None for f in flags):
-            raise RuntimeError("matmul_multi: ready flags need problems the CTA-pair kernel takes")
+        if (flags is not None and any(f is not None for f in flags)) or any(a is not None and len(a.shards) > 1 for a in sharded):
+            raise RuntimeError("matmul_multi: ready flags and row-sharded activations need problems the CTA-pair kernel takes")
         for (A, B, _), o in zip(problems, outs):
             matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5], out=o)
     else:

@@ -74,44 +74,45 @@ struct GemmParams {
   float* sp_partials;  // [split][tile][column group of 4][sp_rows][4]
 };
 
-// Bounded mbarrier wait.  Control flow stays warp-uniform: when the limit expires the lane
-// records `code`, raises the CTA's stop flag and returns; from then on every wait of the CTA
-// returns at once, the loops run out (their results are garbage and are not stored) and
-// the kernel ends normally.
-__device__ __forceinline__ void wait_parity(uint32_t bar, uint32_t parity, volatile int* stop, int* status,
+// Bounded mbarrier wait: true once the phase has completed.  When the limit expires the lane
+// records `code`, raises the CTA's stop flag and returns false; from then on every wait of the CTA
+// that does not find its phase complete at the first probe returns false at once.  A role whose
+// wait failed issues nothing more (no copies, no MMAs, no arrivals) and leaves its loops; the
+// kernel then ends normally, with nothing stored.
+__device__ __forceinline__ bool wait_parity(uint32_t bar, uint32_t parity, volatile int* stop, int* status,
                                             long long limit, int code) {
-  if (ptx::mbar_try_wait(bar, parity)) return;
+  if (ptx::mbar_try_wait(bar, parity)) return true;
   long long t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
-    if (ptx::mbar_try_wait(bar, parity)) return;
+    if (ptx::mbar_try_wait(bar, parity)) return true;
     if ((spin & 63u) == 0) {
-      if (*stop) return;
+      if (*stop) return false;
       const long long now = clock64();
       if (spin == 0) t0 = now;
       if (now - t0 > limit) {
         *stop = 1;
         atomicOr(status, code);
-        return;
+        return false;
       }
     }
   }
 }
 
 // The same for a barrier whose phase is completed by other CTAs of the cluster.
-__device__ __forceinline__ void wait_parity_cluster(uint32_t bar, uint32_t parity, volatile int* stop, int* status,
+__device__ __forceinline__ bool wait_parity_cluster(uint32_t bar, uint32_t parity, volatile int* stop, int* status,
                                                     long long limit, int code) {
-  if (ptx::mbar_try_wait_cluster(bar, parity)) return;
+  if (ptx::mbar_try_wait_cluster(bar, parity)) return true;
   long long t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
-    if (ptx::mbar_try_wait_cluster(bar, parity)) return;
+    if (ptx::mbar_try_wait_cluster(bar, parity)) return true;
     if ((spin & 63u) == 0) {
-      if (*stop) return;
+      if (*stop) return false;
       const long long now = clock64();
       if (spin == 0) t0 = now;
       if (now - t0 > limit) {
         *stop = 1;
         atomicOr(status, code);
-        return;
+        return false;
       }
     }
   }
@@ -238,13 +239,14 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
     int stage = 0;
     uint32_t phase = 0;
     int skip_countdown = p.skip_load;
-    for (int w = blockIdx.x; w < total_items; w += gridDim.x) {
+    bool live = true;  // false once a wait of this role has failed: nothing more is issued
+    for (int w = blockIdx.x; w < total_items && live; w += gridDim.x) {
       const int t = w / splits, split = w - t * splits;
       const int u0 = S_units * split / splits, u1 = S_units * (split + 1) / splits;
       int m_tile, n_tile;
       raster(t, p.tiles_m, p.tiles_n, m_tile, n_tile);
 #pragma unroll 1
-      for (int seg = 0; seg < 3; ++seg) {
+      for (int seg = 0; seg < 3 && live; ++seg) {
         const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
         const CUtensorMap* ta = seg == 0 ? &tmA0 : (seg == 1 ? &tmA1 : &tmA2);
         const CUtensorMap* tb = seg == 0 ? &tmB0 : (seg == 1 ? &tmB1 : &tmB2);
@@ -256,7 +258,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
         const int s_lo = max(u0 - so, 0), s_hi = min(u1 - so, sp.nstages);
 #pragma unroll 1
         for (int s = s_lo; s < s_hi; ++s) {
-          wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, p.wait_cycles, 1);
+          if (!wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, p.wait_cycles, 1)) { live = false; break; }
           const int atom0 = seg == 0 ? 2 * s : s;
           const int natoms = seg == 0 ? min(2, sp.katoms - atom0) : 1;
           const uint32_t sbase = base + stage * C::STAGE_BYTES;
@@ -290,24 +292,25 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
     int stage = 0;
     uint32_t phase = 0, slot = 0;
     int it = 0;
-    for (int w = blockIdx.x; w < total_items; w += gridDim.x, ++it) {
+    bool live = true;
+    for (int w = blockIdx.x; w < total_items && live; w += gridDim.x, ++it) {
       const int split = w % splits;
       const int u0 = S_units * split / splits, u1 = S_units * (split + 1) / splits;
       const int acc = it % C::ACC;
       const uint32_t acc_phase = (uint32_t)(it / C::ACC) & 1u;
-      wait_parity(tempty_bar(acc), acc_phase ^ 1u, stop, p.status, p.wait_cycles, 4);
+      if (!wait_parity(tempty_bar(acc), acc_phase ^ 1u, stop, p.status, p.wait_cycles, 4)) break;
       ptx::tc_fence_after();
       const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
       uint32_t accumulate = 0;
 #pragma unroll 1
-      for (int seg = 0; seg < 3; ++seg) {
+      for (int seg = 0; seg < 3 && live; ++seg) {
         const SegParams sp = seg == 0 ? p.seg[0] : (seg == 1 ? p.seg[1] : p.seg[2]);
         const uint32_t id0 = seg == 0 ? kIdesc[0] : (seg == 1 ? kIdesc[1] : kIdesc[2]);
         const int so = seg == 0 ? 0 : (seg == 1 ? seg_off1 : seg_off2);
         const int s_lo = max(u0 - so, 0), s_hi = min(u1 - so, sp.nstages);
 #pragma unroll 1
         for (int s = s_lo; s < s_hi; ++s) {
-          wait_parity(full_bar(stage), phase, stop, p.status, p.wait_cycles, 2);
+          if (!wait_parity(full_bar(stage), phase, stop, p.status, p.wait_cycles, 2)) { live = false; break; }
           ptx::tc_fence_after();
           const uint32_t sbase = base + stage * C::STAGE_BYTES;
           const uint32_t sfa_lo = ptx::desc_lo(sbase + C::A_BYTES + C::B_BYTES);
@@ -356,7 +359,7 @@ mixed_gemm_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmA0,
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
-      if (leader) ptx::tc_commit(tfull_bar(acc));
+      if (leader && live) ptx::tc_commit(tfull_bar(acc));
     }
   } else {
     // ------------------------------------------------------------ epilogue (4 warps)
@@ -628,6 +631,13 @@ struct PairProb {
   int flag_count;
   const int* flag_epoch;
   int flag_value;
+  // The activation may be stored in row shards (what a multi-GPU exchange fills shard by shard with
+  // one copy each): rows [i * shard_rows, (i+1) * shard_rows) of every code buffer are contiguous
+  // at the row pitch, consecutive shards lie `shard stride` bytes apart (part of the tensor map),
+  // and the scale blocks of shard i start sf_shard_stride[seg] bytes after those of shard i - 1.
+  // Unsharded: shard_rows >= M.
+  int shard_rows;
+  uint32_t sf_shard_stride[3];
   int flag_rows;  // > 0: flag i covers rows [i * flag_rows, (i + 1) * flag_rows) and a tile waits only for its own rows' flag
   int m_rot;      // 256-row block the problem's tile order starts with (the blocks whose rows are there first)
 };
@@ -736,7 +746,8 @@ mixed_gemm_pair_kernel(const __grid_constant__ PairParams p, const __grid_consta
     uint32_t phase = 0;
     int flag_prob = -1;      // problem the mask below belongs to
     uint32_t flag_mask = 0;  // its flags that have been seen up
-    for (int t = first_tile; t < total_tiles; t += tile_step) {
+    bool live = true;        // false once a wait of this role has failed: nothing more is issued
+    for (int t = first_tile; t < total_tiles && live; t += tile_step) {
       int prob, m_pt, n_tile;
       locate(t, prob, m_pt, n_tile);
       const PairProb& pp = p.prob[prob];
@@ -757,41 +768,48 @@ mixed_gemm_pair_kernel(const __grid_constant__ PairParams p, const __grid_consta
           for (;;) {
             int v;
             asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(pp.flag + f) : "memory");
-            if (v - target >= 0 || *stop) break;
+            if (v - target >= 0) break;
+            if (*stop) { live = false; break; }
             __nanosleep(200);
             if (clock64() - t0 > wait_limit) {
               *stop = 1;
               atomicOr(p.status, 1024);
             }
           }
+          if (!live) break;
           flag_mask |= 1u << (f & 31);
           waited = true;
         }
+        if (!live) break;
         if (waited) asm volatile("fence.proxy.async.global;" ::: "memory");
       }
       const int m_row0 = m_pt * 256 + (int)rank * 128, n_row0 = n_tile * 256 + (int)rank * 128;
+      // this CTA's 128 rows inside their shard (the map is 3-D: byte, row of the shard, shard), and
+      // their scale blocks; a CTA whose 128 rows lie wholly beyond M reads the last real row
+      // block's scales (its accumulator rows are never stored), so that no copy leaves the buffer
+      const int a_shard = m_row0 / pp.shard_rows, a_row = m_row0 - a_shard * pp.shard_rows;
+      const int row_blk = min(m_pt * 2 + (int)rank, (pp.M + 127) / 128 - 1);
+      const int sf_shard = (row_blk * 128) / pp.shard_rows, sf_blk = row_blk - sf_shard * (pp.shard_rows >> 7);
 #pragma unroll 1
-      for (int seg = 0; seg < 3; ++seg) {
+      for (int seg = 0; seg < 3 && live; ++seg) {
         const SegParams sp = seg == 0 ? pp.seg[0] : (seg == 1 ? pp.seg[1] : pp.seg[2]);
         const CUtensorMap* ta = &gm.a[prob][seg];
         const CUtensorMap* tb = &gm.b[prob][seg];
         const uint32_t tx_ab = seg == 0 ? p.tx_a[0] + p.tx_b[0]
                                         : (seg == 1 ? p.tx_a[1] + p.tx_b[1] : p.tx_a[2] + p.tx_b[2]);
-        // a CTA whose 128 rows lie wholly beyond M reads the last real row block's scales (its
-        // accumulator rows are never stored), so that no copy leaves the scale buffer
-        const int row_blk = min(m_pt * 2 + (int)rank, (pp.M + 127) / 128 - 1);
-        const uint8_t* sfa_row = sp.sfa + (size_t)row_blk * sp.katoms * 512;
+        const uint32_t sf_stride = seg == 0 ? pp.sf_shard_stride[0] : (seg == 1 ? pp.sf_shard_stride[1] : pp.sf_shard_stride[2]);
+        const uint8_t* sfa_row = sp.sfa + (size_t)sf_shard * sf_stride + (size_t)sf_blk * sp.katoms * 512;
         const uint8_t* sfb_row = sp.sfb + (size_t)(n_tile * 2) * sp.katoms * 512;
 #pragma unroll 1
         for (int s = 0; s < sp.nstages; ++s) {
-          wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, wait_limit, 1);
+          if (!wait_parity(empty_bar(stage), phase ^ 1u, stop, p.status, wait_limit, 1)) { live = false; break; }
           const int atom0 = seg == 0 ? 2 * s : s;
           const int natoms = seg == 0 ? min(2, sp.katoms - atom0) : 1;
           const uint32_t sbase = ring + stage * C::STAGE_BYTES;
           const uint32_t fb = full_bar(stage);
           if (leader) {
             ptx::mbar_expect_tx(fb, tx_ab + (uint32_t)natoms * 512u * 3u);
-            ptx::tma_load_2d(sbase, ta, s * 128, m_row0, fb);
+            ptx::tma_load_3d(sbase, ta, s * 128, a_row, a_shard, fb);
             ptx::tma_load_2d(sbase + C::A_BYTES, tb, s * 128, n_row0, fb);
             ptx::bulk_load_1d(sbase + C::A_BYTES + C::B_BYTES, sfa_row + (size_t)atom0 * 512, natoms * 512, fb);
 #pragma unroll
@@ -807,13 +825,14 @@ mixed_gemm_pair_kernel(const __grid_constant__ PairParams p, const __grid_consta
     // ------------------------------------------------------------ relay: stage landed -> leader's ready barrier
     int stage = 0;
     uint32_t phase = 0;
-    for (int t = first_tile; t < total_tiles; t += tile_step) {
+    bool live = true;
+    for (int t = first_tile; t < total_tiles && live; t += tile_step) {
       int prob, m_pt, n_tile;
       locate(t, prob, m_pt, n_tile);
       const int s_units = p.prob[prob].s_units;
 #pragma unroll 1
       for (int s = 0; s < s_units; ++s) {
-        wait_parity(full_bar(stage), phase, stop, p.status, wait_limit, 64);
+        if (!wait_parity(full_bar(stage), phase, stop, p.status, wait_limit, 64)) { live = false; break; }
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ready_bar(stage), 0));
         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -830,21 +849,22 @@ mixed_gemm_pair_kernel(const __grid_constant__ PairParams p, const __grid_consta
       int stage = 0;
       uint32_t phase = 0, slot = 0;
       int it = 0;
-      for (int t = first_tile; t < total_tiles; t += tile_step, ++it) {
+      bool live = true;
+      for (int t = first_tile; t < total_tiles && live; t += tile_step, ++it) {
         int prob, m_pt, n_tile;
         locate(t, prob, m_pt, n_tile);
         const PairProb& pp = p.prob[prob];
-        wait_parity(tempty_bar, ((uint32_t)it & 1u) ^ 1u, stop, p.status, wait_limit, 4);
+        if (!wait_parity(tempty_bar, ((uint32_t)it & 1u) ^ 1u, stop, p.status, wait_limit, 4)) break;
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base;
         uint32_t accumulate = 0;
 #pragma unroll 1
-        for (int seg = 0; seg < 3; ++seg) {
+        for (int seg = 0; seg < 3 && live; ++seg) {
           const SegParams sp = seg == 0 ? pp.seg[0] : (seg == 1 ? pp.seg[1] : pp.seg[2]);
           const uint32_t id0 = seg == 0 ? kIdesc[0] : (seg == 1 ? kIdesc[1] : kIdesc[2]);
 #pragma unroll 1
           for (int s = 0; s < sp.nstages; ++s) {
-            wait_parity(ready_bar(stage), phase, stop, p.status, wait_limit, 2);
+            if (!wait_parity(ready_bar(stage), phase, stop, p.status, wait_limit, 2)) { live = false; break; }
             ptx::tc_fence_after();
             const uint32_t sbase = ring + stage * C::STAGE_BYTES;
             const uint32_t sfa_lo = ptx::desc_lo(sbase + C::A_BYTES + C::B_BYTES);
@@ -890,7 +910,7 @@ mixed_gemm_pair_kernel(const __grid_constant__ PairParams p, const __grid_consta
             if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
           }
         }
-        if (leader) ptx::tc_commit_pair(tfull_bar, 3);  // accumulators of both CTAs are complete
+        if (leader && live) ptx::tc_commit_pair(tfull_bar, 3);  // accumulators of both CTAs are complete
       }
     }
   } else {
@@ -953,9 +973,14 @@ mixed_gemm_pair_kernel(const __grid_constant__ PairParams p, const __grid_consta
 
   // ------------------------------------------------------------ teardown
   ptx::tc_fence_before();
+  // A CTA that gave up tells its peer (which is still here: it cannot pass the barrier below before
+  // this CTA arrives), so that both take the same path through the second barrier.
+  __syncthreads();
+  if (threadIdx.x == 0 && *stop) ptx::st_cluster_u32(ptx::map_to_cta(ptx::smem_u32(const_cast<int*>(stop)), rank ^ 1u), 1u);
   ptx::cluster_sync();
   ptx::tc_fence_after();
   if (*stop) {
+    // give copies and MMAs that are still in flight time to land before either CTA goes away
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
     ptx::cluster_sync();
   }
@@ -1011,6 +1036,26 @@ int make_map(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, uint64_t k
   cuuint32_t box[2] = {box_k, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    mg::note_cuda_error(cudaErrorInvalidValue);
+    return MG_ERR_CUDA;
+  }
+  return MG_OK;
+}
+
+// 3-D K-major operand stored in row shards: `kdim` elements per row, `shard_rows` rows `pitch` bytes
+// apart per shard, `nshards` shards `shard_stride` bytes apart.  One shard describes a plain 2-D operand.
+int make_map3(CUtensorMap* m, CUtensorMapDataType dt, const void* ptr, uint64_t kdim, uint64_t shard_rows,
+              uint64_t nshards, uint64_t pitch, uint64_t shard_stride, uint32_t box_k, uint32_t box_rows) {
+  PFN_cuTensorMapEncodeTiled_v12000 enc;
+  if (get_encoder(&enc) != MG_OK) return MG_ERR_CUDA;
+  cuuint64_t dims[3] = {kdim, shard_rows, nshards};
+  cuuint64_t strides[2] = {pitch, shard_stride};
+  cuuint32_t box[3] = {box_k, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -1221,6 +1266,9 @@ struct PairProblem {
   int flag_value;
   int flag_rows;
   int first_row;
+  int shard_rows;              // 0: the activation is one block of M rows
+  size_t a_shard_stride[3];    // bytes between consecutive shards of AN / AS / AO
+  size_t sfa_shard_stride[3];  // and of their scale buffers
 };
 
 // Validates the problems, builds their tensor maps and launches the CTA-pair kernel once.
@@ -1252,7 +1300,15 @@ int launch_pair(int nprob, const PairProblem* pr, int sms, cudaStream_t st) {
       const uint64_t kd = sg == 0 ? q.KN / 2 : (sg == 1 ? pl.ksp : pl.kop);
       const CUtensorMapDataType da = sg == 1 ? CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
       const CUtensorMapDataType db = sg == 0 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B;
-      if ((rc = make_map(&gm.a[j][seg], da, q.a[sg], kd, q.M, pl.pitch[sg * 2], 128, BM))) return rc;
+      const int srows = q.shard_rows > 0 ? q.shard_rows : q.M;
+      const int nshards = (q.M + srows - 1) / srows;
+      if (nshards > 1) {
+        if (srows % 128 || q.M % srows || q.a_shard_stride[sg] % 32 || q.sfa_shard_stride[sg] % 16 || q.sfa_shard_stride[sg] > 0xffffffffull ||
+            q.a_shard_stride[sg] < (size_t)srows * pl.pitch[sg * 2])
+          return MG_ERR_SHAPE;
+      }
+      const uint64_t sstride = nshards > 1 ? q.a_shard_stride[sg] : (uint64_t)align_up((size_t)srows * pl.pitch[sg * 2], 32);
+      if ((rc = make_map3(&gm.a[j][seg], da, q.a[sg], kd, srows, nshards, pl.pitch[sg * 2], sstride, 128, BM))) return rc;
       if ((rc = make_map(&gm.b[j][seg], db, q.b[sg], kd, q.N, pl.pitch[sg * 2 + 1], 128, 128))) return rc;
     }
     if ((rc = make_map(&gm.d[j], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, q.D, q.N, q.M, (uint64_t)q.ldd * 2, 64, 128))) return rc;
@@ -1261,6 +1317,8 @@ int launch_pair(int nprob, const PairProblem* pr, int sms, cudaStream_t st) {
     d.seg[1] = {q.KS, (q.KS + 127) / 128, (q.KS + 127) / 128, q.sfa[1], q.sfb[1]};
     d.seg[2] = {q.KO, (q.KO + 127) / 128, (q.KO + 127) / 128, q.sfa[2], q.sfb[2]};
     d.M = q.M;
+    d.shard_rows = q.shard_rows > 0 && q.shard_rows < q.M ? q.shard_rows : ((q.M + 127) / 128) * 128;
+    for (int seg = 0; seg < 3; ++seg) d.sf_shard_stride[seg] = (uint32_t)q.sfa_shard_stride[seg];
     d.tiles_m2 = (q.M + 255) / 256;
     tiles += d.tiles_m2 * (q.N / 256);
     d.tile_end = tiles;
@@ -1576,6 +1634,8 @@ extern "C" int mg_matmul_multi(int nprob, const mg_problem_t* probs, void* strea
     q.D = s.D_bf16; q.ldd = s.ldd;
     q.flag = s.ready_flags; q.flag_count = s.ready_count; q.flag_epoch = s.ready_epoch; q.flag_value = s.ready_value;
     q.flag_rows = s.ready_rows; q.first_row = s.first_row;
+    q.shard_rows = s.a_shard_rows;
+    for (int i = 0; i < 3; ++i) { q.a_shard_stride[i] = s.a_shard_stride[i]; q.sfa_shard_stride[i] = s.sfa_shard_stride[i]; }
   }
   return launch_pair(nprob, pr, di.sm_count, static_cast<cudaStream_t>(stream));
 }

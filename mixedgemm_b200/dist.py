@@ -8,9 +8,9 @@ gathers them.  The transfers are made by the C ABI (include/mixedgemm_c.h, csrc/
   Communicator   NCCL collectives through mg_dist_* / mg_bcast_activations / mg_allgather_*:
                  "quantise once, broadcast", or "quantise M/P rows each, all-gather"
   PushExchange   the overlapped exchange: every rank quantises M/P rows in place in its own
-                 full-size buffer and pushes them into every peer's buffer with copy-engine
-                 copies over NVLink (mg_push_shard); the GEMM is launched at once and waits,
-                 row shard by row shard, for the flags that follow the data
+                 full-size buffer and pushes them into every peer's buffer with one copy-engine
+                 copy per peer over NVLink (mg_push_shard); the GEMM is launched at once and
+                 waits, row shard by row shard, for the flags that follow the data
 
 The only thing the host framework (torch.distributed) is used for is handing small byte strings
 from rank to rank at set-up time: the NCCL id and the IPC handles of the exchange buffers.
@@ -171,10 +171,14 @@ class PushExchange:
     """Exchange buffers for `n_sets` x len(shapes) quantised activations (shapes = [(M, (KN, KS, KO)), ...];
     n_sets = 2 lets consecutive steps alternate, which they must: a rank may start pushing the next
     step while a slower peer still multiplies the current one).  Every buffer is one device
-    allocation that holds the six row-pitched tensors of alloc_quantized_x plus `world` flag words,
-    laid out identically on every rank and opened on every other rank through CUDA IPC."""
+    allocation, laid out identically on every rank and opened on every other rank through CUDA IPC.
+    It is stored shard by shard: the M/P rows that rank r quantises - three code tensors at their row
+    pitch, then their three scale tensors - form ONE contiguous block, so that a push is one large
+    copy per peer (small copies reach a fraction of the NVLink rate), followed by `world` flag words.
+    The GEMM reads that layout in place (api.ShardedActivation)."""
 
     def __init__(self, shapes, world, rank, device, n_sets=2, group=None):
+        from .api import ShardedActivation
         self.lib = lib = _capi.load()
         self.world, self.rank, self.device = world, rank, device
         self.shapes = list(shapes)
@@ -188,35 +192,36 @@ class PushExchange:
                 for (M, split) in self.shapes:
                     if M % (256 * world) != 0:
                         raise ValueError("M = %d must split into %d shards of whole 256-row blocks" % (M, world))
+                    mp = M // world
                     logical = (split[0] // 2, split[1] // 4 * 3, split[2])
                     pitch = [lib.mg_code_pitch(0, i, k) for i, k in enumerate(split)]
-                    sizes = [M * p for p in pitch] + [lib.mg_sf_bytes(M, k) for k in split]
+                    sizes = [mp * p for p in pitch] + [lib.mg_sf_bytes(mp, k) for k in split]
                     offs, off = [], 0
                     for n in sizes:
                         offs.append(off)
-                        off += _align(max(n, 1))
-                    flag_off = off
-                    total = off + _align(4 * world)
+                        off += _align(n)
+                    shard_bytes = off
+                    flag_off = world * shard_bytes
+                    total = flag_off + _align(4 * world)
                     ptr = ctypes.c_void_p()
                     _capi.check(lib.mg_xbuf_alloc(ctypes.byref(ptr), total), "mg_xbuf_alloc")
                     h = ctypes.create_string_buffer(64)
                     _capi.check(lib.mg_ipc_export(ptr, h), "mg_ipc_export")
                     handles.append(h.raw)
                     flat = torch.as_tensor(_Raw(ptr.value, total), device=device)
-                    A = []
-                    for i in range(3):
-                        v = flat[offs[i]:offs[i] + sizes[i]].view(M, pitch[i])
-                        A.append(v[:, :logical[i]] if pitch[i] != logical[i] else v)
-                    for i in range(3):
-                        A.append(flat[offs[3 + i]:offs[3 + i] + sizes[3 + i]])
+                    shards = []
+                    for r in range(world):
+                        blk = flat[r * shard_bytes:(r + 1) * shard_bytes]
+                        A = []
+                        for i in range(3):
+                            v = blk[offs[i]:offs[i] + sizes[i]].view(mp, pitch[i])
+                            A.append(v[:, :logical[i]] if pitch[i] != logical[i] else v)
+                        for i in range(3):
+                            A.append(blk[offs[3 + i]:offs[3 + i] + sizes[3 + i]])
+                        shards.append(tuple(A))
                     flags = flat[flag_off:flag_off + 4 * world].view(torch.int32)
-                    mp = M // world
-                    segs = [(offs[i] + rank * mp * pitch[i], mp * pitch[i]) for i in range(3)]
-                    for i, k in enumerate(split):
-                        per_block = ((k + 127) // 128) * 512
-                        segs.append((offs[3 + i] + (rank * mp // 128) * per_block, (mp // 128) * per_block))
-                    bufs.append(dict(ptr=ptr, A=tuple(A), flags=flags, flag_off=flag_off, segs=segs, M=M, split=split,
-                                     bases=None, flat=flat))
+                    bufs.append(dict(ptr=ptr, A=ShardedActivation(shards), flags=flags, flag_off=flag_off,
+                                     segs=[(rank * shard_bytes, shard_bytes)], M=M, split=split, bases=None, flat=flat))
                 self.sets.append(bufs)
         # every rank opens every other rank's buffers
         self._imported = []
@@ -238,13 +243,13 @@ class PushExchange:
                 k += 1
 
     def buffers(self, set_index, i):
-        """The six tensors (alloc_quantized_x layout) of activation i in set `set_index`."""
+        """Activation i of set `set_index` as the api.ShardedActivation that matmul_multi takes."""
         return self.sets[set_index][i]["A"]
 
-    def shard(self, set_index, i):
-        """Views of this rank's M/P rows of activation i: what its quantiser writes."""
-        b = self.sets[set_index][i]
-        return activation_shard(b["A"], b["M"], b["split"], self.world, self.rank)
+    def shard(self, set_index, i, rank=None):
+        """The six tensors of this rank's (or `rank`'s) M/P rows of activation i: what its quantiser
+        writes (`out=` of reorder_quantize_x)."""
+        return self.sets[set_index][i]["A"].shards[self.rank if rank is None else rank]
 
     def begin_step(self):
         """Once per step, before the quantisers: the value the flags of this step will carry."""

@@ -543,6 +543,60 @@ def test_multi_problem_launch_equals_separate_calls(mgopt):
     assert torch.equal(outs[1].view(torch.int16), mg.matmul(*_abargs(A, B)).view(torch.int16))
 
 
+def test_row_sharded_activation_equals_the_contiguous_one(mgopt):
+    """The layout a multi-GPU exchange fills (every shard's codes and scales in one contiguous block,
+    shards equally spaced) multiplies to the bytes of the plain layout: shard counts 2, 4 and 8, an M
+    whose last tile pair is half empty, a shard smaller than a tile pair, and a second, plain problem
+    in the same launch."""
+    import mixedgemm_b200 as mg
+    from mixedgemm_b200 import _capi
+    lib = _capi.load()
+    mgopt.setenv("MG_GEMM_CSPLIT", "0")
+    mgopt.setenv("MG_GEMM_SPLITK", "0")
+    for (M, N, split, world) in [(512, 512, (1280, 640, 128), 2), (1024, 256, (2560, 1408, 128), 4),
+                                 (1024, 512, (1280, 640, 128), 8), (384, 256, (256, 128, 128), 3),
+                                 (2048, 768, (3584, 0, 512), 2)]:
+        K = sum(split)
+        A, B = _quantise(M, N, K, split, seed=90 + world)
+        want = mg.matmul(*_abargs(A, B))
+        mp = M // world
+        pitch = [lib.mg_code_pitch(0, i, k) for i, k in enumerate(split)]
+        logical = (split[0] // 2, split[1] // 4 * 3, split[2])
+        sizes = [mp * p for p in pitch] + [lib.mg_sf_bytes(mp, k) for k in split]
+        offs, off = [], 0
+        for n in sizes:
+            offs.append(off)
+            off += (n + 1023) // 1024 * 1024
+        flat = torch.full((world * off + 1024,), 0x5A, dtype=torch.uint8, device="cuda")
+        flat = flat[(-flat.data_ptr()) % 1024:]
+        shards = []
+        for r in range(world):
+            blk = flat[r * off:(r + 1) * off]
+            part = []
+            for i in range(3):
+                v = blk[offs[i]:offs[i] + sizes[i]].view(mp, pitch[i])[:, :logical[i]]
+                v.copy_(A[i][r * mp:(r + 1) * mp])
+                part.append(v)
+            for i, k in enumerate(split):
+                per_block = ((k + 127) // 128) * 512
+                v = blk[offs[3 + i]:offs[3 + i] + sizes[3 + i]]
+                v.copy_(A[3 + i][(r * mp // 128) * per_block:((r + 1) * mp // 128) * per_block])
+                part.append(v)
+            shards.append(tuple(part))
+        SA = mg.ShardedActivation(shards)
+        assert SA.rows == M and SA.shard_rows == mp
+        other = _quantise(300, 256, K, split, seed=95)
+        outs = mg.matmul_multi([(SA, B, None), (other[0], other[1], None)])
+        torch.cuda.synchronize()
+        assert mg.device_status() == 0
+        assert torch.equal(outs[0].view(torch.int16), want.view(torch.int16)), (M, N, split, world)
+        assert torch.equal(outs[1].view(torch.int16), mg.matmul(*_abargs(*other)).view(torch.int16))
+    with pytest.raises(RuntimeError):
+        mg.ShardedActivation([shards[1], shards[0]])       # not in memory order
+    with pytest.raises(RuntimeError):
+        mg.ShardedActivation([shards[0], tuple(t[:64] if t.dim() == 2 else t for t in shards[1])])
+
+
 def test_ready_flag_holds_a_problem_back_until_its_activation_is_there(mgopt):
     """A problem with a ready flag is not read before the flag reaches its value: the activation is
     filled, and the flag raised, by copy-engine copies on another stream AFTER the launch."""
@@ -615,7 +669,24 @@ def test_bounded_waits_run_out_and_the_context_survives(mgopt):
     torch.cuda.synchronize()
     assert mg.device_status() & 1024
     assert torch.all(out2 == 7.0)
+    # the same in a launch of many tiles per CTA pair and two problems: the roles stop issuing at once
+    # instead of running through the remaining tiles, so nothing is in flight when the CTAs leave
+    M3, N3, split3 = 2048, 6144, (1280, 640, 128)
+    A3, B3 = _quantise(M3, N3, sum(split3), split3, seed=82)
+    out3 = [torch.full((M3, N3), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    flags3 = torch.zeros(4, dtype=torch.int32, device="cuda")
+    flags3[:2] = 1                                       # rows 0..1023 are "there", the rest never comes
+    mg.matmul_multi([(A3, B3, out3[0]), (A3, B3, out3[1])], flags=[None, (flags3, 1, 512, 0)])
+    torch.cuda.synchronize()
+    assert mg.device_status() & 1024
     mg.set_wait_limit_us(0)
+    flags3.fill_(1)
+    mg.matmul_multi([(A3, B3, out3[0]), (A3, B3, out3[1])], flags=[None, (flags3, 1, 512, 0)])
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    want3 = mg.matmul(*_abargs(A3, B3))
+    assert torch.equal(out3[0].view(torch.int16), want3.view(torch.int16))
+    assert torch.equal(out3[1].view(torch.int16), want3.view(torch.int16))
     flag.fill_(1)
     mg.matmul_multi([(A2, B2, out2)], flags=[(flag, 1)])
     torch.cuda.synchronize()
