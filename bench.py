@@ -196,7 +196,7 @@ class Job:
     output buffers, and - on several GPUs - the exchange that brings every rank the whole
     quantised activation."""
 
-    def __init__(self, wl_name, rank, world, device, exchange, fused=True):
+    def __init__(self, wl_name, rank, world, device, exchange, fused=True, pipeline=True):
         import mixedgemm_b200 as mg
         self.mg = mg
         wl = WORKLOADS[wl_name]
@@ -248,13 +248,17 @@ class Job:
                                                                          for (_, Nl, _, _) in self.groups[i]["layers"]))
         self.nsets = 1
         self.ex = self.comm = None
+        # push: the quantise + push of step i + 1 is issued before the GEMM of step i, so that the
+        # transfer runs under a GEMM that already has its data (steps are independent batches)
+        self.pipeline = pipeline and self.exchange == "push"
+        self.primed = False
         if self.exchange == "push":
             from mixedgemm_b200 import dist as mgd
-            # two buffer sets used in turn: a rank may push the next step while a peer still multiplies this one
-            self.nsets = 2
-            self.ex = mgd.PushExchange([(M, gr["split"]) for gr in self.groups], world, rank, device, n_sets=2)
+            # buffer sets used in turn: a rank may push a later step while a peer still multiplies this one
+            self.nsets = 4 if self.pipeline else 2
+            self.ex = mgd.PushExchange([(M, gr["split"]) for gr in self.groups], world, rank, device, n_sets=self.nsets)
             for gi, gr in enumerate(self.groups):
-                gr["A"] = [self.ex.buffers(s, gi) for s in range(2)]
+                gr["A"] = [self.ex.buffers(s, gi) for s in range(self.nsets)]
         else:
             if self.exchange in ("bcast", "allgather"):
                 from mixedgemm_b200 import dist as mgd
@@ -267,6 +271,11 @@ class Job:
         self.fused = self.fused and can_fuse
         grouped = [M > 128 and len(gr["layers"]) <= 8 and all(Nl % 256 == 0 for (_, Nl, _, _) in gr["layers"])
                    for gr in self.groups]
+        # one quantiser launch for all activations of a step where the rows are sharded (small problems
+        # that do not fill the GPU one by one)
+        self.multi_q = self.sharded_q
+        if self.multi_q:
+            nq = 1
         # kernels of this library per step: the quantisers + the GEMM launches (+ the epoch bump)
         self.n_kernels = nq + (1 if self.fused else sum(1 if g_ else len(gr["layers"]) for g_, gr in zip(grouped, self.groups)))
         self.n_kernels += 1 if self.ex is not None else 0
@@ -288,10 +297,20 @@ class Job:
         else:
             self.mg.reorder_quantize_x(gr["X"], gr["idx"], KN, KS, KO, self.M, 0, out=A)
 
+    def quantize_all(self, s=0):
+        """This rank's rows of every activation in one launch (sharded quantisation only)."""
+        from mixedgemm_b200 import dist as mgd
+        probs = []
+        for gi in self.order:
+            gr = self.groups[gi]
+            out = self.ex.shard(s, gi) if self.ex is not None else mgd.activation_shard(gr["A"][s], self.M, gr["split"], self.world, self.rank)
+            probs.append((gr["X"], gr["idx"], *gr["split"], out))
+        self.mg.reorder_quantize_x_multi(probs)
+
     def exchange_a(self, gi, s=0):
         gr = self.groups[gi]
         if self.exchange == "push":
-            self.ex.push(s, gi)
+            raise RuntimeError("the push exchange moves a whole step at once: fill()")
         elif self.exchange == "bcast":
             self.comm.broadcast_activations(gr["A"][s], src=0)
         elif self.exchange == "allgather":
@@ -314,11 +333,38 @@ class Job:
                 flags.append(self.ex.ready(s, gi) if self.ex is not None else None)
         self.mg.matmul_multi(probs, flags=flags if self.ex is not None else None)
 
-    def step(self, s=0):
-        """One pass: quantise (this rank's part of) every activation, exchange, multiply."""
-        if self.ex is not None:
-            self.ex.begin_step()
+    def fill(self, s):
+        """Push exchange: quantise this rank's rows of every activation into set s and send them."""
+        self.ex.begin_step(s)
+        self.quantize_all(s)
+        self.ex.push(s)
+
+    def multiply(self, s):
         if self.fused:
+            self.gemm_fused(s)
+        else:
+            for gi in range(len(self.groups)):
+                self.gemm_group(gi, s)
+
+    def step(self, s=0):
+        """One pass: quantise (this rank's part of) every activation, exchange, multiply.  Pipelined
+        push: the pass quantises and sends batch s + 1 and multiplies batch s, which the pass before
+        sent (prime() sends the very first one)."""
+        if self.ex is not None:
+            if self.pipeline:
+                if not self.primed:
+                    self.prime(s)
+                self.fill((s + 1) % self.nsets)
+            else:
+                self.fill(s)
+            self.multiply(s)
+            self.ex.join()
+        elif self.multi_q:
+            self.quantize_all(s)
+            for gi in self.order:
+                self.exchange_a(gi, s)
+            self.multiply(s)
+        elif self.fused:
             for gi in self.order:
                 self.quantize(gi, s)
                 self.exchange_a(gi, s)
@@ -328,8 +374,11 @@ class Job:
                 self.quantize(gi, s)
                 self.exchange_a(gi, s)
                 self.gemm_group(gi, s)
-        if self.ex is not None:
-            self.ex.join()
+
+    def prime(self, s=0):
+        self.fill(s)
+        self.ex.join()
+        self.primed = True
 
     def close(self):
         if self.ex is not None:
@@ -437,6 +486,8 @@ def main():
     ap.add_argument("--workload", default=None, choices=list(WORKLOADS))
     ap.add_argument("--exchange", default="push", choices=["push", "allgather", "bcast", "replicated"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-pipeline", action="store_true",
+                    help="push exchange: send and multiply the same batch in a step instead of sending batch i + 1 under the GEMM of batch i")
     ap.add_argument("--no-fuse", action="store_true", help="one GEMM launch per activation instead of one over all layers")
     ap.add_argument("--no-extra", action="store_true", help="skip the `extra` kernels of the default line")
     ap.add_argument("--cpu-rows", type=int, default=128)
@@ -508,7 +559,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    job = Job(wl_name, rank, world, device, a.exchange, fused=not a.no_fuse)
+    job = Job(wl_name, rank, world, device, a.exchange, fused=not a.no_fuse, pipeline=not a.no_pipeline)
     pk = peaks()
     nsets = job.nsets
 
@@ -647,22 +698,29 @@ def main():
                     job.groups[g]["X"].copy_(hX[g], non_blocking=True)
                     ev_in[g].record(in_s)
             if job.ex is not None:
-                job.ex.begin_step()
-            for g in order:
-                main_s.wait_event(ev_in[g])
-                job.quantize(g, s_)
-                ev_xfree[g].record(main_s)
-                job.exchange_a(g, s_)
-                if not e2e_fused:
-                    main_s.wait_event(ev_yfree[g])
-                    job.gemm_group(g, s_)
-                    ev_done[g].record(main_s)
-            if e2e_fused:
+                # the push exchange moves a step's activations at once: all uploads, one quantiser
+                # launch, one push, then the GEMMs (not pipelined across steps here)
+                for g in order:
+                    main_s.wait_event(ev_in[g])
+                job.ex.begin_step(s_)
+                job.quantize_all(s_)
+                for g in order:
+                    ev_xfree[g].record(main_s)
+                job.ex.push(s_)
                 for g in order:
                     main_s.wait_event(ev_yfree[g])
-                job.gemm_fused(s_)
+                job.multiply(s_)
                 job.ex.join()
                 for g in order:
+                    ev_done[g].record(main_s)
+            else:
+                for g in order:
+                    main_s.wait_event(ev_in[g])
+                    job.quantize(g, s_)
+                    ev_xfree[g].record(main_s)
+                    job.exchange_a(g, s_)
+                    main_s.wait_event(ev_yfree[g])
+                    job.gemm_group(g, s_)
                     ev_done[g].record(main_s)
             for g in order:
                 out_s.wait_event(ev_done[g])
@@ -732,6 +790,9 @@ def main():
                    "layers": [[gr["K"], [[n, N * world] for (n, N, _, _) in gr["layers"]]] for gr in job.groups],
                    "k_split": "62.5% fp4 / 34.375% fp6 / 3.125% fp8", "parallelism": "n-shard x%d" % world,
                    "exchange": job.exchange, "cuda_graph": use_graph,
+                   "pipeline": ("every step quantises and sends batch i + 1 (one quantiser launch, one copy per peer) and "
+                                "multiplies batch i, which the step before sent; %d buffer sets in turn" % job.nsets)
+                   if job.pipeline else None,
                    "gemm_launch": "one launch over all layers" if job.fused else "one launch per activation",
                    "l2": "inputs larger than L2: one step touches ~%d MB of weights, activations and outputs" % (
                        (sum(t.numel() * t.element_size() for gr in job.groups for (_, _, B, Y) in gr["layers"]

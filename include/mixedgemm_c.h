@@ -167,6 +167,22 @@ size_t mg_code_pitch(int weights, int segment, int kseg);
 int mg_reorder_quantize_pitched(int weights, const void* X, int rows, int K, const int16_t* idx, int KN, int KS,
                                 int KO, uint8_t* C4, uint8_t* C6, uint8_t* C8, const size_t* pitches,
                                 uint8_t* SF4, uint8_t* SF6, uint8_t* SF8, void* stream);
+/*
+ * Up to eight independent quantisations (own input, reorder index, K split and output buffers) in one
+ * launch: the CTAs are dealt out to the problems in proportion to their sizes, so that the
+ * activations of a step are quantised in one wave.  Every problem is what one
+ * mg_reorder_quantize_pitched call takes (pitch = {0, 0, 0} means dense rows) and gives the same bytes.
+ */
+typedef struct mg_quant_problem {
+  const void* X; /* [rows, K] bf16 */
+  int rows, K;
+  const int16_t* idx;
+  int KN, KS, KO;
+  uint8_t *C4, *C6, *C8;
+  size_t pitch[3];
+  uint8_t *SF4, *SF6, *SF8;
+} mg_quant_problem_t;
+int mg_reorder_quantize_multi(int weights, int nprob, const mg_quant_problem_t* probs, void* stream);
 size_t mg_matmul_pitched_workspace_bytes(int M, int N, int KN, int KS, int KO, const size_t* pitches);
 int mg_matmul_pitched(const uint8_t* AN, const uint8_t* BN, const uint8_t* AS, const uint8_t* BS,
                       const uint8_t* AO, const uint8_t* BO, const size_t* pitches, int out_f32, int M, int N,

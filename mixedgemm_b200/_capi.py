@@ -25,6 +25,7 @@ PROTOTYPES = {
     "mg_get_option": (_i, [ctypes.c_char_p, ctypes.POINTER(_i)]),
     "mg_reset_options": (None, []),
     "mg_matmul_multi": (_i, [_i, _vp, _vp]),
+    "mg_reorder_quantize_multi": (_i, [_i, _i, _vp, _vp]),
     "mg_dist_unique_id": (_i, [_vp]),
     "mg_dist_init": (_i, [ctypes.POINTER(_vp), _vp, _i, _i]),
     "mg_dist_destroy": (_i, [_vp]),
@@ -57,6 +58,12 @@ PROTOTYPES = {
     "mg_matmul_fp8": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
 }
 
+
+
+class QuantProblem(ctypes.Structure):
+    """mg_quant_problem_t of include/mixedgemm_c.h."""
+    _fields_ = [("X", _vp), ("rows", _i), ("K", _i), ("idx", _vp), ("KN", _i), ("KS", _i), ("KO", _i),
+                ("C4", _vp), ("C6", _vp), ("C8", _vp), ("pitch", _sz * 3), ("SF4", _vp), ("SF6", _vp), ("SF8", _vp)]
 
 
 class Problem(ctypes.Structure):

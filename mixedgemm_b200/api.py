@@ -136,6 +136,43 @@ def reorder_quantize_x(X, reorder_index, KN, KS, KO, seqlen=None, outfeatures=No
     return XN, XS, XO, sfs[0], sfs[1], sfs[2]
 
 
+def reorder_quantize_x_multi(problems):
+    """One launch for up to eight activations: problems = [(X, reorder_index, KN, KS, KO, out), ...]
+    with `out` the six buffers to write (alloc_quantized_x) or None.  Every entry gives the bytes of
+    its own reorder_quantize_x call; the CTAs are shared out in proportion to the sizes
+    (mg_reorder_quantize_multi).  Returns the list of six-tuples."""
+    import ctypes
+    lib = _capi.load()
+    n = len(problems)
+    if not 1 <= n <= 8:
+        raise RuntimeError("reorder_quantize_x_multi: 1 to 8 problems per launch")
+    arr = (_capi.QuantProblem * n)()
+    outs = []
+    dev = problems[0][0].device
+    for j, (X, idx, KN, KS, KO, out) in enumerate(problems):
+        _check_in(X, idx, KN, KS, KO, "reorder_quantize_x_multi")
+        if X.device != dev:
+            raise RuntimeError("reorder_quantize_x_multi: all problems must be on one device")
+        M = X.size(0)
+        XN, XS, XO, *sfs = out if out is not None else alloc_quantized_x(M, KN, KS, KO, dev)
+        _check_codes((XN, XS, XO), "reorder_quantize_x_multi")
+        for t, k in zip(sfs, (KN, KS, KO)):
+            if t.numel() < lib.mg_sf_bytes(M, k) or t.device != dev or t.dtype != torch.uint8:
+                raise RuntimeError("reorder_quantize_x_multi: a scale buffer is too small or on another device")
+        q = arr[j]
+        q.X, q.rows, q.K, q.idx = _ptr(X), M, X.size(1), _ptr(idx)
+        q.KN, q.KS, q.KO = KN, KS, KO
+        q.C4, q.C6, q.C8 = _ptr(XN), _ptr(XS), _ptr(XO)
+        for i, t in enumerate((XN, XS, XO)):
+            q.pitch[i] = t.stride(0) if t.size(1) else 0
+        q.SF4, q.SF6, q.SF8 = _ptr(sfs[0]), _ptr(sfs[1]), _ptr(sfs[2])
+        outs.append((XN, XS, XO, sfs[0], sfs[1], sfs[2]))
+    with torch.cuda.device(dev):
+        st = lib.mg_reorder_quantize_multi(0, n, ctypes.cast(arr, ctypes.c_void_p), _stream())
+    _capi.check(st, "reorder_quantize_x_multi")
+    return outs
+
+
 def reorder_quantize_w(W, reorder_index, KN, KS, KO, seqlen=None, outfeatures=None, out=None):
     """bindings.cpp:188-305.  Returns (WN[N,KN/2], WS[N,KS/2], WO[N,KO/2], SFWN, SFWS, SFWO), all uint8."""
     _check_in(W, reorder_index, KN, KS, KO, "reorder_quantize_w")

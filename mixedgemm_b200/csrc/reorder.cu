@@ -206,8 +206,9 @@ __device__ __forceinline__ void quantise_group(const ReorderParams& p, const Row
   }
 }
 
+// One CTA's work: block `blk` of the `nblk` blocks that share the rows of problem p.
 template <int R, bool WEIGHTS>
-__global__ void __launch_bounds__(kThreads, 1) reorder_quantize_kernel(const ReorderParams p) {
+__device__ __forceinline__ void reorder_quantize_cta(const ReorderParams& p, int blk, int nblk) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int K = p.K;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -234,8 +235,8 @@ __global__ void __launch_bounds__(kThreads, 1) reorder_quantize_kernel(const Reo
   ptx::grid_dep_wait();  // nothing before this line reads or writes global memory
 
   // This CTA's contiguous share of the rows, walked in stages of up to R rows.
-  const int row_begin = (int)((long long)p.rows * blockIdx.x / gridDim.x);
-  const int row_end = (int)((long long)p.rows * (blockIdx.x + 1) / gridDim.x);
+  const int row_begin = (int)((long long)p.rows * blk / nblk);
+  const int row_end = (int)((long long)p.rows * (blk + 1) / nblk);
   const int nstage = (row_end - row_begin + R - 1) / R;
 
   const int G = K >> 5;
@@ -322,6 +323,36 @@ __global__ void __launch_bounds__(kThreads, 1) reorder_quantize_kernel(const Reo
   }
 }
 
+template <int R, bool WEIGHTS>
+__global__ void __launch_bounds__(kThreads, 1) reorder_quantize_kernel(const __grid_constant__ ReorderParams p) {
+  reorder_quantize_cta<R, WEIGHTS>(p, (int)blockIdx.x, (int)gridDim.x);
+}
+
+// Several independent problems (own input, index, K split and outputs) in one launch: the CTAs are
+// dealt out to the problems in proportion to their bytes, so that a step's activations are quantised
+// in one wave instead of one launch - and one partly filled wave - each.
+constexpr int kMaxQuant = 8;
+struct ReorderMulti {
+  int nprob;
+  int cta_end[kMaxQuant];  // problem j owns CTAs [cta_end[j-1], cta_end[j])
+  int rows_per_stage[kMaxQuant];
+  ReorderParams prob[kMaxQuant];
+};
+
+template <bool WEIGHTS>
+__global__ void __launch_bounds__(kThreads, 1) reorder_quantize_multi_kernel(const __grid_constant__ ReorderMulti mp) {
+  int j = 0, first = 0;
+  while (j + 1 < mp.nprob && (int)blockIdx.x >= mp.cta_end[j]) first = mp.cta_end[j++];
+  const ReorderParams& p = mp.prob[j];
+  const int blk = (int)blockIdx.x - first, nblk = mp.cta_end[j] - first;
+  switch (mp.rows_per_stage[j]) {
+    case 8: reorder_quantize_cta<8, WEIGHTS>(p, blk, nblk); break;
+    case 4: reorder_quantize_cta<4, WEIGHTS>(p, blk, nblk); break;
+    case 2: reorder_quantize_cta<2, WEIGHTS>(p, blk, nblk); break;
+    default: reorder_quantize_cta<1, WEIGHTS>(p, blk, nblk); break;
+  }
+}
+
 size_t smem_bytes(int K, int R, int S) {
   return (size_t)((2 * K + 15) & ~15) + (size_t)S * R * (2 * K + kRowSkew) + 16 * 8 + 16;
 }
@@ -334,9 +365,12 @@ int launch(const ReorderParams& p, int grid, size_t smem, cudaStream_t st) {
   return MG_OK;
 }
 
-int reorder_quantize(bool weights, const void* X, int rows, int K, const int16_t* idx, int KN, int KS,
-                     int KO, uint8_t* o4, uint8_t* o6, uint8_t* o8, const size_t* pitches, uint8_t* s4, uint8_t* s6,
-                     uint8_t* s8, void* stream) {
+// Checks one problem and fills its kernel parameters (everything but the stage shape, which depends
+// on how many CTAs the problem gets).  MG_OK with p->rows == 0 means "nothing to do".
+int fill_params(bool weights, const void* X, int rows, int K, const int16_t* idx, int KN, int KS, int KO, uint8_t* o4,
+                uint8_t* o6, uint8_t* o8, const size_t* pitches, uint8_t* s4, uint8_t* s6, uint8_t* s8,
+                ReorderParams* out) {
+  out->rows = 0;
   if (rows < 0 || K <= 0 || KN < 0 || KS < 0 || KO < 0 || KN + KS + KO != K) return MG_ERR_SHAPE;
   if ((KN | KS | KO) & 31) return MG_ERR_SHAPE;
   if (K > 32736) return MG_ERR_SHAPE;  // int16 index
@@ -346,11 +380,7 @@ int reorder_quantize(bool weights, const void* X, int rows, int K, const int16_t
   if (!mg::aligned(X, 16)) return MG_ERR_ALIGN;
   if (!mg::aligned(o4, 16) || !mg::aligned(o6, 8) || !mg::aligned(o8, 16)) return MG_ERR_ALIGN;
 
-  mg::DeviceInfo di;
-  int rc = mg::device_info(&di);
-  if (rc != MG_OK) return rc;
-
-  ReorderParams p;
+  ReorderParams& p = *out;
   p.X = static_cast<const uint16_t*>(X);
   p.idx = idx;
   p.rows = rows;
@@ -361,21 +391,22 @@ int reorder_quantize(bool weights, const void* X, int rows, int K, const int16_t
   const size_t align[3] = {16, (size_t)(weights ? 16 : 8), 16};
   size_t pitch[3];
   for (int i = 0; i < 3; ++i) {
-    pitch[i] = pitches ? pitches[i] : dense[i];
+    pitch[i] = pitches && pitches[i] ? pitches[i] : dense[i];
     if (pitch[i] < dense[i] || pitch[i] > 0x7fffffffu) return MG_ERR_SHAPE;
     if (pitch[i] % align[i]) return MG_ERR_ALIGN;
   }
   p.seg[0] = {o4, s4, (KN + 127) / 128, (int)pitch[0]};
   p.seg[1] = {o6, s6, (KS + 127) / 128, (int)pitch[1]};
   p.seg[2] = {o8, s8, (KO + 127) / 128, (int)pitch[2]};
+  p.wait_cycles = mg::wait_limit_cycles();
+  return mg::device_status_word(&p.status);
+}
 
-  // Rows per stage (8, 4, 2 or 1): as many as fit twice (double buffering) beside the index, but no more than
-  // half of a CTA's share so that its last stage is not mostly empty.  Then as many stages as
-  // fit, up to 4.
-  const size_t budget = (size_t)di.smem_optin - 1024;
-  int grid = rows < di.sm_count ? rows : di.sm_count;  // rows are dealt out evenly, at least one per CTA
-  const int cap = mg::options().reorder_ctas;  // a caller that runs another kernel beside this one may cap the grid
-  if (cap > 0 && grid > cap) grid = cap;
+// Rows per stage and stage count of a problem whose rows are shared by `grid` CTAs; returns the
+// shared memory a CTA needs, or 0 when the problem does not fit.
+size_t stage_shape(ReorderParams* p, int grid, size_t smem_optin, int* rows_per_stage) {
+  const int K = p->K, rows = p->rows;
+  const size_t budget = smem_optin - 1024;
   const int rows_per_cta = rows / grid;
   static const int kRs[] = {8, 4, 2, 1};
   int R = 1;
@@ -385,12 +416,31 @@ int reorder_quantize(bool weights, const void* X, int rows, int K, const int16_t
   while (S < 4 && smem_bytes(K, R, S + 1) <= budget) ++S;
   if (smem_bytes(K, R, 2) > budget) S = 1;
   const size_t smem = smem_bytes(K, R, S);
-  if (smem > (size_t)di.smem_optin) return MG_ERR_SHAPE;
-  p.num_tiles = (rows + R - 1) / R;
-  p.stages = S;
-  p.wait_cycles = mg::wait_limit_cycles();
-  rc = mg::device_status_word(&p.status);
-  if (rc != MG_OK) return rc;
+  if (smem > smem_optin) return 0;
+  p->num_tiles = (rows + R - 1) / R;
+  p->stages = S;
+  *rows_per_stage = R;
+  return smem;
+}
+
+int reorder_quantize(bool weights, const void* X, int rows, int K, const int16_t* idx, int KN, int KS,
+                     int KO, uint8_t* o4, uint8_t* o6, uint8_t* o8, const size_t* pitches, uint8_t* s4, uint8_t* s6,
+                     uint8_t* s8, void* stream) {
+  ReorderParams p;
+  int rc = fill_params(weights, X, rows, K, idx, KN, KS, KO, o4, o6, o8, pitches, s4, s6, s8, &p);
+  if (rc != MG_OK || p.rows == 0) return rc;
+  mg::DeviceInfo di;
+  if ((rc = mg::device_info(&di)) != MG_OK) return rc;
+
+  // Rows per stage (8, 4, 2 or 1): as many as fit twice (double buffering) beside the index, but no more than
+  // half of a CTA's share so that its last stage is not mostly empty.  Then as many stages as
+  // fit, up to 4.
+  int grid = rows < di.sm_count ? rows : di.sm_count;  // rows are dealt out evenly, at least one per CTA
+  const int cap = mg::options().reorder_ctas;  // a caller that runs another kernel beside this one may cap the grid
+  if (cap > 0 && grid > cap) grid = cap;
+  int R = 1;
+  const size_t smem = stage_shape(&p, grid, (size_t)di.smem_optin, &R);
+  if (smem == 0) return MG_ERR_SHAPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
 #define MG_LAUNCH_R(RR)                                                            \
@@ -406,7 +456,60 @@ int reorder_quantize(bool weights, const void* X, int rows, int K, const int16_t
   return MG_ERR_SHAPE;
 }
 
+template <bool WEIGHTS>
+int launch_multi(const ReorderMulti& mp, int grid, size_t smem, cudaStream_t st) {
+  auto kern = reorder_quantize_multi_kernel<WEIGHTS>;
+  if (smem > 48 * 1024) MG_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  MG_CUDA_TRY(mg::launch_kernel(kern, dim3(grid), dim3(kThreads), smem, st, mp));
+  return MG_OK;
+}
+
 }  // namespace
+
+extern "C" int mg_reorder_quantize_multi(int weights, int nprob, const mg_quant_problem_t* probs, void* stream) {
+  if (nprob < 0 || nprob > kMaxQuant) return MG_ERR_SHAPE;
+  if (nprob == 0) return MG_OK;
+  if (!probs) return MG_ERR_NULL;
+  mg::DeviceInfo di;
+  int rc = mg::device_info(&di);
+  if (rc != MG_OK) return rc;
+  ReorderMulti mp;
+  int n = 0;
+  double bytes[kMaxQuant], total = 0;
+  for (int j = 0; j < nprob; ++j) {
+    const mg_quant_problem_t& q = probs[j];
+    ReorderParams& p = mp.prob[n];
+    rc = fill_params(weights != 0, q.X, q.rows, q.K, q.idx, q.KN, q.KS, q.KO, q.C4, q.C6, q.C8, q.pitch, q.SF4, q.SF6,
+                     q.SF8, &p);
+    if (rc != MG_OK) return rc;
+    if (p.rows == 0) continue;
+    bytes[n] = (double)p.rows * p.K;
+    total += bytes[n];
+    ++n;
+  }
+  if (n == 0) return MG_OK;
+  // CTAs in proportion to the bytes, at least one and at most one per row; one CTA per SM in all
+  int sms = di.sm_count;
+  const int cap = mg::options().reorder_ctas;
+  if (cap > 0 && sms > cap) sms = cap;
+  if (sms < n) sms = n;
+  int grid = 0;
+  size_t smem = 0;
+  for (int j = 0; j < n; ++j) {
+    int g = (int)(sms * bytes[j] / total);
+    if (g < 1) g = 1;
+    if (g > mp.prob[j].rows) g = mp.prob[j].rows;
+    const size_t sm = stage_shape(&mp.prob[j], g, (size_t)di.smem_optin, &mp.rows_per_stage[j]);
+    if (sm == 0) return MG_ERR_SHAPE;
+    if (sm > smem) smem = sm;
+    grid += g;
+    mp.cta_end[j] = grid;
+  }
+  for (int j = n; j < kMaxQuant; ++j) { mp.cta_end[j] = grid; mp.rows_per_stage[j] = 1; }
+  mp.nprob = n;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return weights ? launch_multi<true>(mp, grid, smem, st) : launch_multi<false>(mp, grid, smem, st);
+}
 
 extern "C" int mg_reorder_quantize_x(const void* X, int M, int K, const int16_t* idx, int KN, int KS, int KO,
                                      uint8_t* AN, uint8_t* AS, uint8_t* AO, uint8_t* SFAN, uint8_t* SFAS,

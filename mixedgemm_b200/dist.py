@@ -168,50 +168,59 @@ def _align(n, a=1024):
 
 
 class PushExchange:
-    """Exchange buffers for `n_sets` x len(shapes) quantised activations (shapes = [(M, (KN, KS, KO)), ...];
-    n_sets = 2 lets consecutive steps alternate, which they must: a rank may start pushing the next
-    step while a slower peer still multiplies the current one).  Every buffer is one device
-    allocation, laid out identically on every rank and opened on every other rank through CUDA IPC.
-    It is stored shard by shard: the M/P rows that rank r quantises - three code tensors at their row
-    pitch, then their three scale tensors - form ONE contiguous block, so that a push is one large
-    copy per peer (small copies reach a fraction of the NVLink rate), followed by `world` flag words.
-    The GEMM reads that layout in place (api.ShardedActivation)."""
+    """Exchange buffers for `n_sets` steps' worth of quantised activations (shapes = [(M, (KN, KS, KO)), ...],
+    the activations of one step).  A set is one device allocation, laid out identically on every rank
+    and opened on every other rank through CUDA IPC.  It is stored rank by rank: everything rank r
+    quantises in a step - its M/P rows of every activation, each as three code tensors at their row
+    pitch followed by their three scale tensors - is ONE contiguous block, so that a step's push is
+    one large copy per peer (small copies reach a fraction of the NVLink rate, and every copy costs
+    tens of microseconds of latency), followed by `world` flag words.  The GEMM reads that layout in
+    place (api.ShardedActivation).
+
+    How many sets: a rank may run ahead of a peer by the steps the caller keeps in flight.  When a
+    step pushes, multiplies and joins the same set, 2 sets are enough; when the push of step i + 1 is
+    issued before the GEMM of step i (so that the transfer hides under it), a set is overwritten three
+    steps after it was read and 4 are needed."""
 
     def __init__(self, shapes, world, rank, device, n_sets=2, group=None):
         from .api import ShardedActivation
         self.lib = lib = _capi.load()
         self.world, self.rank, self.device = world, rank, device
         self.shapes = list(shapes)
-        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = torch.zeros(n_sets, dtype=torch.int32, device=device)
         self.streams = [torch.cuda.Stream(device=device) for _ in range(max(world - 1, 1))]
         self.sets = []
         handles = []
+        # the block of one rank: per activation six parts, each aligned to 1 KB
+        parts, off = [], 0
+        for (M, split) in self.shapes:
+            if M % (256 * world) != 0:
+                raise ValueError("M = %d must split into %d shards of whole 256-row blocks" % (M, world))
+            mp = M // world
+            logical = (split[0] // 2, split[1] // 4 * 3, split[2])
+            pitch = [lib.mg_code_pitch(0, i, k) for i, k in enumerate(split)]
+            sizes = [mp * p for p in pitch] + [lib.mg_sf_bytes(mp, k) for k in split]
+            offs = []
+            for n in sizes:
+                offs.append(off)
+                off += _align(n)
+            parts.append((mp, logical, pitch, sizes, offs))
+        self.block_bytes = off
+        self.flag_off = world * off
+        total = self.flag_off + _align(4 * world)
         with torch.cuda.device(device):
             for s in range(n_sets):
-                bufs = []
-                for (M, split) in self.shapes:
-                    if M % (256 * world) != 0:
-                        raise ValueError("M = %d must split into %d shards of whole 256-row blocks" % (M, world))
-                    mp = M // world
-                    logical = (split[0] // 2, split[1] // 4 * 3, split[2])
-                    pitch = [lib.mg_code_pitch(0, i, k) for i, k in enumerate(split)]
-                    sizes = [mp * p for p in pitch] + [lib.mg_sf_bytes(mp, k) for k in split]
-                    offs, off = [], 0
-                    for n in sizes:
-                        offs.append(off)
-                        off += _align(n)
-                    shard_bytes = off
-                    flag_off = world * shard_bytes
-                    total = flag_off + _align(4 * world)
-                    ptr = ctypes.c_void_p()
-                    _capi.check(lib.mg_xbuf_alloc(ctypes.byref(ptr), total), "mg_xbuf_alloc")
-                    h = ctypes.create_string_buffer(64)
-                    _capi.check(lib.mg_ipc_export(ptr, h), "mg_ipc_export")
-                    handles.append(h.raw)
-                    flat = torch.as_tensor(_Raw(ptr.value, total), device=device)
+                ptr = ctypes.c_void_p()
+                _capi.check(lib.mg_xbuf_alloc(ctypes.byref(ptr), total), "mg_xbuf_alloc")
+                h = ctypes.create_string_buffer(64)
+                _capi.check(lib.mg_ipc_export(ptr, h), "mg_ipc_export")
+                handles.append(h.raw)
+                flat = torch.as_tensor(_Raw(ptr.value, total), device=device)
+                acts = []
+                for (mp, logical, pitch, sizes, offs) in parts:
                     shards = []
                     for r in range(world):
-                        blk = flat[r * shard_bytes:(r + 1) * shard_bytes]
+                        blk = flat[r * off:(r + 1) * off]
                         A = []
                         for i in range(3):
                             v = blk[offs[i]:offs[i] + sizes[i]].view(mp, pitch[i])
@@ -219,66 +228,62 @@ class PushExchange:
                         for i in range(3):
                             A.append(blk[offs[3 + i]:offs[3 + i] + sizes[3 + i]])
                         shards.append(tuple(A))
-                    flags = flat[flag_off:flag_off + 4 * world].view(torch.int32)
-                    bufs.append(dict(ptr=ptr, A=ShardedActivation(shards), flags=flags, flag_off=flag_off,
-                                     segs=[(rank * shard_bytes, shard_bytes)], M=M, split=split, bases=None, flat=flat))
-                self.sets.append(bufs)
-        # every rank opens every other rank's buffers
+                    acts.append(ShardedActivation(shards))
+                flags = flat[self.flag_off:self.flag_off + 4 * world].view(torch.int32)
+                self.sets.append(dict(ptr=ptr, A=acts, flags=flags, bases=None, flat=flat))
+        # every rank opens every other rank's sets
         self._imported = []
         all_handles = _exchange_bytes(handles, group) if world > 1 else [handles]
-        k = 0
-        for bufs in self.sets:
-            for b in bufs:
-                bases = []
-                for r in range(world):
-                    if r == rank:
-                        bases.append(b["ptr"].value)
-                    else:
-                        p = ctypes.c_void_p()
-                        with torch.cuda.device(device):
-                            _capi.check(lib.mg_ipc_import(all_handles[r][k], ctypes.byref(p)), "mg_ipc_import")
-                        self._imported.append(p)
-                        bases.append(p.value)
-                b["bases"] = bases
-                k += 1
+        for k, b in enumerate(self.sets):
+            bases = []
+            for r in range(world):
+                if r == rank:
+                    bases.append(b["ptr"].value)
+                else:
+                    p = ctypes.c_void_p()
+                    with torch.cuda.device(device):
+                        _capi.check(lib.mg_ipc_import(all_handles[r][k], ctypes.byref(p)), "mg_ipc_import")
+                    self._imported.append(p)
+                    bases.append(p.value)
+            b["bases"] = bases
 
     def buffers(self, set_index, i):
         """Activation i of set `set_index` as the api.ShardedActivation that matmul_multi takes."""
-        return self.sets[set_index][i]["A"]
+        return self.sets[set_index]["A"][i]
 
     def shard(self, set_index, i, rank=None):
         """The six tensors of this rank's (or `rank`'s) M/P rows of activation i: what its quantiser
         writes (`out=` of reorder_quantize_x)."""
-        return self.sets[set_index][i]["A"].shards[self.rank if rank is None else rank]
+        return self.sets[set_index]["A"][i].shards[self.rank if rank is None else rank]
 
-    def begin_step(self):
-        """Once per step, before the quantisers: the value the flags of this step will carry."""
-        _capi.check(self.lib.mg_epoch_bump(self.epoch.data_ptr(), _stream()), "mg_epoch_bump")
+    def begin_step(self, set_index):
+        """Before the quantisers that fill set `set_index`: the value its flags will carry this time."""
+        _capi.check(self.lib.mg_epoch_bump(self.epoch[set_index:].data_ptr(), _stream()), "mg_epoch_bump")
 
-    def push(self, set_index, i):
-        """After this rank's rows of activation i have been quantised on the current stream: copy
-        them into every peer's buffer and raise this rank's flag there.  The copies run on the
-        exchange's own streams, ordered after the current stream's work so far."""
-        b = self.sets[set_index][i]
+    def push(self, set_index):
+        """After this rank's rows of every activation of the set have been quantised on the current
+        stream: copy its block into every peer's set and raise this rank's flag there.  The copies run
+        on the exchange's own streams, ordered after the current stream's work so far."""
+        b = self.sets[set_index]
         done = torch.cuda.Event()
         done.record()
         for st in self.streams:
             st.wait_event(done)
         _capi.check(self.lib.mg_push_shard(
-            self.world, self.rank, _vp_array(b["bases"]), _sz_array([o for o, _ in b["segs"]]),
-            _sz_array([n for _, n in b["segs"]]), len(b["segs"]), b["flag_off"], self.epoch.data_ptr(),
+            self.world, self.rank, _vp_array(b["bases"]), _sz_array([self.rank * self.block_bytes]),
+            _sz_array([self.block_bytes]), 1, self.flag_off, self.epoch[set_index:].data_ptr(),
             _vp_array([st.cuda_stream for st in self.streams])), "mg_push_shard")
 
     def ready(self, set_index, i):
-        """The `flags` entry of api.matmul_multi for a problem that reads activation i: one flag per
-        row shard, target = this step's epoch, tiles start with this rank's own rows."""
-        b = self.sets[set_index][i]
-        mp = b["M"] // self.world
-        return (b["flags"], self.epoch, mp, self.rank * mp)
+        """The `flags` entry of api.matmul_multi for a problem that reads activation i of the set: one
+        flag per rank, target = the set's current epoch, tiles start with this rank's own rows."""
+        b = self.sets[set_index]
+        mp = b["A"][i].shard_rows
+        return (b["flags"], self.epoch[set_index:set_index + 1], mp, self.rank * mp)
 
     def join(self):
-        """Make the current stream wait for the copies this rank has issued (end of a step: the
-        buffers it pushed FROM may be overwritten afterwards)."""
+        """Make the current stream wait for the copies this rank has issued (the buffers it pushed
+        FROM may be overwritten afterwards)."""
         for st in self.streams:
             torch.cuda.current_stream().wait_stream(st)
 
@@ -287,8 +292,7 @@ class PushExchange:
         for p in self._imported:
             self.lib.mg_ipc_close(p)
         self._imported = []
-        for bufs in self.sets:
-            for b in bufs:
-                b["A"] = b["flags"] = b["flat"] = None
-                self.lib.mg_xbuf_free(b["ptr"])
+        for b in self.sets:
+            b["A"] = b["flags"] = b["flat"] = None
+            self.lib.mg_xbuf_free(b["ptr"])
         self.sets = []

@@ -74,18 +74,58 @@ def _worker(rank, world, port, ret):
         Yl = mg.matmul(*ab(A, Bl))
         ok["allgather"] = bool(torch.equal(Yl.view(torch.int16), reference(Xs[1])[:, n0:n0 + nl].contiguous().view(torch.int16)))
         comm.close()
-        # 3. the overlapped exchange, four steps over two alternating buffer sets
-        ex = mgd.PushExchange([(M, SPLIT)], world, rank, dev, n_sets=2)
+        # 3. the overlapped exchange: two activations per step (different K splits) travel as one block
+        # per peer.  First push, multiply and join one set per step; then the pipelined order, where
+        # the push of step i + 1 is issued before the GEMM of step i (four sets).
+        SPLIT2, N2 = (256, 128, 128), 512
+        K2 = sum(SPLIT2)
+        W2 = H.make_w(N2, K2, seed=3).cuda()
+        X2s = [H.make_x(M, K2, seed=30 + s).cuda() for s in range(4)]
+        idx2 = H.reorder_index(X2s[0].cpu()).cuda()
+        B2full = mg.reorder_quantize_w(W2, idx2, *SPLIT2, M, N2)
+        B2l = mgd.shard_weights(B2full, N2, *SPLIT2, world, rank)
+        m0, ml = mgd.shard_range(N2, world, rank)
+
+        def reference2(X):
+            Af = mg.reorder_quantize_x(X, idx2, *SPLIT2, M, N2)
+            return mg.matmul(*ab(Af, B2full))
+
+        ex = mgd.PushExchange([(M, SPLIT), (M, SPLIT2)], world, rank, dev, n_sets=4)
+        rows = slice(rank * mp_, (rank + 1) * mp_)
+
+        def fill(step, s):
+            ex.begin_step(s)
+            mg.reorder_quantize_x_multi([(Xs[step][rows].contiguous(), idx, KN, KS, KO, ex.shard(s, 0)),
+                                         (X2s[step][rows].contiguous(), idx2, *SPLIT2, ex.shard(s, 1))])
+            ex.push(s)
+
+        def multiply(s):
+            return mg.matmul_multi([(ex.buffers(s, 0), Bl, None), (ex.buffers(s, 1), B2l, None)],
+                                   flags=[ex.ready(s, 0), ex.ready(s, 1)])
+
+        def check(step, outs):
+            a = torch.equal(outs[0].view(torch.int16), reference(Xs[step])[:, n0:n0 + nl].contiguous().view(torch.int16))
+            b = torch.equal(outs[1].view(torch.int16), reference2(X2s[step])[:, m0:m0 + ml].contiguous().view(torch.int16))
+            return bool(a and b)
+
         good = True
         for step in range(4):
             s = step % 2
-            ex.begin_step()
-            mg.reorder_quantize_x(Xs[step][rank * mp_:(rank + 1) * mp_].contiguous(), idx, KN, KS, KO, mp_, N,
-                                  out=ex.shard(s, 0))
-            ex.push(s, 0)
-            out = mg.matmul_multi([(ex.buffers(s, 0), Bl, None)], flags=[ex.ready(s, 0)])[0]
+            fill(step, s)
+            outs = multiply(s)
             ex.join()
-            good &= bool(torch.equal(out.view(torch.int16), reference(Xs[step])[:, n0:n0 + nl].contiguous().view(torch.int16)))
+            good &= check(step, outs)
+        torch.cuda.synchronize()
+        dist.barrier()
+        piped = True
+        fill(0, 0)
+        for step in range(4):
+            if step + 1 < 4:
+                fill(step + 1, (step + 1) % 4)
+            outs = multiply(step % 4)
+            ex.join()
+            piped &= check(step, outs)
+        ok["pipelined"] = piped
         torch.cuda.synchronize()
         ok["push"] = good
         ok["status"] = mg.device_status()
@@ -104,5 +144,5 @@ def test_two_gpu_n_sharded_gemm_equals_single_gpu():
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
     for rank in (0, 1):
-        assert ret[rank]["bcast"] and ret[rank]["allgather"] and ret[rank]["push"], dict(ret[rank])
+        assert ret[rank]["bcast"] and ret[rank]["allgather"] and ret[rank]["push"] and ret[rank]["pipelined"], dict(ret[rank])
         assert ret[rank]["status"] == 0

@@ -161,3 +161,45 @@ def test_reorder_index_kernel(M, K):
     assert np.array_equal(idx.cpu().numpy(), want)
     tidx = torch.sort(Xb.float().abs().amax(0), stable=True).indices.to(torch.int16)
     assert torch.equal(idx.cpu(), tidx)
+
+
+def test_multi_problem_launch_equals_separate_calls():
+    """Several activations in one launch (mg_reorder_quantize_multi) give, problem by problem, the
+    bytes of a launch each: sizes that differ by 100x, stages of 1, 4 and 8 rows in one grid, a
+    single-row problem, pitched and dense outputs, an empty problem."""
+    import mixedgemm_b200 as mg
+    shapes = [(1024, (5120, 2816, 256)), (1024, (17920, 9856, 896)), (1, (128, 64, 64)), (77, (2560, 1408, 128)),
+              (4096, (256, 128, 128)), (16, (8960, 4928, 448)), (300, (1024, 0, 0)), (513, (0, 0, 2048))]
+    rng = np.random.default_rng(5)
+    probs, want = [], []
+    for j, (M, split) in enumerate(shapes):
+        K = sum(split)
+        X = H.make_x(M, K, seed=200 + j).cuda()
+        idx = torch.from_numpy(rng.permutation(K).astype(np.int16)).cuda()
+        out = mg.alloc_quantized_x(M, *split, X.device, padded=bool(j % 2))
+        for t in out:
+            t.fill_(0x5A)
+        probs.append((X, idx, *split, out))
+        # rows beyond M inside the last scale atom are never written: same fill on both sides
+        ref = mg.alloc_quantized_x(M, *split, X.device, padded=bool(j % 2))
+        for t in ref:
+            t.fill_(0x5A)
+        want.append(mg.reorder_quantize_x(X, idx, *split, out=ref))
+    got = mg.reorder_quantize_x_multi(probs)
+    torch.cuda.synchronize()
+    assert mg.device_status() == 0
+    lib_sf = mg.sf_bytes
+    for (M, split), g, w in zip(shapes, got, want):
+        for i in range(3):
+            assert torch.equal(g[i], w[i]), (M, split, i)
+            n = lib_sf(M, split[i])
+            assert torch.equal(g[3 + i][:n], w[3 + i][:n]), (M, split, "sf", i)
+    # a list of one, and a list with an empty problem in it
+    one = mg.reorder_quantize_x_multi([probs[3][:5] + (None,)])[0]
+    assert all(torch.equal(a, b) for a, b in zip(one[:3], want[3][:3]))
+    empty = torch.empty((0, 512), dtype=torch.bfloat16, device="cuda")
+    idx512 = torch.arange(512, dtype=torch.int16, device="cuda")
+    two = mg.reorder_quantize_x_multi([(empty, idx512, 256, 128, 128, None), probs[0][:5] + (None,)])
+    assert torch.equal(two[1][0], want[0][0]) and two[0][0].shape == (0, 128)
+    with pytest.raises(RuntimeError):
+        mg.reorder_quantize_x_multi([probs[0]] * 9)
