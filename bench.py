@@ -196,7 +196,7 @@ class Job:
     output buffers, and - on several GPUs - the exchange that brings every rank the whole
     quantised activation."""
 
-    def __init__(self, wl_name, rank, world, device, exchange, fused=True, pipeline=True):
+    def __init__(self, wl_name, rank, world, device, exchange, fused=True, pipeline=True, multi_q=None):
         import mixedgemm_b200 as mg
         self.mg = mg
         wl = WORKLOADS[wl_name]
@@ -228,6 +228,12 @@ class Job:
                 mp = M // world
                 Xb = Xb[rank * mp:(rank + 1) * mp].contiguous()  # this rank's rows are all it ever reads
             Ls = []
+            # Column shards that are not whole 256-column tiles (k and v of a grouped-query layer on 8
+            # GPUs: 128 columns each) are multiplied as ONE weight per rank, its rows the rank's
+            # rows of q, k and v one after the other - the fused QKV layout of a tensor-parallel layer.
+            shard_n = [N // world for (_, N) in layers]
+            merge = M > 128 and any(n % 256 for n in shard_n) and sum(shard_n) % 256 == 0
+            parts = []
             for li, (name, N) in enumerate(layers):
                 assert N % (128 * world) == 0, "every shard must be a multiple of 128 columns"
                 Nl = N // world
@@ -235,12 +241,22 @@ class Job:
                 W = (torch.randn(N, K, generator=gw, device=device) * wl["wstd"]).to(torch.bfloat16)
                 Wl = W[rank * Nl:(rank + 1) * Nl].contiguous()
                 del W
+                self.flops_local += 2 * M * Nl * K
+                self.flops_total += 2 * M * N * K
+                if merge:
+                    parts.append(Wl)
+                    continue
                 B = mg.reorder_quantize_w(Wl, idx, KN, KS, KO, M, Nl)
                 del Wl
                 Y = torch.empty((M, Nl), dtype=torch.bfloat16, device=device)
                 Ls.append((name, Nl, B, Y))
-                self.flops_local += 2 * M * Nl * K
-                self.flops_total += 2 * M * N * K
+                self.gemm_shapes.append((M, Nl, K))
+            if merge:
+                Wl = torch.cat(parts, 0)
+                Nl = Wl.size(0)
+                B = mg.reorder_quantize_w(Wl, idx, KN, KS, KO, M, Nl)
+                del Wl, parts
+                Ls.append(("+".join(n for (n, _) in layers), Nl, B, torch.empty((M, Nl), dtype=torch.bfloat16, device=device)))
                 self.gemm_shapes.append((M, Nl, K))
             self.groups.append(dict(K=K, split=(KN, KS, KO), X=Xb, idx=idx, layers=Ls))
         # the fused launch and the exchange take the activations with the most work first
@@ -271,9 +287,9 @@ class Job:
         self.fused = self.fused and can_fuse
         grouped = [M > 128 and len(gr["layers"]) <= 8 and all(Nl % 256 == 0 for (_, Nl, _, _) in gr["layers"])
                    for gr in self.groups]
-        # one quantiser launch for all activations of a step where the rows are sharded (small problems
-        # that do not fill the GPU one by one)
-        self.multi_q = self.sharded_q
+        # one quantiser launch for all activations of a step: one wave of CTAs shared out by size instead
+        # of a launch - and a partly filled last wave - per activation
+        self.multi_q = (multi_q is None or multi_q) and self.exchange in ("none", "replicated", "push", "allgather") and nq <= 8
         if self.multi_q:
             nq = 1
         # kernels of this library per step: the quantisers + the GEMM launches (+ the epoch bump)
@@ -303,7 +319,12 @@ class Job:
         probs = []
         for gi in self.order:
             gr = self.groups[gi]
-            out = self.ex.shard(s, gi) if self.ex is not None else mgd.activation_shard(gr["A"][s], self.M, gr["split"], self.world, self.rank)
+            if not self.sharded_q:
+                out = gr["A"][s]
+            elif self.ex is not None:
+                out = self.ex.shard(s, gi)
+            else:
+                out = mgd.activation_shard(gr["A"][s], self.M, gr["split"], self.world, self.rank)
             probs.append((gr["X"], gr["idx"], *gr["split"], out))
         self.mg.reorder_quantize_x_multi(probs)
 
@@ -358,7 +379,12 @@ class Job:
             else:
                 self.fill(s)
             self.multiply(s)
-            self.ex.join()
+            # The copies read this rank's own block of a set that is not written again before the
+            # set comes round, so in the pipelined order the main stream takes them back only at the
+            # end of a round of sets (the unit that is captured and timed): a transfer may then run
+            # on under the next step instead of holding it up.
+            if not self.pipeline or s == self.nsets - 1:
+                self.ex.join()
         elif self.multi_q:
             self.quantize_all(s)
             for gi in self.order:
@@ -486,6 +512,8 @@ def main():
     ap.add_argument("--workload", default=None, choices=list(WORKLOADS))
     ap.add_argument("--exchange", default="push", choices=["push", "allgather", "bcast", "replicated"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--quantize", choices=["each", "multi"], default=None,
+                    help="one quantiser launch per activation, or one for all of a step (default: multi)")
     ap.add_argument("--no-pipeline", action="store_true",
                     help="push exchange: send and multiply the same batch in a step instead of sending batch i + 1 under the GEMM of batch i")
     ap.add_argument("--no-fuse", action="store_true", help="one GEMM launch per activation instead of one over all layers")
@@ -559,7 +587,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    job = Job(wl_name, rank, world, device, a.exchange, fused=not a.no_fuse, pipeline=not a.no_pipeline)
+    job = Job(wl_name, rank, world, device, a.exchange, fused=not a.no_fuse, pipeline=not a.no_pipeline,
+              multi_q=None if a.quantize is None else a.quantize == "multi")
     pk = peaks()
     nsets = job.nsets
 
@@ -624,7 +653,7 @@ def main():
         # The GEMMs are timed both ways: one launch per activation (so that every layer group has its
         # own figure) and the single launch over all layers that the step uses.
         ev = lambda: torch.cuda.Event(enable_timing=True)
-        q_ms, g_ms, q_each, g_each, fused_ms = 0.0, 0.0, [], [], None
+        q_ms, g_ms, q_each, g_each, fused_ms, q_all_ms = 0.0, 0.0, [], [], None, None
         if world == 1:
             reps = max(3, min(a.steps, 10))
             marks = []
@@ -648,6 +677,12 @@ def main():
                     job.gemm_fused()
                     e1.record()
                     marks.append((("f", 0), e0, e1))
+                if job.multi_q:
+                    e0, e1 = ev(), ev()
+                    e0.record()
+                    job.quantize_all()
+                    e1.record()
+                    marks.append((("qa", 0), e0, e1))
             torch.cuda.synchronize()
             acc = {}
             for key, e0, e1 in marks:
@@ -660,6 +695,7 @@ def main():
                 g_each.append((names, job.M, Nsum, gr["K"], acc[("g", gi)]))
                 g_ms += acc[("g", gi)]
             fused_ms = acc.get(("f", 0))
+            q_all_ms = acc.get(("qa", 0))
 
         # ---- end to end: activations from pinned host memory, results back to pinned host memory.
         # Every rank uploads the rows it quantises (all of them on one GPU; M / P with a sharded
@@ -832,9 +868,15 @@ def main():
             "launches_per_activation_us": g_ms * 1e3,
             "launch_all_layers_us": fused_ms * 1e3 if fused_ms is not None else None}
         rbytes = sum(reorder_bytes(job.M, K) for (K, _) in q_each)
+        q_best = q_all_ms if (q_all_ms is not None and job.multi_q) else q_ms
         out["roofline_reorder"] = {
-            "kernel": "reorder_quantize_kernel", "bound": "hbm", "achieved": rbytes / (q_ms * 1e-3) / 1e9,
-            "peak": pk["hbm"], "unit": "GB/s", "frac": rbytes / (q_ms * 1e-3) / 1e9 / pk["hbm"],
+            "kernel": "reorder_quantize_multi_kernel" if q_best is q_all_ms else "reorder_quantize_kernel",
+            "bound": "hbm", "achieved": rbytes / (q_best * 1e-3) / 1e9,
+            "peak": pk["hbm"], "unit": "GB/s", "frac": rbytes / (q_best * 1e-3) / 1e9 / pk["hbm"],
+            "what": ("the step's single quantiser launch over all activations, %.1f us" % (q_best * 1e3)) if q_best is q_all_ms
+            else "the step's quantiser launches, %.1f us together" % (q_best * 1e3),
+            "launches_per_activation_us": q_ms * 1e3,
+            "launch_all_activations_us": q_all_ms * 1e3 if q_all_ms is not None else None,
             # one K=4096 launch under ncu: 16.8 MB read, the 5.3 MB written are still in L2 at kernel end
             "traffic": 16.8e6 if wl_name == "llama3-8b-m2048" else None,
             "traffic_source": "ncu capture at 8192 x 16384 scaled by rows x K, summarised in profiles/reorder_quantize_kernel_8192x16384.md",

@@ -483,22 +483,44 @@ extern "C" int mg_reorder_quantize_multi(int weights, int nprob, const mg_quant_
                      q.SF8, &p);
     if (rc != MG_OK) return rc;
     if (p.rows == 0) continue;
-    bytes[n] = (double)p.rows * p.K;
+    // Cost of a problem = its elements, weighted by how well its rows pipeline: a row must be whole
+    // in shared memory (the index may gather from anywhere in it), so a large K leaves room for only
+    // one or two rows per stage and two or three stages, and a CTA then moves 1.5x / 1.3x fewer bytes
+    // per second than with four or more rows per stage (measured per CTA with all SMs busy).
+    int r_fit = 1;
+    for (int cand : {8, 4, 2})
+      if (smem_bytes(p.K, cand, 2) <= (size_t)di.smem_optin - 1024) { r_fit = cand; break; }
+    bytes[n] = (double)p.rows * p.K * (r_fit == 1 ? 1.48 : r_fit == 2 ? 1.3 : 1.0);
     total += bytes[n];
     ++n;
   }
   if (n == 0) return MG_OK;
-  // CTAs in proportion to the bytes, at least one and at most one per row; one CTA per SM in all
+  // CTAs in proportion to the cost, at least one and at most one per row; one CTA per SM in all
   int sms = di.sm_count;
   const int cap = mg::options().reorder_ctas;
   if (cap > 0 && sms > cap) sms = cap;
   if (sms < n) sms = n;
-  int grid = 0;
-  size_t smem = 0;
+  int share[kMaxQuant], used = 0;
   for (int j = 0; j < n; ++j) {
     int g = (int)(sms * bytes[j] / total);
     if (g < 1) g = 1;
     if (g > mp.prob[j].rows) g = mp.prob[j].rows;
+    share[j] = g;
+    used += g;
+  }
+  // what rounding down left over goes, one CTA at a time, to the problem whose CTAs carry the most
+  while (used < sms) {
+    int best = -1;
+    for (int j = 0; j < n; ++j)
+      if (share[j] < mp.prob[j].rows && (best < 0 || bytes[j] / share[j] > bytes[best] / share[best])) best = j;
+    if (best < 0) break;
+    ++share[best];
+    ++used;
+  }
+  int grid = 0;
+  size_t smem = 0;
+  for (int j = 0; j < n; ++j) {
+    const int g = share[j];
     const size_t sm = stage_shape(&mp.prob[j], g, (size_t)di.smem_optin, &mp.rows_per_stage[j]);
     if (sm == 0) return MG_ERR_SHAPE;
     if (sm > smem) smem = sm;

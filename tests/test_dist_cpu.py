@@ -107,3 +107,29 @@ def test_shard_helpers():
     want = full[orc.sf_offset(r, kb, 448)]
     got = mgd.sf_shard(torch.from_numpy(full), 512, 448, 2, 1).numpy()[orc.sf_offset(r - 256, kb, 448)]
     assert np.array_equal(got, want)
+
+
+def test_sharded_activation_describes_equally_spaced_blocks():
+    """api.ShardedActivation (the layout the overlapped exchange fills, one block per rank) works out
+    the shard strides from the tensors it is given and refuses anything but equal, equally spaced,
+    ascending shards of whole 128-row scale blocks.  Host logic only: CPU tensors."""
+    from mixedgemm_b200.api import ShardedActivation
+    mp_, block = 128, 40960
+    flat = torch.zeros(4 * block, dtype=torch.uint8)
+
+    def shard(r, rows=mp_):
+        blk = flat[r * block:(r + 1) * block]
+        return (blk[0:rows * 64].view(rows, 64), blk[8192:8192 + rows * 48].view(rows, 48),
+                blk[16384:16384 + rows * 128].view(rows, 128)[:, :64], blk[32768:33280], blk[33792:34304], blk[34816:35328])
+
+    sa = ShardedActivation([shard(r) for r in range(4)])
+    assert sa.rows == 512 and sa.shard_rows == 128 and sa.stride == [block] * 6
+    assert ShardedActivation([shard(0)]).rows == 128
+    with pytest.raises(RuntimeError):
+        ShardedActivation([shard(1), shard(0)])              # descending
+    with pytest.raises(RuntimeError):
+        ShardedActivation([shard(0), shard(1), shard(3)])    # not equally spaced
+    with pytest.raises(RuntimeError):
+        ShardedActivation([shard(0, 64), shard(1, 64)])      # not whole scale blocks
+    with pytest.raises(RuntimeError):
+        ShardedActivation([shard(0), shard(1)[:5]])          # not six tensors
