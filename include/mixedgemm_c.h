@@ -77,6 +77,7 @@ int mg_set_wait_limit_us(long long us);
  *   GEMM_CSPLIT      0: cluster split-K off
  *   GEMM_SPLITK      0: split-K through the workspace off;  n > 0: n splits
  *   GEMM_SWAP        0 / 1: decode form off / on for every M <= 128
+ *   GEMM_SCHED       0: tiles of a multi-problem launch dealt out round-robin, not by cost
  *   PDL              0: no programmatic dependent launch
  *   REORDER_CTAS     n > 0: at most n CTAs for the quantiser (to share the GPU with another kernel)
  *   FAULT_SKIP_LOAD  n > 0: host-side fault injection for tests - the first CTA of the single-CTA

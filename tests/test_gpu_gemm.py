@@ -597,6 +597,30 @@ def test_row_sharded_activation_equals_the_contiguous_one(mgopt):
         mg.ShardedActivation([shards[0], tuple(t[:64] if t.dim() == 2 else t for t in shards[1])])
 
 
+def test_cost_balanced_tile_schedule_equals_separate_calls(mgopt):
+    """More tiles than SM pairs, and tiles of different cost (K): the launch then follows the host's
+    schedule table (each tile to the SM pair that is free first) instead of dealing the tiles out
+    round-robin.  Every tile must still be computed exactly once, whatever pair it lands on."""
+    import mixedgemm_b200 as mg
+    mgopt.setenv("MG_GEMM_CSPLIT", "0")
+    mgopt.setenv("MG_GEMM_SPLITK", "0")
+    shapes = [(2048, 2048, (2560, 1408, 128)), (1024, 1024, (8960, 4928, 448)), (512, 4096, (1280, 640, 128)),
+              (300, 512, (128, 0, 0))]
+    probs = []
+    for j, (M, N, split) in enumerate(shapes):
+        A, B = _quantise(M, N, sum(split), split, seed=110 + j)
+        probs.append((A, B, torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")))
+    for order in ([0, 1, 2, 3], [3, 1, 0, 2]):
+        for (_, _, o) in probs:
+            o.fill_(7.0)
+        outs = mg.matmul_multi([probs[j] for j in order])
+        torch.cuda.synchronize()
+        assert mg.device_status() == 0
+        for j, y in zip(order, outs):
+            A, B, _ = probs[j]
+            assert torch.equal(y.view(torch.int16), mg.matmul(*_abargs(A, B)).view(torch.int16)), (order, j)
+
+
 def test_ready_flag_holds_a_problem_back_until_its_activation_is_there(mgopt):
     """A problem with a ready flag is not read before the flag reaches its value: the activation is
     filled, and the flag raised, by copy-engine copies on another stream AFTER the launch."""
