@@ -856,10 +856,9 @@ def main():
             "frac_sustained": achieved_t / peak_s, "peak_burst": peak_b, "frac_burst": achieved_t / peak_b,
             "what": ("the step's single GEMM launch over all layers, %.1f us" % (g_best * 1e3)) if job.fused and fused_ms
             else "the step's GEMM launches, %.1f us together" % (g_best * 1e3),
-            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the largest GEMM of the set
-            # (gate/up, 2048 x 14336 x 4096) under ncu
-            "traffic": 50.6e6 if wl_name == "llama3-8b-m2048" else None,
-            "traffic_source": "ncu capture of the 2048 x 14336 x 4096 launch, summarised in profiles/mixed_gemm_pair_kernel_2048x14336x4096.md",
+            # dram__bytes_read.sum + dram__bytes_write.sum of the step's launch over all layers under ncu
+            "traffic": 290.1e6 if (wl_name == "llama3-8b-m2048" and job.fused) else None,
+            "traffic_source": "ncu capture of the step's launch, summarised in profiles/mixed_gemm_pair_kernel_llama3-8b-m2048_step.md",
             "peak_note": ("%s copy bandwidth" % pk["source"]) if job.M <= 128 else
             "K-blended tensor peak: fp4 segment at 4x and fp6/fp8 at 2x the %s bf16 rate (sustained %.1f, burst %.1f TF/s)" % (
                 pk["source"], pk["bf16_sustained"], pk["bf16"]),
@@ -877,9 +876,10 @@ def main():
             else "the step's quantiser launches, %.1f us together" % (q_best * 1e3),
             "launches_per_activation_us": q_ms * 1e3,
             "launch_all_activations_us": q_all_ms * 1e3 if q_all_ms is not None else None,
-            # one K=4096 launch under ncu: 16.8 MB read, the 5.3 MB written are still in L2 at kernel end
-            "traffic": 16.8e6 if wl_name == "llama3-8b-m2048" else None,
-            "traffic_source": "ncu capture at 8192 x 16384 scaled by rows x K, summarised in profiles/reorder_quantize_kernel_8192x16384.md",
+            # the step's launch over the four activations under ncu: 109.3 MB read, 14.5 of the 34.5 MB
+            # written have left L2 when the kernel ends
+            "traffic": 123.8e6 if (wl_name == "llama3-8b-m2048" and q_best is q_all_ms) else None,
+            "traffic_source": "ncu capture of the step's launch, summarised in profiles/reorder_quantize_multi_kernel_llama3-8b-m2048_step.md",
             "peak_note": "%s copy bandwidth" % pk["source"],
             "launches": [{"M": job.M, "K": K, "us": t * 1e3, "gbs": reorder_bytes(job.M, K) / (t * 1e-3) / 1e9}
                          for (K, t) in q_each]}
