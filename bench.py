@@ -2,7 +2,7 @@
 """Benchmark of the hot path: activation reorder-and-quantise + mixed MXFP4/6/8 GEMM.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                  [--workload NAME] [--exchange push|allgather|bcast|replicated] [--no-graph] [--no-fuse]
+                  [--workload NAME] [--exchange push|push-ce|allgather|bcast|replicated] [--no-graph] [--no-fuse]
   python bench.py --kernel gemm|reorder --shape M,N,K     one kernel, one shape
   python bench.py --sweep decode|square|all               the other benchmark configurations, a line per shape
 
@@ -13,9 +13,12 @@ launch.  Weights are quantised once, outside the timed region, as in deployment.
 
   N = 1 (default)   workload llama3-8b-m2048 (M = 2048 tokens on the Llama-3-8B projections)
   N > 1             workload llama3-70b-m4096: weights sharded along N over the ranks.  --exchange
-                    push (default): every rank quantises M / P rows and pushes them into every
-                    peer's buffer with copy-engine copies over NVLink while the GEMM, already
-                    launched, waits row shard by row shard for the flags that follow the data;
+                    push (default): every rank quantises its M / P rows of all activations with one
+                    launch and a small kernel stores them into every peer's buffer over NVLink,
+                    on the same SMs as - and hidden under - the GEMM of the batch before (the
+                    exchange runs one step ahead; --no-pipeline sends and multiplies the same
+                    batch in a step); the GEMM's producer waits for the flags that follow the data;
+                    push-ce: the same with one copy-engine copy per peer instead of the kernel;
                     allgather: the same rows, completed by NCCL all-gathers before the GEMM;
                     bcast: rank 0 quantises, NCCL broadcast; replicated: every rank quantises
                     everything, nothing is exchanged
@@ -202,6 +205,9 @@ class Job:
         wl = WORKLOADS[wl_name]
         self.M = M = wl["M"]
         self.rank, self.world, self.device = rank, world, device
+        self.push_mode = "ce" if exchange == "push-ce" else "sm"
+        if exchange == "push-ce":
+            exchange = "push"
         self.exchange = exchange if world > 1 else "none"
         self.fused = fused
         self.sharded_q = self.exchange in ("push", "allgather")  # every rank quantises M / P rows
@@ -272,7 +278,8 @@ class Job:
             from mixedgemm_b200 import dist as mgd
             # buffer sets used in turn: a rank may push a later step while a peer still multiplies this one
             self.nsets = 4 if self.pipeline else 2
-            self.ex = mgd.PushExchange([(M, gr["split"]) for gr in self.groups], world, rank, device, n_sets=self.nsets)
+            self.ex = mgd.PushExchange([(M, gr["split"]) for gr in self.groups], world, rank, device, n_sets=self.nsets,
+                                       mode=self.push_mode)
             for gi, gr in enumerate(self.groups):
                 gr["A"] = [self.ex.buffers(s, gi) for s in range(self.nsets)]
         else:
@@ -294,7 +301,7 @@ class Job:
             nq = 1
         # kernels of this library per step: the quantisers + the GEMM launches (+ the epoch bump)
         self.n_kernels = nq + (1 if self.fused else sum(1 if g_ else len(gr["layers"]) for g_, gr in zip(grouped, self.groups)))
-        self.n_kernels += 1 if self.ex is not None else 0
+        self.n_kernels += (2 if self.push_mode == "sm" else 1) if self.ex is not None else 0  # epoch bump (+ push kernel)
         self.reorder_bytes = sum(reorder_bytes(gr["X"].size(0), gr["K"]) for gr in self.groups)
         torch.cuda.synchronize()
 
@@ -510,7 +517,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=list(WORKLOADS))
-    ap.add_argument("--exchange", default="push", choices=["push", "allgather", "bcast", "replicated"])
+    ap.add_argument("--exchange", default="push", choices=["push", "push-ce", "allgather", "bcast", "replicated"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--quantize", choices=["each", "multi"], default=None,
                     help="one quantiser launch per activation, or one for all of a step (default: multi)")
@@ -825,7 +832,7 @@ def main():
         "config": {"workload": wl_name, "M": job.M,
                    "layers": [[gr["K"], [[n, N * world] for (n, N, _, _) in gr["layers"]]] for gr in job.groups],
                    "k_split": "62.5% fp4 / 34.375% fp6 / 3.125% fp8", "parallelism": "n-shard x%d" % world,
-                   "exchange": job.exchange, "cuda_graph": use_graph,
+                   "exchange": (job.exchange + ("/" + job.push_mode if job.ex is not None else "")), "cuda_graph": use_graph,
                    "pipeline": ("every step quantises and sends batch i + 1 (one quantiser launch, one copy per peer) and "
                                 "multiplies batch i, which the step before sent; %d buffer sets in turn" % job.nsets)
                    if job.pipeline else None,

@@ -328,6 +328,16 @@ int mg_ipc_close(void* ptr);
 int mg_epoch_bump(int* epoch_word, void* stream);
 int mg_push_shard(int world, int rank, void* const* bases, const size_t* seg_off, const size_t* seg_bytes, int nseg,
                   size_t flag_off, const int* epoch_word, void* const* streams);
+/*
+ * The same push made by a kernel instead of the copy engines: `ctas` CTAs (0 = one per SM) copy the
+ * block [block_off, block_off + block_bytes) of bases[rank] into the same place of every other rank's
+ * buffer with plain peer stores, and the CTA that finishes last writes *epoch_word into this rank's
+ * flag word (flag_off + 4 rank) on every rank, its own included.  The kernel uses no shared memory
+ * and few registers, so it runs beside a GEMM on the same SMs; one launch, no per-copy latency.
+ * `counter` is a zeroed device word that the kernel leaves at zero.  world <= 16.
+ */
+int mg_push_block(int world, int rank, void* const* bases, size_t block_off, size_t block_bytes, size_t flag_off,
+                  const int* epoch_word, int* counter, int ctas, void* stream);
 
 /*
  * mg_matmul for callers that cannot allocate.  No counterpart in the reference (its binding

@@ -26,6 +26,7 @@ PROTOTYPES = {
     "mg_reset_options": (None, []),
     "mg_matmul_multi": (_i, [_i, _vp, _vp]),
     "mg_reorder_quantize_multi": (_i, [_i, _i, _vp, _vp]),
+    "mg_push_block": (_i, [_i, _i, _vp, _sz, _sz, _sz, _vp, _vp, _i, _vp]),
     "mg_dist_unique_id": (_i, [_vp]),
     "mg_dist_init": (_i, [ctypes.POINTER(_vp), _vp, _i, _i]),
     "mg_dist_destroy": (_i, [_vp]),

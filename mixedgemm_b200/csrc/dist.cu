@@ -71,6 +71,48 @@ struct Comm {
 
 __global__ void epoch_bump_kernel(int* word) { *word += 1; }
 
+// The same push made by the SMs: every CTA copies a share of this rank's block into every peer's
+// buffer with 16-byte loads and plain peer stores; the CTA that finishes last raises this rank's
+// flag on every rank.  It uses no shared memory and few registers, so its CTAs sit beside the
+// GEMM's on the same SMs (whose warps issue on a tenth of the cycles) and the transfer runs under
+// the GEMM without a copy engine's per-copy latency.
+constexpr int kMaxPeers = 15;
+struct PushParams {
+  const uint4* src;
+  uint4* dst[kMaxPeers];   // the block's place in each peer's buffer, nearest peer first
+  int* flag[kMaxPeers + 1];  // this rank's flag word on each peer, then on this rank itself
+  int npeers;
+  size_t n16;
+  const int* epoch_word;
+  int* counter;  // CTAs that have finished (returns to zero)
+};
+
+__global__ void __launch_bounds__(512) push_block_kernel(const __grid_constant__ PushParams p) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n16; i += stride) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p.src + i));
+#pragma unroll 1
+    for (int q = 0; q < p.npeers; ++q) p.dst[q][i] = v;
+  }
+  // release: every thread's stores, then the CTA's arrival; the last CTA's flag stores come after
+  // every other CTA's arrival, hence after their stores
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(p.counter, 1);
+    if (done == (int)gridDim.x - 1) {
+      *p.counter = 0;
+      __threadfence_system();
+      const int e = *reinterpret_cast<const volatile int*>(p.epoch_word);
+      for (int q = 0; q <= p.npeers; ++q)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.flag[q]), "r"(e) : "memory");
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" int mg_dist_unique_id(void* id128) {
@@ -222,5 +264,39 @@ extern "C" int mg_push_shard(int world, int rank, void* const* bases, const size
     // stream order: the flag leaves after the data has arrived
     MG_CUDA_TRY(cudaMemcpyAsync(dst + flag_off + (size_t)rank * sizeof(int), epoch_word, sizeof(int), cudaMemcpyDefault, st));
   }
+  return MG_OK;
+}
+
+extern "C" int mg_push_block(int world, int rank, void* const* bases, size_t block_off, size_t block_bytes,
+                             size_t flag_off, const int* epoch_word, int* counter, int ctas, void* stream) {
+  if (!bases || !epoch_word || !counter) return MG_ERR_NULL;
+  if (world < 1 || world > kMaxPeers + 1 || rank < 0 || rank >= world || ctas < 0) return MG_ERR_SHAPE;
+  if (block_bytes % 16 || block_off % 16 || flag_off % 4) return MG_ERR_ALIGN;
+  PushParams p{};
+  uint8_t* mine = static_cast<uint8_t*>(bases[rank]);
+  if (!mine) return MG_ERR_NULL;
+  p.src = reinterpret_cast<const uint4*>(mine + block_off);
+  p.npeers = world - 1;
+  for (int step = 1; step < world; ++step) {
+    // ring order downwards from this rank, as in mg_push_shard
+    uint8_t* peer = static_cast<uint8_t*>(bases[(rank - step + world) % world]);
+    if (!peer) return MG_ERR_NULL;
+    if (!mg::aligned(peer, 16)) return MG_ERR_ALIGN;
+    p.dst[step - 1] = reinterpret_cast<uint4*>(peer + block_off);
+    p.flag[step - 1] = reinterpret_cast<int*>(peer + flag_off) + rank;
+  }
+  if (!mg::aligned(mine, 16)) return MG_ERR_ALIGN;
+  p.flag[world - 1] = reinterpret_cast<int*>(mine + flag_off) + rank;
+  p.n16 = block_bytes / 16;
+  p.epoch_word = epoch_word;
+  p.counter = counter;
+  mg::DeviceInfo di;
+  int rc = mg::device_info(&di);
+  if (rc != MG_OK) return rc;
+  int grid = ctas > 0 ? ctas : di.sm_count;
+  const size_t need = (p.n16 + 511) / 512;
+  if ((size_t)grid > need) grid = need ? (int)need : 1;
+  push_block_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  MG_CUDA_TRY(cudaGetLastError());
   return MG_OK;
 }

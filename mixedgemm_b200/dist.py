@@ -172,20 +172,27 @@ class PushExchange:
     the activations of one step).  A set is one device allocation, laid out identically on every rank
     and opened on every other rank through CUDA IPC.  It is stored rank by rank: everything rank r
     quantises in a step - its M/P rows of every activation, each as three code tensors at their row
-    pitch followed by their three scale tensors - is ONE contiguous block, so that a step's push is
-    one large copy per peer (small copies reach a fraction of the NVLink rate, and every copy costs
-    tens of microseconds of latency), followed by `world` flag words.  The GEMM reads that layout in
-    place (api.ShardedActivation).
+    pitch followed by their three scale tensors - is ONE contiguous block, followed by `world` flag
+    words.  A step's push is then either one kernel that reads the block once and stores it into every
+    peer's set (mode "sm", mg_push_block: no shared memory, 30 registers, so it runs on the same SMs
+    as the GEMM that is multiplying the step before), or one large copy-engine copy per peer (mode
+    "ce", mg_push_shard: small copies reach a fraction of the NVLink rate, every copy costs tens of
+    microseconds of latency, and copies to several peers at once share the engines badly).  The GEMM
+    reads that layout in place (api.ShardedActivation).
 
     How many sets: a rank may run ahead of a peer by the steps the caller keeps in flight.  When a
     step pushes, multiplies and joins the same set, 2 sets are enough; when the push of step i + 1 is
     issued before the GEMM of step i (so that the transfer hides under it), a set is overwritten three
     steps after it was read and 4 are needed."""
 
-    def __init__(self, shapes, world, rank, device, n_sets=2, group=None):
+    def __init__(self, shapes, world, rank, device, n_sets=2, group=None, mode="sm", push_ctas=0):
         from .api import ShardedActivation
+        if mode not in ("sm", "ce"):
+            raise ValueError("mode is 'sm' (a kernel stores into the peers' buffers) or 'ce' (copy engines)")
         self.lib = lib = _capi.load()
         self.world, self.rank, self.device = world, rank, device
+        self.mode, self.push_ctas = mode, push_ctas
+        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
         self.shapes = list(shapes)
         self.epoch = torch.zeros(n_sets, dtype=torch.int32, device=device)
         self.streams = [torch.cuda.Stream(device=device) for _ in range(max(world - 1, 1))]
@@ -267,6 +274,15 @@ class PushExchange:
         b = self.sets[set_index]
         done = torch.cuda.Event()
         done.record()
+        if self.mode == "sm":
+            # one kernel on one side stream: it shares the SMs with whatever the current stream runs next
+            st = self.streams[0]
+            st.wait_event(done)
+            _capi.check(self.lib.mg_push_block(
+                self.world, self.rank, _vp_array(b["bases"]), self.rank * self.block_bytes, self.block_bytes,
+                self.flag_off, self.epoch[set_index:].data_ptr(), self.counter.data_ptr(), self.push_ctas,
+                st.cuda_stream), "mg_push_block")
+            return
         for st in self.streams:
             st.wait_event(done)
         _capi.check(self.lib.mg_push_shard(

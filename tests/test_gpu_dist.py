@@ -90,51 +90,63 @@ def _worker(rank, world, port, ret):
             Af = mg.reorder_quantize_x(X, idx2, *SPLIT2, M, N2)
             return mg.matmul(*ab(Af, B2full))
 
-        ex = mgd.PushExchange([(M, SPLIT), (M, SPLIT2)], world, rank, dev, n_sets=4)
         rows = slice(rank * mp_, (rank + 1) * mp_)
-
-        def fill(step, s):
-            ex.begin_step(s)
-            mg.reorder_quantize_x_multi([(Xs[step][rows].contiguous(), idx, KN, KS, KO, ex.shard(s, 0)),
-                                         (X2s[step][rows].contiguous(), idx2, *SPLIT2, ex.shard(s, 1))])
-            ex.push(s)
-
-        def multiply(s):
-            return mg.matmul_multi([(ex.buffers(s, 0), Bl, None), (ex.buffers(s, 1), B2l, None)],
-                                   flags=[ex.ready(s, 0), ex.ready(s, 1)])
-
-        def check(step, outs):
-            a = torch.equal(outs[0].view(torch.int16), reference(Xs[step])[:, n0:n0 + nl].contiguous().view(torch.int16))
-            b = torch.equal(outs[1].view(torch.int16), reference2(X2s[step])[:, m0:m0 + ml].contiguous().view(torch.int16))
-            return bool(a and b)
-
-        good = True
-        for step in range(4):
-            s = step % 2
-            fill(step, s)
-            outs = multiply(s)
-            ex.join()
-            good &= check(step, outs)
-        torch.cuda.synchronize()
-        dist.barrier()
-        piped = True
-        fill(0, 0)
-        for step in range(4):
-            if step + 1 < 4:
-                fill(step + 1, (step + 1) % 4)
-            outs = multiply(step % 4)
-            ex.join()
-            piped &= check(step, outs)
-        ok["pipelined"] = piped
-        torch.cuda.synchronize()
-        ok["push"] = good
+        good, piped = True, True
+        for mode in ("sm", "ce"):       # a kernel's peer stores / copy-engine copies
+            ex = mgd.PushExchange([(M, SPLIT), (M, SPLIT2)], world, rank, dev, n_sets=4, mode=mode)
+            g_, p_ = _push_steps(mg, ex, Xs, X2s, idx, idx2, (KN, KS, KO), SPLIT2, rows, Bl, B2l, reference, reference2,
+                                 (n0, nl), (m0, ml))
+            good &= g_
+            piped &= p_
+            torch.cuda.synchronize()
+            dist.barrier()
+            ex.close()
+            dist.barrier()
+        ok["push"], ok["pipelined"] = good, piped
         ok["status"] = mg.device_status()
-        dist.barrier()
-        ex.close()
         ret[rank] = ok
         dist.barrier()
     finally:
         dist.destroy_process_group()
+
+
+def _push_steps(mg, ex, Xs, X2s, idx, idx2, split, SPLIT2, rows, Bl, B2l, reference, reference2, ncols, mcols):
+    import torch.distributed as dist
+    KN, KS, KO = split
+    (n0, nl), (m0, ml) = ncols, mcols
+    def fill(step, s):
+        ex.begin_step(s)
+        mg.reorder_quantize_x_multi([(Xs[step][rows].contiguous(), idx, KN, KS, KO, ex.shard(s, 0)),
+                                     (X2s[step][rows].contiguous(), idx2, *SPLIT2, ex.shard(s, 1))])
+        ex.push(s)
+
+    def multiply(s):
+        return mg.matmul_multi([(ex.buffers(s, 0), Bl, None), (ex.buffers(s, 1), B2l, None)],
+                               flags=[ex.ready(s, 0), ex.ready(s, 1)])
+
+    def check(step, outs):
+        a = torch.equal(outs[0].view(torch.int16), reference(Xs[step])[:, n0:n0 + nl].contiguous().view(torch.int16))
+        b = torch.equal(outs[1].view(torch.int16), reference2(X2s[step])[:, m0:m0 + ml].contiguous().view(torch.int16))
+        return bool(a and b)
+
+    good = True
+    for step in range(4):
+        s = step % 2
+        fill(step, s)
+        outs = multiply(s)
+        ex.join()
+        good &= check(step, outs)
+    torch.cuda.synchronize()
+    dist.barrier()
+    piped = True
+    fill(0, 0)
+    for step in range(4):
+        if step + 1 < 4:
+            fill(step + 1, (step + 1) % 4)
+        outs = multiply(step % 4)
+        ex.join()
+        piped &= check(step, outs)
+    return good, piped
 
 
 def test_two_gpu_n_sharded_gemm_equals_single_gpu():
@@ -146,3 +158,39 @@ def test_two_gpu_n_sharded_gemm_equals_single_gpu():
     for rank in (0, 1):
         assert ret[rank]["bcast"] and ret[rank]["allgather"] and ret[rank]["push"] and ret[rank]["pipelined"], dict(ret[rank])
         assert ret[rank]["status"] == 0
+
+
+def test_push_kernel_on_one_gpu():
+    """mg_push_block with every "rank's" buffer on this GPU: each rank's block lands in every buffer,
+    every flag word carries the epoch, the arrival counter is back at zero; block sizes that do not
+    fill the last CTA, a capped grid, and the argument checks."""
+    import ctypes
+    from mixedgemm_b200 import _capi
+    lib = _capi.load()
+    dev = torch.device("cuda", 0)
+    for world, block, ctas in ((4, 16 * 1237, 0), (8, 16 * 70001, 0), (2, 1 << 20, 3), (16, 4096, 1)):
+        flag_off = world * block
+        total = flag_off + 4 * world
+        bufs = [torch.zeros(total, dtype=torch.uint8, device=dev) for _ in range(world)]
+        want = [torch.randint(0, 256, (block,), dtype=torch.uint8, device=dev) for _ in range(world)]
+        bases = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+        epoch = torch.full((1,), 5, dtype=torch.int32, device=dev)
+        counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        for r in range(world):
+            bufs[r][r * block:(r + 1) * block] = want[r]
+        for r in range(world):
+            st = lib.mg_push_block(world, r, bases, r * block, block, flag_off, epoch.data_ptr(), counter.data_ptr(), ctas, None)
+            assert st == 0
+        torch.cuda.synchronize()
+        assert int(counter.item()) == 0
+        for b in bufs:
+            for r in range(world):
+                assert torch.equal(b[r * block:(r + 1) * block], want[r]), (world, r)
+            assert torch.all(b[flag_off:].view(torch.int32) == 5)
+    bases = (ctypes.c_void_p * 2)(bufs[0].data_ptr(), bufs[1].data_ptr())
+    e, c = epoch.data_ptr(), counter.data_ptr()
+    assert lib.mg_push_block(2, 0, bases, 0, 24, 4096, e, c, 0, None) == 3        # MG_ERR_ALIGN: not whole 16 bytes
+    assert lib.mg_push_block(17, 0, bases, 0, 32, 4096, e, c, 0, None) == 1       # MG_ERR_SHAPE: more than 16 ranks
+    assert lib.mg_push_block(2, 2, bases, 0, 32, 4096, e, c, 0, None) == 1
+    assert lib.mg_push_block(2, 0, bases, 0, 32, 4096, None, c, 0, None) == 2     # MG_ERR_NULL
+    assert lib.mg_push_block(2, 0, None, 0, 32, 4096, e, c, 0, None) == 2

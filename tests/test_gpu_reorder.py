@@ -203,3 +203,43 @@ def test_multi_problem_launch_equals_separate_calls():
     assert torch.equal(two[1][0], want[0][0]) and two[0][0].shape == (0, 128)
     with pytest.raises(RuntimeError):
         mg.reorder_quantize_x_multi([probs[0]] * 9)
+
+
+def test_multi_problem_launch_of_weights_through_the_c_abi():
+    """mg_reorder_quantize_multi with weights = 1 (every segment to E2M1): the bytes of
+    reorder_quantize_w, problem by problem, and the argument checks of the entry point."""
+    import ctypes
+    import mixedgemm_b200 as mg
+    from mixedgemm_b200 import _capi
+    lib = _capi.load()
+    shapes = [(512, (2560, 1408, 128)), (1024, (256, 128, 128)), (128, (5120, 2816, 256))]   # whole scale atoms
+    arr = (_capi.QuantProblem * len(shapes))()
+    keep, want = [], []
+    rng = np.random.default_rng(11)
+    for j, (N, split) in enumerate(shapes):
+        K = sum(split)
+        W = H.make_w(N, K, seed=300 + j).cuda()
+        idx = torch.from_numpy(rng.permutation(K).astype(np.int16)).cuda()
+        out = mg.alloc_quantized_w(N, *split, W.device)
+        keep.append((W, idx, out))
+        want.append(mg.reorder_quantize_w(W, idx, *split))
+        q = arr[j]
+        q.X, q.rows, q.K, q.idx = W.data_ptr(), N, K, idx.data_ptr()
+        q.KN, q.KS, q.KO = split
+        q.C4, q.C6, q.C8 = out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr()
+        for i in range(3):
+            q.pitch[i] = out[i].stride(0)
+        q.SF4, q.SF6, q.SF8 = out[3].data_ptr(), out[4].data_ptr(), out[5].data_ptr()
+    st = lib.mg_reorder_quantize_multi(1, len(shapes), ctypes.cast(arr, ctypes.c_void_p), None)
+    assert st == 0
+    torch.cuda.synchronize()
+    for (N, split), (_, _, out), w in zip(shapes, keep, want):
+        for i in range(3):
+            assert torch.equal(out[i], w[i]), (N, split, i)
+            n = mg.sf_bytes(N, split[i])
+            assert torch.equal(out[3 + i][:n], w[3 + i][:n])
+    assert lib.mg_reorder_quantize_multi(1, 9, ctypes.cast(arr, ctypes.c_void_p), None) == 1     # MG_ERR_SHAPE
+    assert lib.mg_reorder_quantize_multi(1, 2, None, None) == 2                                  # MG_ERR_NULL
+    assert lib.mg_reorder_quantize_multi(1, 0, None, None) == 0
+    arr[1].K = 500                                                                               # K != KN + KS + KO
+    assert lib.mg_reorder_quantize_multi(1, 3, ctypes.cast(arr, ctypes.c_void_p), None) == 1
