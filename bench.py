@@ -2,7 +2,7 @@
 """Benchmark of the hot path: activation reorder-and-quantise + mixed MXFP4/6/8 GEMM.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                  [--workload NAME] [--exchange push|push-ce|allgather|bcast|replicated] [--no-graph] [--no-fuse]
+                  [--workload NAME] [--exchange push|push-ce|push-sm|allgather|bcast|replicated] [--no-graph] [--no-fuse]
   python bench.py --kernel gemm|reorder --shape M,N,K     one kernel, one shape
   python bench.py --sweep decode|square|all               the other benchmark configurations, a line per shape
 
@@ -14,11 +14,13 @@ launch.  Weights are quantised once, outside the timed region, as in deployment.
   N = 1 (default)   workload llama3-8b-m2048 (M = 2048 tokens on the Llama-3-8B projections)
   N > 1             workload llama3-70b-m4096: weights sharded along N over the ranks.  --exchange
                     push (default): every rank quantises its M / P rows of all activations with one
-                    launch and a small kernel stores them into every peer's buffer over NVLink,
-                    on the same SMs as - and hidden under - the GEMM of the batch before (the
-                    exchange runs one step ahead; --no-pipeline sends and multiplies the same
-                    batch in a step); the GEMM's producer waits for the flags that follow the data;
-                    push-ce: the same with one copy-engine copy per peer instead of the kernel;
+                    launch and sends them into every peer's buffer over NVLink - with one copy-engine
+                    copy per peer, or with a small kernel that keeps a few SMs to itself - hidden
+                    under the GEMM of the batch before (the exchange runs one step ahead;
+                    --no-pipeline sends and multiplies the same batch in a step); the GEMM's
+                    producer waits for the flags that follow the data;
+                    push-ce / push-sm: force copy-engine copies (one per peer; the default up to four
+                    GPUs) or the kernel (eight SMs of its own; the default beyond);
                     allgather: the same rows, completed by NCCL all-gathers before the GEMM;
                     bcast: rank 0 quantises, NCCL broadcast; replicated: every rank quantises
                     everything, nothing is exchanged
@@ -205,8 +207,11 @@ class Job:
         wl = WORKLOADS[wl_name]
         self.M = M = wl["M"]
         self.rank, self.world, self.device = rank, world, device
-        self.push_mode = "ce" if exchange == "push-ce" else "sm"
-        if exchange == "push-ce":
+        # the push: copy engines up to four GPUs (their all-to-all rate is enough to hide under the GEMM
+        # there and they cost no SM), a kernel on eight SMs of its own beyond that
+        self.push_mode = {"push-ce": "ce", "push-sm": "sm"}.get(exchange, "ce" if world <= 4 else "sm")
+        self.push_ctas = 8
+        if exchange in ("push-ce", "push-sm"):
             exchange = "push"
         self.exchange = exchange if world > 1 else "none"
         self.fused = fused
@@ -279,7 +284,11 @@ class Job:
             # buffer sets used in turn: a rank may push a later step while a peer still multiplies this one
             self.nsets = 4 if self.pipeline else 2
             self.ex = mgd.PushExchange([(M, gr["split"]) for gr in self.groups], world, rank, device, n_sets=self.nsets,
-                                       mode=self.push_mode)
+                                       mode=self.push_mode, push_ctas=self.push_ctas)
+            if self.push_mode == "sm":
+                # the GEMM leaves the push kernel's SM pairs alone
+                mg.set_option("GEMM_MAX_CLUSTERS", torch.cuda.get_device_properties(device).multi_processor_count // 2
+                              - self.push_ctas // 2)
             for gi, gr in enumerate(self.groups):
                 gr["A"] = [self.ex.buffers(s, gi) for s in range(self.nsets)]
         else:
@@ -517,7 +526,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=list(WORKLOADS))
-    ap.add_argument("--exchange", default="push", choices=["push", "push-ce", "allgather", "bcast", "replicated"])
+    ap.add_argument("--exchange", default="push", choices=["push", "push-ce", "push-sm", "allgather", "bcast", "replicated"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--quantize", choices=["each", "multi"], default=None,
                     help="one quantiser launch per activation, or one for all of a step (default: multi)")
@@ -791,6 +800,7 @@ def main():
         # not have to be taken against the (smaller) default workload of `--gpus 1`: rank 0 alone,
         # all weights, same graph-replay timing, while the other ranks wait.
         if rank == 0:
+            job.mg.set_option("GEMM_MAX_CLUSTERS", 0)  # the single-GPU figure uses every SM pair
             job1 = Job(wl_name, 0, 1, device, "none", fused=not a.no_fuse)
             with torch.cuda.stream(stream):
                 for _ in range(a.warmup):

@@ -78,6 +78,8 @@ int mg_set_wait_limit_us(long long us);
  *   GEMM_SPLITK      0: split-K through the workspace off;  n > 0: n splits
  *   GEMM_SWAP        0 / 1: decode form off / on for every M <= 128
  *   GEMM_SCHED       0: tiles of a multi-problem launch dealt out round-robin, not by cost
+ *   GEMM_MAX_CLUSTERS n > 0: the CTA-pair kernel uses at most n SM pairs (to leave SMs to a kernel that
+ *                    runs beside it, e.g. mg_push_block)
  *   PDL              0: no programmatic dependent launch
  *   REORDER_CTAS     n > 0: at most n CTAs for the quantiser (to share the GPU with another kernel)
  *   FAULT_SKIP_LOAD  n > 0: host-side fault injection for tests - the first CTA of the single-CTA
@@ -329,12 +331,16 @@ int mg_epoch_bump(int* epoch_word, void* stream);
 int mg_push_shard(int world, int rank, void* const* bases, const size_t* seg_off, const size_t* seg_bytes, int nseg,
                   size_t flag_off, const int* epoch_word, void* const* streams);
 /*
- * The same push made by a kernel instead of the copy engines: `ctas` CTAs (0 = one per SM) copy the
- * block [block_off, block_off + block_bytes) of bases[rank] into the same place of every other rank's
- * buffer with plain peer stores, and the CTA that finishes last writes *epoch_word into this rank's
- * flag word (flag_off + 4 rank) on every rank, its own included.  The kernel uses no shared memory
- * and few registers, so it runs beside a GEMM on the same SMs; one launch, no per-copy latency.
- * `counter` is a zeroed device word that the kernel leaves at zero.  world <= 16.
+ * The same push made by a kernel instead of the copy engines: the block [block_off, block_off +
+ * block_bytes) of bases[rank] is stored into the same place of every other rank's buffer with plain
+ * peer stores, and the CTA that finishes last writes *epoch_word into this rank's flag word
+ * (flag_off + 4 rank) on every rank, its own included.  One launch, no per-copy latency.
+ * ctas > 0: that many CTAs, each of which claims 32 KB of shared memory it does not use, so that it
+ * does not share its SM with a GEMM or quantiser CTA (sharing slows the GEMM CTA by a third, and a
+ * GEMM ends with its slowest SM pair): launch the GEMM that runs beside it on correspondingly fewer
+ * SM pairs (option GEMM_MAX_CLUSTERS).  ctas == 0: one CTA per SM, no shared memory (for a push that
+ * has the GPU to itself).  `counter` is a zeroed device word that the kernel leaves at zero.
+ * world <= 16.
  */
 int mg_push_block(int world, int rank, void* const* bases, size_t block_off, size_t block_bytes, size_t flag_off,
                   const int* epoch_word, int* counter, int ctas, void* stream);

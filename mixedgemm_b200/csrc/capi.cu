@@ -34,7 +34,7 @@ const OptionSlot kOptionSlots[] = {
     {"GEMM_CSPLIT", &mg::Options::gemm_csplit, -1}, {"GEMM_SPLITK", &mg::Options::gemm_splitk, -1},
     {"GEMM_SWAP", &mg::Options::gemm_swap, -1},     {"PDL", &mg::Options::pdl, 1},
     {"REORDER_CTAS", &mg::Options::reorder_ctas, 0}, {"FAULT_SKIP_LOAD", &mg::Options::fault_skip_load, 0},
-    {"GEMM_SCHED", &mg::Options::gemm_sched, 1},
+    {"GEMM_SCHED", &mg::Options::gemm_sched, 1},    {"GEMM_MAX_CLUSTERS", &mg::Options::gemm_max_clusters, 0},
 };
 mg::Options g_options;
 bool g_options_ready = false;

@@ -71,11 +71,13 @@ struct Comm {
 
 __global__ void epoch_bump_kernel(int* word) { *word += 1; }
 
-// The same push made by the SMs: every CTA copies a share of this rank's block into every peer's
-// buffer with 16-byte loads and plain peer stores; the CTA that finishes last raises this rank's
-// flag on every rank.  It uses no shared memory and few registers, so its CTAs sit beside the
-// GEMM's on the same SMs (whose warps issue on a tenth of the cycles) and the transfer runs under
-// the GEMM without a copy engine's per-copy latency.
+// The same push made by SMs: every CTA copies a share of this rank's block into every peer's buffer
+// with 16-byte loads (four in flight per thread) and plain peer stores; the CTA that finishes last
+// raises this rank's flag on every rank.  One launch, no per-copy latency, and all-to-all traffic at
+// the link rate where concurrent copy-engine copies fall to half of it.  Sharing an SM with a GEMM
+// CTA slows that CTA by a third (measured), and the GEMM ends with its slowest SM pair, so the few
+// CTAs of the default form ask for shared memory they do not use: an SM that holds one has no room
+// for a GEMM or quantiser CTA, and the GEMM is launched on correspondingly fewer SM pairs.
 constexpr int kMaxPeers = 15;
 struct PushParams {
   const uint4* src;
@@ -87,15 +89,30 @@ struct PushParams {
   int* counter;  // CTAs that have finished (returns to zero)
 };
 
-__global__ void __launch_bounds__(512) push_block_kernel(const __grid_constant__ PushParams p) {
+constexpr int kPushThreads = 1024;
+constexpr int kPushUnroll = 8;
+
+__global__ void __launch_bounds__(kPushThreads) push_block_kernel(const __grid_constant__ PushParams p) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n16; i += stride) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p.src + i));
+  for (size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < p.n16; i0 += stride * kPushUnroll) {
+    uint4 v[kPushUnroll];
+#pragma unroll
+    for (int u = 0; u < kPushUnroll; ++u) {
+      const size_t i = i0 + (size_t)u * stride;
+      if (i < p.n16)
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v[u].x), "=r"(v[u].y), "=r"(v[u].z), "=r"(v[u].w)
+                     : "l"(p.src + i));
+    }
 #pragma unroll 1
-    for (int q = 0; q < p.npeers; ++q) p.dst[q][i] = v;
+    for (int q = 0; q < p.npeers; ++q) {
+      uint4* dst = p.dst[q];
+#pragma unroll
+      for (int u = 0; u < kPushUnroll; ++u) {
+        const size_t i = i0 + (size_t)u * stride;
+        if (i < p.n16) dst[i] = v[u];
+      }
+    }
   }
   // release: every thread's stores, then the CTA's arrival; the last CTA's flag stores come after
   // every other CTA's arrival, hence after their stores
@@ -294,9 +311,27 @@ extern "C" int mg_push_block(int world, int rank, void* const* bases, size_t blo
   int rc = mg::device_info(&di);
   if (rc != MG_OK) return rc;
   int grid = ctas > 0 ? ctas : di.sm_count;
-  const size_t need = (p.n16 + 511) / 512;
+  const size_t need = (p.n16 + kPushThreads - 1) / kPushThreads;
   if ((size_t)grid > need) grid = need ? (int)need : 1;
-  push_block_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  MG_CUDA_TRY(cudaGetLastError());
+  // ctas > 0: each CTA claims 32 KB of shared memory, so that it has its SM to itself beside kernels
+  // that fill shared memory (see above); ctas == 0: one CTA per SM, sharing it with whatever runs
+  // and they are launched as clusters of two, which land on the two SMs of one pair: n CTAs then
+  // cost the CTA-pair GEMM n / 2 of its SM pairs, not n
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  cfg.blockDim = dim3(kPushThreads);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  if (ctas > 0) {
+    grid = (grid + 1) & ~1;
+    cfg.dynamicSmemBytes = 32 * 1024;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cfg.gridDim = dim3(grid);
+  MG_CUDA_TRY(cudaLaunchKernelEx(&cfg, push_block_kernel, p));
   return MG_OK;
 }

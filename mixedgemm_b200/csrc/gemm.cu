@@ -1436,7 +1436,9 @@ int launch_pair(int nprob, const PairProblem* pr, int sms, cudaStream_t st) {
   p.wait_cycles = mg::wait_limit_cycles();
   rc = mg::device_status_word(&p.status);
   if (rc != MG_OK) return rc;
-  const int max_clusters = sms / 2;
+  int max_clusters = sms / 2;
+  const int cap = mg::options().gemm_max_clusters;
+  if (cap > 0 && cap < max_clusters) max_clusters = cap;
   const int clusters = tiles < max_clusters ? tiles : max_clusters;
   ScheduleKey key;
   memset(&key, 0, sizeof(key));

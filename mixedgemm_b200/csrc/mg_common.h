@@ -40,6 +40,7 @@ struct Options {
   int gemm_splitk;    // GEMM_SPLITK: 0 turns split-K through the workspace off, n > 0 forces n splits
   int gemm_swap;      // GEMM_SWAP: 0 / 1 forces the decode form (weights as the 128-row operand) off / on
   int gemm_sched;     // GEMM_SCHED: 0 deals the CTA-pair kernel's tiles out round-robin instead of by cost
+  int gemm_max_clusters;  // GEMM_MAX_CLUSTERS: n > 0 caps the SM pairs the CTA-pair kernel uses
   int pdl;            // PDL: 0 launches without programmatic dependent launch
   int reorder_ctas;   // REORDER_CTAS: n > 0 caps the quantiser's grid (to share the GPU with another kernel)
   int fault_skip_load;  // FAULT_SKIP_LOAD: n > 0 makes the GEMM's first CTA withhold its n-th stage load

@@ -174,8 +174,9 @@ class PushExchange:
     quantises in a step - its M/P rows of every activation, each as three code tensors at their row
     pitch followed by their three scale tensors - is ONE contiguous block, followed by `world` flag
     words.  A step's push is then either one kernel that reads the block once and stores it into every
-    peer's set (mode "sm", mg_push_block: no shared memory, 30 registers, so it runs on the same SMs
-    as the GEMM that is multiplying the step before), or one large copy-engine copy per peer (mode
+    peer's set (mode "sm", mg_push_block, on `push_ctas` SMs that it keeps to itself: launch the GEMM
+    that runs beside it with option GEMM_MAX_CLUSTERS = SM pairs - push_ctas / 2; push_ctas = 0 uses
+    every SM and is for a push that runs alone), or one large copy-engine copy per peer (mode
     "ce", mg_push_shard: small copies reach a fraction of the NVLink rate, every copy costs tens of
     microseconds of latency, and copies to several peers at once share the engines badly).  The GEMM
     reads that layout in place (api.ShardedActivation).
@@ -185,7 +186,7 @@ class PushExchange:
     issued before the GEMM of step i (so that the transfer hides under it), a set is overwritten three
     steps after it was read and 4 are needed."""
 
-    def __init__(self, shapes, world, rank, device, n_sets=2, group=None, mode="sm", push_ctas=0):
+    def __init__(self, shapes, world, rank, device, n_sets=2, group=None, mode="sm", push_ctas=8):
         from .api import ShardedActivation
         if mode not in ("sm", "ce"):
             raise ValueError("mode is 'sm' (a kernel stores into the peers' buffers) or 'ce' (copy engines)")
@@ -300,7 +301,7 @@ class PushExchange:
     def join(self):
         """Make the current stream wait for the copies this rank has issued (the buffers it pushed
         FROM may be overwritten afterwards)."""
-        for st in self.streams:
+        for st in (self.streams[:1] if self.mode == "sm" else self.streams):
             torch.cuda.current_stream().wait_stream(st)
 
     def close(self):
