@@ -20,7 +20,7 @@ launch.  Weights are quantised once, outside the timed region, as in deployment.
                     --no-pipeline sends and multiplies the same batch in a step); the GEMM's
                     producer waits for the flags that follow the data;
                     push-ce / push-sm: force copy-engine copies (one per peer; the default up to four
-                    GPUs) or the kernel (eight SMs of its own; the default beyond);
+                    GPUs) or the kernel (twelve SMs of its own; the default beyond);
                     allgather: the same rows, completed by NCCL all-gathers before the GEMM;
                     bcast: rank 0 quantises, NCCL broadcast; replicated: every rank quantises
                     everything, nothing is exchanged
@@ -210,7 +210,9 @@ class Job:
         # the push: copy engines up to four GPUs (their all-to-all rate is enough to hide under the GEMM
         # there and they cost no SM), a kernel on eight SMs of its own beyond that
         self.push_mode = {"push-ce": "ce", "push-sm": "sm"}.get(exchange, "ce" if world <= 4 else "sm")
-        self.push_ctas = 8
+        # 12 SMs: a push SM sustains about 50 GB/s of peer stores and the fabric about 540 GB/s per rank
+        # (measured with 4 GPUs), and at 8 GPUs 107 MB per rank and step must leave within the GEMM's 200 us
+        self.push_ctas = 12
         if exchange in ("push-ce", "push-sm"):
             exchange = "push"
         self.exchange = exchange if world > 1 else "none"

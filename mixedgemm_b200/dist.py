@@ -7,10 +7,11 @@ gathers them.  The transfers are made by the C ABI (include/mixedgemm_c.h, csrc/
 
   Communicator   NCCL collectives through mg_dist_* / mg_bcast_activations / mg_allgather_*:
                  "quantise once, broadcast", or "quantise M/P rows each, all-gather"
-  PushExchange   the overlapped exchange: every rank quantises M/P rows in place in its own
-                 full-size buffer and pushes them into every peer's buffer with one copy-engine
-                 copy per peer over NVLink (mg_push_shard); the GEMM is launched at once and
-                 waits, row shard by row shard, for the flags that follow the data
+  PushExchange   the overlapped exchange: every rank quantises M/P rows in place in its own block
+                 of a buffer that is laid out rank by rank, and pushes the block into every
+                 peer's buffer over NVLink - one copy-engine copy per peer (mg_push_shard) or one
+                 kernel with plain peer stores (mg_push_block); the GEMM waits, row shard by row
+                 shard, for the flags that follow the data
 
 The only thing the host framework (torch.distributed) is used for is handing small byte strings
 from rank to rank at set-up time: the NCCL id and the IPC handles of the exchange buffers.
