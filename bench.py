@@ -288,9 +288,12 @@ class Job:
             self.ex = mgd.PushExchange([(M, gr["split"]) for gr in self.groups], world, rank, device, n_sets=self.nsets,
                                        mode=self.push_mode, push_ctas=self.push_ctas)
             if self.push_mode == "sm":
-                # the GEMM leaves the push kernel's SM pairs alone
-                mg.set_option("GEMM_MAX_CLUSTERS", torch.cuda.get_device_properties(device).multi_processor_count // 2
-                              - self.push_ctas // 2)
+                # the GEMM and the quantiser leave the push kernel's SMs alone: a quantiser CTA fills an
+                # SM's shared memory, so on the SMs where the push of the step before is still running
+                # it would have to wait for it
+                sms = torch.cuda.get_device_properties(device).multi_processor_count
+                mg.set_option("GEMM_MAX_CLUSTERS", sms // 2 - self.push_ctas // 2)
+                mg.set_option("REORDER_CTAS", sms - self.push_ctas)
             for gi, gr in enumerate(self.groups):
                 gr["A"] = [self.ex.buffers(s, gi) for s in range(self.nsets)]
         else:
@@ -802,7 +805,8 @@ def main():
         # not have to be taken against the (smaller) default workload of `--gpus 1`: rank 0 alone,
         # all weights, same graph-replay timing, while the other ranks wait.
         if rank == 0:
-            job.mg.set_option("GEMM_MAX_CLUSTERS", 0)  # the single-GPU figure uses every SM pair
+            job.mg.set_option("GEMM_MAX_CLUSTERS", 0)  # the single-GPU figure uses every SM
+            job.mg.set_option("REORDER_CTAS", 0)
             job1 = Job(wl_name, 0, 1, device, "none", fused=not a.no_fuse)
             with torch.cuda.stream(stream):
                 for _ in range(a.warmup):
