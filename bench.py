@@ -281,6 +281,10 @@ class Job:
         # transfer runs under a GEMM that already has its data (steps are independent batches)
         self.pipeline = pipeline and self.exchange == "push"
         self.primed = False
+        # The kernel push at 8 GPUs takes as long as the GEMM (214 against 203 us), so it gets the
+        # whole step: the pass that multiplies batch i pushes batch i + 1 from its first instant (the
+        # pass before quantised it) and quantises batch i + 2.
+        self.lookahead = 2 if (self.pipeline and self.push_mode == "sm") else 1
         if self.exchange == "push":
             from mixedgemm_b200 import dist as mgd
             # buffer sets used in turn: a rank may push a later step while a peer still multiplies this one
@@ -393,10 +397,24 @@ class Job:
         push: the pass quantises and sends batch s + 1 and multiplies batch s, which the pass before
         sent (prime() sends the very first one)."""
         if self.ex is not None:
-            if self.pipeline:
+            n = self.nsets
+            if self.pipeline and self.lookahead == 2:
                 if not self.primed:
                     self.prime(s)
-                self.fill((s + 1) % self.nsets)
+                self.ex.push((s + 1) % n)
+                if s == 0:
+                    self._pushed_first = torch.cuda.Event()
+                    self._pushed_first.record(self.ex.streams[0])
+                if s == n - 1:
+                    # this pass overwrites the block that the first push of the round read (earlier
+                    # rounds' pushes were taken back by the join that ended them)
+                    torch.cuda.current_stream().wait_event(self._pushed_first)
+                self.ex.begin_step((s + 2) % n)
+                self.quantize_all((s + 2) % n)
+            elif self.pipeline:
+                if not self.primed:
+                    self.prime(s)
+                self.fill((s + 1) % n)
             else:
                 self.fill(s)
             self.multiply(s)
@@ -425,6 +443,9 @@ class Job:
     def prime(self, s=0):
         self.fill(s)
         self.ex.join()
+        if self.lookahead == 2:
+            self.ex.begin_step((s + 1) % self.nsets)
+            self.quantize_all((s + 1) % self.nsets)
         self.primed = True
 
     def close(self):
@@ -849,8 +870,11 @@ def main():
                    "layers": [[gr["K"], [[n, N * world] for (n, N, _, _) in gr["layers"]]] for gr in job.groups],
                    "k_split": "62.5% fp4 / 34.375% fp6 / 3.125% fp8", "parallelism": "n-shard x%d" % world,
                    "exchange": (job.exchange + ("/" + job.push_mode if job.ex is not None else "")), "cuda_graph": use_graph,
-                   "pipeline": ("every step quantises and sends batch i + 1 (one quantiser launch, one copy per peer) and "
-                                "multiplies batch i, which the step before sent; %d buffer sets in turn" % job.nsets)
+                   "pipeline": (("every step sends batch i + 1 (one kernel on %d SMs of its own), quantises batch i + 2 (one "
+                                 "launch) and multiplies batch i; %d buffer sets in turn" % (job.push_ctas, job.nsets))
+                                if job.lookahead == 2 else
+                                ("every step quantises and sends batch i + 1 (one quantiser launch, one copy per peer) and "
+                                 "multiplies batch i, which the step before sent; %d buffer sets in turn" % job.nsets))
                    if job.pipeline else None,
                    "gemm_launch": "one launch over all layers" if job.fused else "one launch per activation",
                    "l2": "inputs larger than L2: one step touches ~%d MB of weights, activations and outputs" % (

@@ -146,6 +146,28 @@ def _push_steps(mg, ex, Xs, X2s, idx, idx2, split, SPLIT2, rows, Bl, B2l, refere
         outs = multiply(step % 4)
         ex.join()
         piped &= check(step, outs)
+    # two steps ahead: the pass that multiplies batch i pushes batch i + 1 first thing (quantised by
+    # the pass before) and quantises batch i + 2
+    torch.cuda.synchronize()
+    dist.barrier()
+
+    def quantise(step, s):
+        ex.begin_step(s)
+        mg.reorder_quantize_x_multi([(Xs[step][rows].contiguous(), idx, KN, KS, KO, ex.shard(s, 0)),
+                                     (X2s[step][rows].contiguous(), idx2, *SPLIT2, ex.shard(s, 1))])
+
+    quantise(0, 0)
+    ex.push(0)
+    ex.join()
+    quantise(1, 1)
+    for step in range(4):
+        if step + 1 < 4:
+            ex.push((step + 1) % 4)
+        if step + 2 < 4:
+            quantise(step + 2, (step + 2) % 4)
+        outs = multiply(step % 4)
+        piped &= check(step, outs)
+    ex.join()
     return good, piped
 
 
