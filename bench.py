@@ -209,11 +209,11 @@ class Job:
         self.rank, self.world, self.device = rank, world, device
         # the push: copy engines up to four GPUs (their all-to-all rate is enough to hide under the GEMM
         # there and they cost no SM), a kernel on eight SMs of its own beyond that
-        self.push_mode = {"push-ce": "ce", "push-sm": "sm"}.get(exchange, "ce" if world <= 4 else "sm")
+        self.push_mode = {"push-ce": "ce", "push-sm": "sm", "push-hybrid": "hybrid"}.get(exchange, "ce" if world <= 4 else "sm")
         # 12 SMs: a push SM sustains about 50 GB/s of peer stores and the fabric about 540 GB/s per rank
         # (measured with 4 GPUs), and at 8 GPUs 107 MB per rank and step must leave within the GEMM's 200 us
         self.push_ctas = 12
-        if exchange in ("push-ce", "push-sm"):
+        if exchange in ("push-ce", "push-sm", "push-hybrid"):
             exchange = "push"
         self.exchange = exchange if world > 1 else "none"
         self.fused = fused
@@ -284,14 +284,14 @@ class Job:
         # The kernel push at 8 GPUs takes as long as the GEMM (214 against 203 us), so it gets the
         # whole step: the pass that multiplies batch i pushes batch i + 1 from its first instant (the
         # pass before quantised it) and quantises batch i + 2.
-        self.lookahead = 2 if (self.pipeline and self.push_mode == "sm") else 1
+        self.lookahead = 2 if (self.pipeline and self.push_mode in ("sm", "hybrid")) else 1
         if self.exchange == "push":
             from mixedgemm_b200 import dist as mgd
             # buffer sets used in turn: a rank may push a later step while a peer still multiplies this one
             self.nsets = 4 if self.pipeline else 2
             self.ex = mgd.PushExchange([(M, gr["split"]) for gr in self.groups], world, rank, device, n_sets=self.nsets,
                                        mode=self.push_mode, push_ctas=self.push_ctas)
-            if self.push_mode == "sm":
+            if self.push_mode in ("sm", "hybrid"):
                 # the GEMM and the quantiser leave the push kernel's SMs alone: a quantiser CTA fills an
                 # SM's shared memory, so on the SMs where the push of the step before is still running
                 # it would have to wait for it
@@ -319,7 +319,7 @@ class Job:
             nq = 1
         # kernels of this library per step: the quantisers + the GEMM launches (+ the epoch bump)
         self.n_kernels = nq + (1 if self.fused else sum(1 if g_ else len(gr["layers"]) for g_, gr in zip(grouped, self.groups)))
-        self.n_kernels += (2 if self.push_mode == "sm" else 1) if self.ex is not None else 0  # epoch bump (+ push kernel)
+        self.n_kernels += (2 if self.push_mode in ("sm", "hybrid") else 1) if self.ex is not None else 0  # epoch bump (+ push kernel)
         self.reorder_bytes = sum(reorder_bytes(gr["X"].size(0), gr["K"]) for gr in self.groups)
         torch.cuda.synchronize()
 
@@ -403,12 +403,16 @@ class Job:
                     self.prime(s)
                 self.ex.push((s + 1) % n)
                 if s == 0:
-                    self._pushed_first = torch.cuda.Event()
-                    self._pushed_first.record(self.ex.streams[0])
+                    self._pushed_first = []
+                    for st in self.ex.used_streams():
+                        e = torch.cuda.Event()
+                        e.record(st)
+                        self._pushed_first.append(e)
                 if s == n - 1:
                     # this pass overwrites the block that the first push of the round read (earlier
                     # rounds' pushes were taken back by the join that ended them)
-                    torch.cuda.current_stream().wait_event(self._pushed_first)
+                    for e in self._pushed_first:
+                        torch.cuda.current_stream().wait_event(e)
                 self.ex.begin_step((s + 2) % n)
                 self.quantize_all((s + 2) % n)
             elif self.pipeline:
@@ -552,7 +556,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=list(WORKLOADS))
-    ap.add_argument("--exchange", default="push", choices=["push", "push-ce", "push-sm", "allgather", "bcast", "replicated"])
+    ap.add_argument("--exchange", default="push", choices=["push", "push-ce", "push-sm", "push-hybrid", "allgather", "bcast", "replicated"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--quantize", choices=["each", "multi"], default=None,
                     help="one quantiser launch per activation, or one for all of a step (default: multi)")

@@ -344,6 +344,16 @@ int mg_push_shard(int world, int rank, void* const* bases, const size_t* seg_off
  */
 int mg_push_block(int world, int rank, void* const* bases, size_t block_off, size_t block_bytes, size_t flag_off,
                   const int* epoch_word, int* counter, int ctas, void* stream);
+/*
+ * Both pushes for a subset of the peers, so that the copy engines and a kernel can share a push
+ * (they reach different parts of the link rate): bit s - 1 of ring_mask names the peer s places down
+ * the ring, (rank - s + world) % world; 0 means all of them, as in the calls above.  With a mask,
+ * mg_push_block_to still writes this rank's own flag and mg_push_shard_to does not.
+ */
+int mg_push_shard_to(int world, int rank, unsigned ring_mask, void* const* bases, const size_t* seg_off,
+                     const size_t* seg_bytes, int nseg, size_t flag_off, const int* epoch_word, void* const* streams);
+int mg_push_block_to(int world, int rank, unsigned ring_mask, void* const* bases, size_t block_off, size_t block_bytes,
+                     size_t flag_off, const int* epoch_word, int* counter, int ctas, void* stream);
 
 /*
  * mg_matmul for callers that cannot allocate.  No counterpart in the reference (its binding

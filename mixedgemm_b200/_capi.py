@@ -27,6 +27,8 @@ PROTOTYPES = {
     "mg_matmul_multi": (_i, [_i, _vp, _vp]),
     "mg_reorder_quantize_multi": (_i, [_i, _i, _vp, _vp]),
     "mg_push_block": (_i, [_i, _i, _vp, _sz, _sz, _sz, _vp, _vp, _i, _vp]),
+    "mg_push_block_to": (_i, [_i, _i, ctypes.c_uint, _vp, _sz, _sz, _sz, _vp, _vp, _i, _vp]),
+    "mg_push_shard_to": (_i, [_i, _i, ctypes.c_uint, _vp, _vp, _vp, _i, _sz, _vp, _vp]),
     "mg_dist_unique_id": (_i, [_vp]),
     "mg_dist_init": (_i, [ctypes.POINTER(_vp), _vp, _i, _i]),
     "mg_dist_destroy": (_i, [_vp]),

@@ -263,8 +263,14 @@ extern "C" int mg_epoch_bump(int* epoch_word, void* stream) {
 
 extern "C" int mg_push_shard(int world, int rank, void* const* bases, const size_t* seg_off, const size_t* seg_bytes,
                              int nseg, size_t flag_off, const int* epoch_word, void* const* streams) {
+  return mg_push_shard_to(world, rank, 0u, bases, seg_off, seg_bytes, nseg, flag_off, epoch_word, streams);
+}
+
+extern "C" int mg_push_shard_to(int world, int rank, unsigned ring_mask, void* const* bases, const size_t* seg_off,
+                                const size_t* seg_bytes, int nseg, size_t flag_off, const int* epoch_word,
+                                void* const* streams) {
   if (!bases || !seg_off || !seg_bytes || !epoch_word || !streams) return MG_ERR_NULL;
-  if (world < 1 || rank < 0 || rank >= world || nseg < 0) return MG_ERR_SHAPE;
+  if (world < 1 || world > 32 || rank < 0 || rank >= world || nseg < 0) return MG_ERR_SHAPE;
   const uint8_t* mine = static_cast<const uint8_t*>(bases[rank]);
   if (!mine) return MG_ERR_NULL;
   for (int step = 0; step < world; ++step) {
@@ -272,6 +278,9 @@ extern "C" int mg_push_shard(int world, int rank, void* const* bases, const size
     // different targets and rank r hears from r + 1 first, then r + 2, ...; step 0 is this rank
     // itself: its rows are already in place, only its own flag goes up
     const int peer = (rank - step + world) % world;
+    // a mask names the peers this call serves by their distance down the ring (bit step - 1); the
+    // own flag then belongs to the call that serves the others (mg_push_block_to)
+    if (ring_mask != 0 && (step == 0 || !(ring_mask >> (step - 1) & 1u))) continue;
     uint8_t* dst = static_cast<uint8_t*>(bases[peer]);
     if (!dst) return MG_ERR_NULL;
     cudaStream_t st = static_cast<cudaStream_t>(streams[step == 0 ? 0 : step - 1]);
@@ -286,6 +295,12 @@ extern "C" int mg_push_shard(int world, int rank, void* const* bases, const size
 
 extern "C" int mg_push_block(int world, int rank, void* const* bases, size_t block_off, size_t block_bytes,
                              size_t flag_off, const int* epoch_word, int* counter, int ctas, void* stream) {
+  return mg_push_block_to(world, rank, 0u, bases, block_off, block_bytes, flag_off, epoch_word, counter, ctas, stream);
+}
+
+extern "C" int mg_push_block_to(int world, int rank, unsigned ring_mask, void* const* bases, size_t block_off,
+                                size_t block_bytes, size_t flag_off, const int* epoch_word, int* counter, int ctas,
+                                void* stream) {
   if (!bases || !epoch_word || !counter) return MG_ERR_NULL;
   if (world < 1 || world > kMaxPeers + 1 || rank < 0 || rank >= world || ctas < 0) return MG_ERR_SHAPE;
   if (block_bytes % 16 || block_off % 16 || flag_off % 4) return MG_ERR_ALIGN;
@@ -293,17 +308,20 @@ extern "C" int mg_push_block(int world, int rank, void* const* bases, size_t blo
   uint8_t* mine = static_cast<uint8_t*>(bases[rank]);
   if (!mine) return MG_ERR_NULL;
   p.src = reinterpret_cast<const uint4*>(mine + block_off);
-  p.npeers = world - 1;
+  int np = 0;
   for (int step = 1; step < world; ++step) {
-    // ring order downwards from this rank, as in mg_push_shard
+    // ring order downwards from this rank, as in mg_push_shard; a mask keeps only the named distances
+    if (ring_mask != 0 && !(ring_mask >> (step - 1) & 1u)) continue;
     uint8_t* peer = static_cast<uint8_t*>(bases[(rank - step + world) % world]);
     if (!peer) return MG_ERR_NULL;
     if (!mg::aligned(peer, 16)) return MG_ERR_ALIGN;
-    p.dst[step - 1] = reinterpret_cast<uint4*>(peer + block_off);
-    p.flag[step - 1] = reinterpret_cast<int*>(peer + flag_off) + rank;
+    p.dst[np] = reinterpret_cast<uint4*>(peer + block_off);
+    p.flag[np] = reinterpret_cast<int*>(peer + flag_off) + rank;
+    ++np;
   }
+  p.npeers = np;
   if (!mg::aligned(mine, 16)) return MG_ERR_ALIGN;
-  p.flag[world - 1] = reinterpret_cast<int*>(mine + flag_off) + rank;
+  p.flag[np] = reinterpret_cast<int*>(mine + flag_off) + rank;
   p.n16 = block_bytes / 16;
   p.epoch_word = epoch_word;
   p.counter = counter;

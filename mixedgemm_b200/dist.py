@@ -187,10 +187,12 @@ class PushExchange:
     issued before the GEMM of step i (so that the transfer hides under it), a set is overwritten three
     steps after it was read and 4 are needed."""
 
-    def __init__(self, shapes, world, rank, device, n_sets=2, group=None, mode="sm", push_ctas=8):
+    def __init__(self, shapes, world, rank, device, n_sets=2, group=None, mode="sm", push_ctas=8, ce_peers=2):
         from .api import ShardedActivation
-        if mode not in ("sm", "ce"):
-            raise ValueError("mode is 'sm' (a kernel stores into the peers' buffers) or 'ce' (copy engines)")
+        if mode not in ("sm", "ce", "hybrid"):
+            raise ValueError("mode is 'sm' (a kernel stores into the peers' buffers), 'ce' (copy engines) or "
+                             "'hybrid' (copy engines for the `ce_peers` farthest peers, the kernel for the rest)")
+        self.ce_peers = min(ce_peers, max(world - 2, 0)) if mode == "hybrid" else 0
         self.lib = lib = _capi.load()
         self.world, self.rank, self.device = world, rank, device
         self.mode, self.push_ctas = mode, push_ctas
@@ -276,14 +278,29 @@ class PushExchange:
         b = self.sets[set_index]
         done = torch.cuda.Event()
         done.record()
-        if self.mode == "sm":
-            # one kernel on one side stream: it shares the SMs with whatever the current stream runs next
+        if self.mode in ("sm", "hybrid"):
+            # one kernel on one side stream; in the hybrid form the copy engines take the peers farthest
+            # down the ring (one stream each) and the kernel the others
+            nring = self.world - 1
+            ce_steps = list(range(nring - self.ce_peers + 1, nring + 1))
+            sm_mask = 0
+            if ce_steps:
+                for step in range(1, nring - self.ce_peers + 1):
+                    sm_mask |= 1 << (step - 1)
             st = self.streams[0]
             st.wait_event(done)
-            _capi.check(self.lib.mg_push_block(
-                self.world, self.rank, _vp_array(b["bases"]), self.rank * self.block_bytes, self.block_bytes,
+            _capi.check(self.lib.mg_push_block_to(
+                self.world, self.rank, sm_mask, _vp_array(b["bases"]), self.rank * self.block_bytes, self.block_bytes,
                 self.flag_off, self.epoch[set_index:].data_ptr(), self.counter.data_ptr(), self.push_ctas,
                 st.cuda_stream), "mg_push_block")
+            for j, step in enumerate(ce_steps):
+                cs = self.streams[1 + j]
+                cs.wait_event(done)
+                per_step = [cs.cuda_stream] * nring
+                _capi.check(self.lib.mg_push_shard_to(
+                    self.world, self.rank, 1 << (step - 1), _vp_array(b["bases"]), _sz_array([self.rank * self.block_bytes]),
+                    _sz_array([self.block_bytes]), 1, self.flag_off, self.epoch[set_index:].data_ptr(),
+                    _vp_array(per_step)), "mg_push_shard")
             return
         for st in self.streams:
             st.wait_event(done)
@@ -302,8 +319,14 @@ class PushExchange:
     def join(self):
         """Make the current stream wait for the copies this rank has issued (the buffers it pushed
         FROM may be overwritten afterwards)."""
-        for st in (self.streams[:1] if self.mode == "sm" else self.streams):
+        for st in self.used_streams():
             torch.cuda.current_stream().wait_stream(st)
+
+    def used_streams(self):
+        """The side streams a push puts work on."""
+        if self.mode == "ce":
+            return self.streams
+        return self.streams[:1 + self.ce_peers]
 
     def close(self):
         torch.cuda.synchronize(self.device)

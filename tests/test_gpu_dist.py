@@ -92,7 +92,7 @@ def _worker(rank, world, port, ret):
 
         rows = slice(rank * mp_, (rank + 1) * mp_)
         good, piped = True, True
-        for mode in ("sm", "ce"):       # a kernel's peer stores / copy-engine copies
+        for mode in ("sm", "ce", "hybrid"):   # a kernel's peer stores / copy-engine copies / both
             ex = mgd.PushExchange([(M, SPLIT), (M, SPLIT2)], world, rank, dev, n_sets=4, mode=mode)
             g_, p_ = _push_steps(mg, ex, Xs, X2s, idx, idx2, (KN, KS, KO), SPLIT2, rows, Bl, B2l, reference, reference2,
                                  (n0, nl), (m0, ml))
@@ -209,6 +209,28 @@ def test_push_kernel_on_one_gpu():
             for r in range(world):
                 assert torch.equal(b[r * block:(r + 1) * block], want[r]), (world, r)
             assert torch.all(b[flag_off:].view(torch.int32) == 5)
+    # the two pushes sharing the peers: the kernel serves ring distances 1 and 2, a copy serves 3
+    world, block = 4, 16 * 4099
+    flag_off = world * block
+    bufs = [torch.zeros(flag_off + 4 * world, dtype=torch.uint8, device=dev) for _ in range(world)]
+    want = [torch.randint(0, 256, (block,), dtype=torch.uint8, device=dev) for _ in range(world)]
+    bases = (ctypes.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    epoch.fill_(9)
+    stream = torch.cuda.current_stream().cuda_stream
+    streams = (ctypes.c_void_p * (world - 1))(*([stream] * (world - 1)))
+    for r in range(world):
+        bufs[r][r * block:(r + 1) * block] = want[r]
+    for r in range(world):
+        assert lib.mg_push_block_to(world, r, 0b011, bases, r * block, block, flag_off, epoch.data_ptr(),
+                                    counter.data_ptr(), 2, stream) == 0
+        off = (ctypes.c_size_t * 1)(r * block)
+        nbytes = (ctypes.c_size_t * 1)(block)
+        assert lib.mg_push_shard_to(world, r, 0b100, bases, off, nbytes, 1, flag_off, epoch.data_ptr(), streams) == 0
+    torch.cuda.synchronize()
+    for b in bufs:
+        for r in range(world):
+            assert torch.equal(b[r * block:(r + 1) * block], want[r]), r
+        assert torch.all(b[flag_off:].view(torch.int32) == 9)
     bases = (ctypes.c_void_p * 2)(bufs[0].data_ptr(), bufs[1].data_ptr())
     e, c = epoch.data_ptr(), counter.data_ptr()
     assert lib.mg_push_block(2, 0, bases, 0, 24, 4096, e, c, 0, None) == 3        # MG_ERR_ALIGN: not whole 16 bytes
