@@ -2,7 +2,7 @@
 """Benchmark of the hot path: activation reorder-and-quantise + mixed MXFP4/6/8 GEMM.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                  [--workload NAME] [--exchange push|push-ce|push-sm|allgather|bcast|replicated] [--no-graph] [--no-fuse]
+                  [--workload NAME] [--exchange push|push-ce|push-sm|push-hybrid|allgather|bcast|replicated] [--no-graph] [--no-fuse]
   python bench.py --kernel gemm|reorder --shape M,N,K     one kernel, one shape
   python bench.py --sweep decode|square|all               the other benchmark configurations, a line per shape
 
@@ -19,8 +19,9 @@ launch.  Weights are quantised once, outside the timed region, as in deployment.
                     under the GEMM of the batch before (the exchange runs one step ahead;
                     --no-pipeline sends and multiplies the same batch in a step); the GEMM's
                     producer waits for the flags that follow the data;
-                    push-ce / push-sm: force copy-engine copies (one per peer; the default up to four
-                    GPUs) or the kernel (twelve SMs of its own; the default beyond);
+                    push-ce / push-sm / push-hybrid: force copy-engine copies (one per peer; the
+                    default up to four GPUs), the kernel (twelve SMs of its own), or the kernel for
+                    all peers but two and copies for those (the default beyond four GPUs);
                     allgather: the same rows, completed by NCCL all-gathers before the GEMM;
                     bcast: rank 0 quantises, NCCL broadcast; replicated: every rank quantises
                     everything, nothing is exchanged
@@ -208,8 +209,9 @@ class Job:
         self.M = M = wl["M"]
         self.rank, self.world, self.device = rank, world, device
         # the push: copy engines up to four GPUs (their all-to-all rate is enough to hide under the GEMM
-        # there and they cost no SM), a kernel on eight SMs of its own beyond that
-        self.push_mode = {"push-ce": "ce", "push-sm": "sm", "push-hybrid": "hybrid"}.get(exchange, "ce" if world <= 4 else "sm")
+        # there and they cost no SM); beyond that a kernel on SMs of its own for all peers but the two
+        # farthest down the ring, which the copy engines serve (measured best at 8 GPUs)
+        self.push_mode = {"push-ce": "ce", "push-sm": "sm", "push-hybrid": "hybrid"}.get(exchange, "ce" if world <= 4 else "hybrid")
         # 12 SMs: a push SM sustains about 50 GB/s of peer stores and the fabric about 540 GB/s per rank
         # (measured with 4 GPUs), and at 8 GPUs 107 MB per rank and step must leave within the GEMM's 200 us
         self.push_ctas = 12
