@@ -6,12 +6,13 @@
 //     mg_allgather_output).  NCCL is taken from the process (the libnccl that the host framework
 //     already loaded) or loaded by name; nothing links against it, so the library loads without it.
 //   * the overlapped exchange: every rank quantises its M / P rows and PUSHES them into every
-//     peer's buffer with copy-engine copies over NVLink (cudaMemcpyAsync on per-peer streams, no SM
-//     involved, so the copies run under the GEMMs), followed by a 4-byte flag copy.  The GEMM that
-//     consumes the activation is already running: its producer waits for the flags
-//     (mg_problem_t.ready_flags).  Peer buffers are opened through CUDA IPC.
-// No kernel of this library ever has another GPU's memory as an operand; the only things that
-// cross NVLink are NCCL's transfers and those copies.
+//     peer's buffer over NVLink - with copy-engine copies (mg_push_shard: cudaMemcpyAsync on
+//     per-peer streams, no SM involved, followed by a 4-byte flag copy), with a kernel that stores
+//     into the peers' buffers from SMs of its own (mg_push_block), or with both sharing the peers
+//     (the _to forms).  The GEMM that consumes the activation may already be running: its producer
+//     waits for the flags (mg_problem_t.ready_flags).  Peer buffers are opened through CUDA IPC.
+// The GEMM and the quantiser never have another GPU's memory as an operand and no tensor map covers
+// it; what crosses NVLink are NCCL's transfers, those copies and the push kernel's plain stores.
 #include <dlfcn.h>
 #include <nccl.h>
 

@@ -16,8 +16,8 @@ gathers them.  The transfers are made by the C ABI (include/mixedgemm_c.h, csrc/
 The only thing the host framework (torch.distributed) is used for is handing small byte strings
 from rank to rank at set-up time: the NCCL id and the IPC handles of the exchange buffers.
 The shard bookkeeping (shard_range, sf_shard, shard_weights, activation_shard) is plain tensor
-slicing and works on CPU tensors too.  The reference has no multi-GPU mode; the kernels never
-have another GPU's memory as an operand.
+slicing and works on CPU tensors too.  The reference has no multi-GPU mode.  The GEMM and the
+quantiser never have another GPU's memory as an operand; only the push kernel stores into it.
 """
 import ctypes
 

@@ -1,8 +1,10 @@
 """Two GPUs: the N-sharded GEMM gives, shard by shard, the bytes of the single-GPU GEMM, with the
 quantised activation travelling each of the three ways the C ABI offers - NCCL broadcast from the
-rank that quantised it, NCCL all-gather of row shards, and the overlapped exchange (copy-engine
-pushes + ready flags that the GEMM waits for).  Skipped on a box with one GPU.  NVLS is switched
-off; no kernel is given another GPU's memory; host plumbing (ids, IPC handles) goes over gloo."""
+rank that quantised it, NCCL all-gather of row shards, and the overlapped exchange (pushes by copy
+engines, by a kernel's peer stores, or both, + ready flags that the GEMM waits for) in the three
+orders a caller may use.  Skipped on a box with one GPU.  NVLS is switched off; the GEMM and the
+quantiser are never given another GPU's memory; host plumbing (ids, IPC handles) goes over gloo.
+The push kernel alone is also tested with every "rank's" buffer on one GPU."""
 import os
 import socket
 
