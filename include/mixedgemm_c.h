@@ -267,6 +267,16 @@ typedef struct mg_problem {
   size_t sfa_shard_stride[3];
 } mg_problem_t;
 int mg_matmul_multi(int nprob, const mg_problem_t* probs, void* stream);
+/*
+ * The tile order a multi-problem launch uses, for inspection and tests (host only, no CUDA call):
+ * problem j has tiles[j] tile pairs of cost[j] (the library uses K stages + 1); the concatenated
+ * tile list is dealt out in order, each tile to the SM pair that is free first.  *use = 0 means
+ * "round-robin" (equal costs, no more tiles than pairs, or more than 8192 tiles); otherwise pair c
+ * computes tile[off[c]] .. tile[off[c + 1] - 1] in that order.  off holds clusters + 1 entries, tile
+ * the total number of tiles.  clusters <= 96.
+ */
+int mg_pair_schedule(int nprob, const int* tiles, const int* cost, int clusters, int* use, uint16_t* off,
+                     uint16_t* tile);
 
 /*
  * Same product with the fp32 accumulator written unrounded: D_f32 [M,N] float, pitch `ldd`

@@ -25,6 +25,7 @@ PROTOTYPES = {
     "mg_get_option": (_i, [ctypes.c_char_p, ctypes.POINTER(_i)]),
     "mg_reset_options": (None, []),
     "mg_matmul_multi": (_i, [_i, _vp, _vp]),
+    "mg_pair_schedule": (_i, [_i, _vp, _vp, _i, ctypes.POINTER(_i), _vp, _vp]),
     "mg_reorder_quantize_multi": (_i, [_i, _i, _vp, _vp]),
     "mg_push_block": (_i, [_i, _i, _vp, _sz, _sz, _sz, _vp, _vp, _i, _vp]),
     "mg_push_block_to": (_i, [_i, _i, ctypes.c_uint, _vp, _sz, _sz, _sz, _vp, _vp, _i, _vp]),

@@ -1457,6 +1457,30 @@ int launch_pair(int nprob, const PairProblem* pr, int sms, cudaStream_t st) {
 
 }  // namespace
 
+extern "C" int mg_pair_schedule(int nprob, const int* tiles, const int* cost, int clusters, int* use,
+                                uint16_t* off, uint16_t* tile) {
+  if (!tiles || !cost || !use || !off || !tile) return MG_ERR_NULL;
+  if (nprob < 1 || nprob > kMaxProb || clusters < 1 || clusters > kMaxClusters) return MG_ERR_SHAPE;
+  ScheduleKey key;
+  memset(&key, 0, sizeof(key));
+  key.nprob = nprob;
+  key.clusters = clusters;
+  long long total = 0;
+  for (int j = 0; j < nprob; ++j) {
+    if (tiles[j] < 0 || cost[j] < 1) return MG_ERR_SHAPE;
+    key.tiles[j] = tiles[j];
+    key.cost[j] = cost[j];
+    total += tiles[j];
+  }
+  const PairSchedule& sc = schedule_for(key);
+  *use = sc.use;
+  if (sc.use) {
+    memcpy(off, sc.off, sizeof(uint16_t) * (size_t)(clusters + 1));
+    memcpy(tile, sc.tile, sizeof(uint16_t) * (size_t)total);
+  }
+  return MG_OK;
+}
+
 extern "C" size_t mg_matmul_workspace_bytes(int M, int N, int KN, int KS, int KO) {
   if (M <= 0 || N <= 0 || KN < 0 || KS < 0 || KO < 0) return 0;
   return make_plan(M, N, KN, KS, KO, nullptr).total;

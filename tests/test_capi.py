@@ -74,3 +74,53 @@ def test_python_mirror_has_reference_entry_points():
         "W", "reorder_index", "KN", "KS", "KO", "seqlen", "outfeatures"]
     assert list(inspect.signature(mg.matmul).parameters)[:12] == [
         "AN", "BN", "AS", "BS", "AO", "BO", "SFAN", "SFBN", "SFAS", "SFBS", "SFAO", "SFBO"]
+
+
+def _schedule(lib, tiles, cost, clusters):
+    n = len(tiles)
+    total = sum(tiles)
+    use = ctypes.c_int(-1)
+    off = (ctypes.c_uint16 * (clusters + 1))()
+    tile = (ctypes.c_uint16 * max(total, 1))()
+    st = lib.mg_pair_schedule(n, (ctypes.c_int * n)(*tiles), (ctypes.c_int * n)(*cost), clusters, ctypes.byref(use),
+                              off, tile)
+    assert st == 0
+    return use.value, list(off), list(tile)[:total]
+
+
+def test_tile_schedule_of_a_multi_problem_launch(lib):
+    """The order the CTA-pair GEMM computes a list of problems in (mg_pair_schedule, host only): every
+    tile exactly once, every SM pair's tiles in list order, the busiest pair within one tile of the
+    mean, and round-robin where a table would change nothing."""
+    # the Llama-3-8B step: gate, up (448 tiles of 22 + 1), down (128 of 78 + 1), q, k, v, o
+    tiles, cost, clusters = [448, 448, 128, 128, 32, 32, 128], [23, 23, 79, 23, 23, 23, 23], 74
+    use, off, tile = _schedule(lib, tiles, cost, clusters)
+    assert use == 1 and off[0] == 0 and off[clusters] == sum(tiles)
+    assert sorted(tile) == list(range(sum(tiles)))
+    per_tile = [c for n, c in zip(tiles, cost) for _ in range(n)]
+    loads = []
+    for c in range(clusters):
+        mine = tile[off[c]:off[c + 1]]
+        assert mine == sorted(mine) and len(mine) >= 1
+        loads.append(sum(per_tile[t] for t in mine))
+    mean = sum(per_tile) / clusters
+    assert max(loads) <= mean + max(cost)
+    rr = [sum(per_tile[t] for t in range(c, sum(tiles), clusters)) for c in range(clusters)]
+    assert max(loads) < max(rr)                      # better than dealing the list out round-robin
+    # equal costs, one problem, or no more tiles than pairs: round-robin
+    assert _schedule(lib, [448, 128], [23, 23], 74)[0] == 0
+    assert _schedule(lib, [500], [23], 74)[0] == 0
+    assert _schedule(lib, [40, 20], [23, 79], 74)[0] == 0
+    assert _schedule(lib, [6000, 3000], [23, 79], 74)[0] == 0      # more tiles than the table holds
+    # the same list again comes from the cache and is the same
+    assert _schedule(lib, tiles, cost, clusters) == (use, off, tile)
+    # five different lists push it out of the four-entry cache and back in
+    for k in range(5):
+        _schedule(lib, [100 + k, 50], [10, 30], 60)
+    assert _schedule(lib, tiles, cost, clusters) == (use, off, tile)
+    assert lib.mg_pair_schedule(0, None, None, 74, None, None, None) == 2
+    n2 = (ctypes.c_int * 2)(10, 10)
+    u = ctypes.c_int()
+    buf = (ctypes.c_uint16 * 200)()
+    assert lib.mg_pair_schedule(2, n2, n2, 97, ctypes.byref(u), buf, buf) == 1
+    assert lib.mg_pair_schedule(9, n2, n2, 74, ctypes.byref(u), buf, buf) == 1
