@@ -168,6 +168,32 @@ def _align(n, a=1024):
     return (n + a - 1) // a * a
 
 
+def exchange_layout(shapes, world):
+    """Where things lie in one buffer set of the overlapped exchange (host arithmetic only).
+    shapes = [(M, (KN, KS, KO)), ...], the activations of a step.  Returns (parts, block_bytes,
+    flag_off, total_bytes): the set is `world` blocks of block_bytes (block r = what rank r quantises)
+    followed by `world` int32 flags at flag_off; parts[i] = (rows per rank, logical row bytes of the
+    three code tensors, their row pitches, byte sizes of the six parts, their offsets inside a block)
+    for activation i.  Every part starts on a 1 KB boundary, which the tensor maps (32 bytes), the
+    scale copies (16) and the 16-byte loads of the push kernel all accept."""
+    lib = _capi.load()
+    parts, off = [], 0
+    for (M, split) in shapes:
+        if M % (256 * world) != 0:
+            raise ValueError("M = %d must split into %d shards of whole 256-row blocks" % (M, world))
+        mp = M // world
+        logical = (split[0] // 2, split[1] // 4 * 3, split[2])
+        pitch = [lib.mg_code_pitch(0, i, k) for i, k in enumerate(split)]
+        sizes = [mp * p for p in pitch] + [lib.mg_sf_bytes(mp, k) for k in split]
+        offs = []
+        for n in sizes:
+            offs.append(off)
+            off += _align(n)
+        parts.append((mp, logical, pitch, sizes, offs))
+    flag_off = world * off
+    return parts, off, flag_off, flag_off + _align(4 * world)
+
+
 class PushExchange:
     """Exchange buffers for `n_sets` steps' worth of quantised activations (shapes = [(M, (KN, KS, KO)), ...],
     the activations of one step).  A set is one device allocation, laid out identically on every rank
@@ -202,23 +228,8 @@ class PushExchange:
         self.streams = [torch.cuda.Stream(device=device) for _ in range(max(world - 1, 1))]
         self.sets = []
         handles = []
-        # the block of one rank: per activation six parts, each aligned to 1 KB
-        parts, off = [], 0
-        for (M, split) in self.shapes:
-            if M % (256 * world) != 0:
-                raise ValueError("M = %d must split into %d shards of whole 256-row blocks" % (M, world))
-            mp = M // world
-            logical = (split[0] // 2, split[1] // 4 * 3, split[2])
-            pitch = [lib.mg_code_pitch(0, i, k) for i, k in enumerate(split)]
-            sizes = [mp * p for p in pitch] + [lib.mg_sf_bytes(mp, k) for k in split]
-            offs = []
-            for n in sizes:
-                offs.append(off)
-                off += _align(n)
-            parts.append((mp, logical, pitch, sizes, offs))
+        parts, off, self.flag_off, total = exchange_layout(self.shapes, world)
         self.block_bytes = off
-        self.flag_off = world * off
-        total = self.flag_off + _align(4 * world)
         with torch.cuda.device(device):
             for s in range(n_sets):
                 ptr = ctypes.c_void_p()

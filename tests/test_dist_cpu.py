@@ -133,3 +133,35 @@ def test_sharded_activation_describes_equally_spaced_blocks():
         ShardedActivation([shard(0, 64), shard(1, 64)])      # not whole scale blocks
     with pytest.raises(RuntimeError):
         ShardedActivation([shard(0), shard(1)[:5]])          # not six tensors
+
+
+def test_exchange_buffer_layout():
+    """exchange_layout (host arithmetic of the overlapped exchange): parts do not overlap, start on
+    1 KB boundaries, hold whole rows and whole scale atoms of a rank's M / P rows; the 70B step's block
+    is the 17.25 MB per rank that the design quotes for 8 GPUs; bad shapes are refused."""
+    from mixedgemm_b200 import dist as mgd
+    from mixedgemm_b200 import _capi
+    lib = _capi.load()
+    shapes = [(4096, (5120, 2816, 256))] * 3 + [(4096, (17920, 9856, 896))]
+    for world in (1, 2, 4, 8):
+        parts, block, flag_off, total = mgd.exchange_layout(shapes, world)
+        assert flag_off == world * block and total >= flag_off + 4 * world and block % 1024 == 0
+        spans = []
+        for (M, split), (mp, logical, pitch, sizes, offs) in zip(shapes, parts):
+            assert mp == M // world
+            assert logical == (split[0] // 2, split[1] // 4 * 3, split[2])
+            for i in range(3):
+                assert pitch[i] >= logical[i] and pitch[i] % 16 == 0 and sizes[i] == mp * pitch[i]
+                assert sizes[3 + i] == lib.mg_sf_bytes(mp, split[i]) == (mp // 128) * ((split[i] + 127) // 128) * 512
+            for o, n in zip(offs, sizes):
+                assert o % 1024 == 0
+                spans.append((o, o + n))
+        spans.sort()
+        assert spans[0][0] == 0 and spans[-1][1] <= block
+        assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))
+    assert mgd.exchange_layout(shapes, 8)[1] == 17252352
+    assert mgd.exchange_layout(shapes, 4)[1] == 34504704
+    with pytest.raises(ValueError):
+        mgd.exchange_layout([(4096, (5120, 2816, 256))], 3)
+    with pytest.raises(ValueError):
+        mgd.exchange_layout([(1024, (256, 128, 128))], 8)     # 128 rows per rank: not whole 256-row tile pairs

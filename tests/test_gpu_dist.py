@@ -240,3 +240,54 @@ def test_push_kernel_on_one_gpu():
     assert lib.mg_push_block(2, 2, bases, 0, 32, 4096, e, c, 0, None) == 1
     assert lib.mg_push_block(2, 0, bases, 0, 32, 4096, None, c, 0, None) == 2     # MG_ERR_NULL
     assert lib.mg_push_block(2, 0, None, 0, 32, 4096, e, c, 0, None) == 2
+
+
+def test_push_exchange_with_one_rank():
+    """The exchange object on a single GPU (world = 1: buffers, layout, epochs, flags, the GEMM
+    reading the block layout through its ready flags) in all three push modes, eagerly and
+    replayed from a CUDA graph."""
+    import mixedgemm_b200 as mg
+    from mixedgemm_b200 import dist as mgd
+    from tests import helpers as H
+    dev = torch.device("cuda", 0)
+    Mq, Nq = 512, 512
+    KN, KS, KO = SPLIT
+    K = sum(SPLIT)
+    X = H.make_x(Mq, K, seed=41).cuda()
+    W = H.make_w(Nq, K, seed=42).cuda()
+    idx = H.reorder_index(X.cpu()).cuda()
+    B = mg.reorder_quantize_w(W, idx, KN, KS, KO, Mq, Nq)
+    A = mg.reorder_quantize_x(X, idx, KN, KS, KO, Mq, Nq)
+    want = mg.matmul(A[0], B[0], A[1], B[1], A[2], B[2], A[3], B[3], A[4], B[4], A[5], B[5])
+    for mode in ("sm", "ce", "hybrid"):
+        ex = mgd.PushExchange([(Mq, SPLIT)], 1, 0, dev, n_sets=2, mode=mode)
+        out = torch.zeros((Mq, Nq), dtype=torch.bfloat16, device=dev)
+
+        def step(s):
+            ex.begin_step(s)
+            mg.reorder_quantize_x_multi([(X, idx, KN, KS, KO, ex.shard(s, 0))])
+            ex.push(s)
+            mg.matmul_multi([(ex.buffers(s, 0), B, out)], flags=[ex.ready(s, 0)])
+            ex.join()
+
+        for s in (0, 1, 0):
+            out.zero_()
+            step(s)
+            torch.cuda.synchronize()
+            assert torch.equal(out.view(torch.int16), want.view(torch.int16)), (mode, s)
+        st = torch.cuda.Stream()
+        with torch.cuda.stream(st):
+            step(1)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                step(0)
+                step(1)
+            for _ in range(3):
+                out.zero_()
+                g.replay()
+            torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int16), want.view(torch.int16)), mode
+        assert mg.device_status() == 0
+        assert int(ex.epoch[0]) >= 4 and torch.all(ex.sets[0]["flags"] == ex.epoch[0])
+        ex.close()
