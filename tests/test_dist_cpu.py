@@ -165,3 +165,52 @@ def test_exchange_buffer_layout():
         mgd.exchange_layout([(4096, (5120, 2816, 256))], 3)
     with pytest.raises(ValueError):
         mgd.exchange_layout([(1024, (256, 128, 128))], 8)     # 128 rows per rank: not whole 256-row tile pairs
+
+
+def _sets_are_safe(n_sets, world=3, steps=14):
+    """Happens-before model of the pipelined exchange.  Per rank x and step k: P[x,k] = the push of batch
+    k + 1 into set (k + 1) % n of every peer, issued in step k; R[x,k] = the GEMM reading set k % n.
+    Orders that the streams and the ready flags enforce:
+      R[x,k-1] -> P[x,k]      the push of step k is issued after the GEMM of step k - 1 (stream order)
+      R[x,k-1] -> R[x,k]
+      P[y,k-1] -> R[x,k]      the GEMM of batch k waits for every peer's push of batch k
+    Safe means: every push into a set is ordered after the target's last GEMM on that set."""
+    import itertools
+    nodes = [(t, x, k) for t in "PR" for x in range(world) for k in range(steps)]
+    succ = {v: set() for v in nodes}
+    for x in range(world):
+        for k in range(1, steps):
+            succ[("R", x, k - 1)].add(("P", x, k))
+            succ[("R", x, k - 1)].add(("R", x, k))
+            for y in range(world):
+                if y != x:
+                    succ[("P", y, k - 1)].add(("R", x, k))
+
+    def reaches(a, b):
+        seen, todo = {a}, [a]
+        while todo:
+            v = todo.pop()
+            if v == b:
+                return True
+            for w in succ[v]:
+                if w not in seen:
+                    seen.add(w)
+                    todo.append(w)
+        return False
+
+    for x, y in itertools.permutations(range(world), 2):
+        for k in range(steps):
+            last_read = k + 1 - n_sets          # y's previous GEMM on the set that x's push of step k overwrites
+            if last_read >= 0 and not reaches(("R", y, last_read), ("P", x, k)):
+                return False
+    return True
+
+
+def test_four_buffer_sets_make_the_pipelined_exchange_safe():
+    """The claim behind PushExchange's `n_sets`: when the push of batch i + 1 is issued before the GEMM
+    of batch i, a rank can overwrite a peer's set only after the peer's last GEMM on it if FOUR sets
+    rotate; with three it cannot be shown (a fast rank may run ahead of a slow one by that much)."""
+    assert _sets_are_safe(4)
+    assert _sets_are_safe(5)
+    assert not _sets_are_safe(3)
+    assert not _sets_are_safe(2)
