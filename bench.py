@@ -2,14 +2,15 @@
 """Benchmark of the hot path: activation reorder-and-quantise + mixed MXFP4/6/8 GEMM.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                  [--workload NAME] [--exchange push|push-ce|push-sm|push-hybrid|allgather|bcast|replicated] [--no-graph] [--no-fuse]
+                  [--workload NAME] [--exchange push|push-ce|push-sm|push-hybrid|allgather|bcast|replicated]
+                  [--no-pipeline] [--quantize each|multi] [--no-graph] [--no-fuse] [--no-extra]
   python bench.py --kernel gemm|reorder --shape M,N,K     one kernel, one shape
   python bench.py --sweep decode|square|all               the other benchmark configurations, a line per shape
 
 One "step" is one pass over a projection set of a Llama-shaped layer stack: every distinct
-activation is reorder-quantised once and multiplied with each weight that consumes it
-(q/k/v share one activation, gate/up another); all products of the step go out as one GEMM
-launch.  Weights are quantised once, outside the timed region, as in deployment.
+activation is reorder-quantised once (all of them in one launch) and multiplied with each weight
+that consumes it (q/k/v share one activation, gate/up another); all products of the step go out as
+one GEMM launch.  Weights are quantised once, outside the timed region, as in deployment.
 
   N = 1 (default)   workload llama3-8b-m2048 (M = 2048 tokens on the Llama-3-8B projections)
   N > 1             workload llama3-70b-m4096: weights sharded along N over the ranks.  --exchange
